@@ -1,0 +1,190 @@
+"""The description of one step's batch, as the kernels read it.
+
+The reference's step takes parallel arrays ``tokens[m], positions[m], slots[m]``;
+rows of one slot at consecutive positions are a prompt portion, and causality
+inside a portion comes from the positions alone because every row's key and
+value are written before any row attends (zllm src/backend/gpu/mod.rs:2165,
+2245-2253, 2485-2491).  The same here, plus what tiled kernels want: which rows
+are single decoded tokens, and the portions cut into query tiles.
+
+All integer arrays of a step live in ONE pinned host buffer and ONE device
+buffer with fixed section offsets, so a step costs one host-to-device copy and
+a captured graph can be replayed on new contents.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+QUERY_TILE = 64          # rows of one portion that one attention tile covers
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its slot, its next tokens, and the places among
+    them whose logits are wanted."""
+
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepBuffers:
+    """Pinned host + device int32 storage for a step of at most ``cap_rows`` rows."""
+
+    SECTIONS = ("token_ids", "positions", "row_slot", "want_rows", "decode_rows", "tiles", "temps", "seeds")
+
+    def __init__(self, cap_rows: int, cap_want: int, device):
+        self.cap_rows = cap_rows
+        self.cap_want = cap_want
+        self.cap_tiles = cap_rows  # every portion has >= 2 rows, so tiles <= rows
+        sizes = {"token_ids": cap_rows, "positions": cap_rows, "row_slot": cap_rows, "want_rows": cap_want,
+                 "decode_rows": cap_rows, "tiles": 4 * self.cap_tiles, "temps": cap_want, "seeds": cap_want}
+        self.offsets = {}
+        off = 0
+        for name in self.SECTIONS:
+            self.offsets[name] = (off, sizes[name])
+            off += sizes[name]
+        self.total = off
+        dev = torch.device(device)
+        self.host = torch.zeros(off, dtype=torch.int32)
+        if dev.type == "cuda":
+            self.host = self.host.pin_memory()
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(off, dtype=torch.int32, device=dev)
+        self.copied = torch.cuda.Event() if dev.type == "cuda" else None
+        self._pending = False
+
+    def host_section(self, name):
+        o, n = self.offsets[name]
+        return self.np[o:o + n]
+
+    def dev_section(self, name, n=None):
+        o, size = self.offsets[name]
+        return self.dev[o:o + (size if n is None else n)]
+
+    def begin_fill(self):
+        if self._pending and self.copied is not None:
+            self.copied.synchronize()   # the previous copy must have read the pinned buffer
+            self._pending = False
+
+    def upload(self):
+        self.dev.copy_(self.host, non_blocking=True)
+        if self.copied is not None:
+            self.copied.record()
+            self._pending = True
+
+
+@dataclass
+class StepContext:
+    """What parts and kernels see of a step."""
+
+    T: int                       # rows in this step (for a replayed graph: the bucket size)
+    R: int                       # rows whose logits are wanted
+    token_ids: torch.Tensor      # [T] int32
+    positions: torch.Tensor      # [T] int32 absolute position of each row
+    row_slot: torch.Tensor       # [T] int32 slot of each row (-1: padding row, skipped)
+    want_rows: torch.Tensor      # [R] int32
+    decode_rows: torch.Tensor    # [n_decode] int32 rows that are single decoded tokens
+    n_decode: int
+    tiles: torch.Tensor          # [n_tiles, 4] int32: first row, rows, slot, position of first row
+    n_tiles: int
+    max_context: int             # largest position + 1 among the rows (bounds split counts)
+    ws: object = None            # workspace
+    entries: Optional[List[StepEntry]] = None
+    starts: Optional[List[int]] = None
+    fixed_splits: int = 0        # > 0: the split count a captured graph was recorded with
+
+
+def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[int], pad_rows: int = 0):
+    """Write the step's arrays into ``buf`` (host side) and return the counts.
+
+    ``starts[i]`` is the position of entry i's first token.  ``pad_rows`` > 0
+    pads the row arrays to that many rows with slot -1 (for graph buckets).
+    """
+    buf.begin_fill()
+    tok = buf.host_section("token_ids")
+    pos = buf.host_section("positions")
+    rs = buf.host_section("row_slot")
+    want = buf.host_section("want_rows")
+    dec = buf.host_section("decode_rows")
+    tiles = buf.host_section("tiles")
+    r = 0
+    nw = 0
+    nd = 0
+    nt = 0
+    max_ctx = 0
+    for e, start in zip(entries, starts):
+        n = len(e.tokens)
+        tok[r:r + n] = e.tokens
+        pos[r:r + n] = np.arange(start, start + n, dtype=np.int32)
+        rs[r:r + n] = e.slot
+        for w in e.want:
+            if not 0 <= w < n:
+                raise IndexError(f"wanted place {w} outside the entry's {n} tokens")
+            want[nw] = r + w
+            nw += 1
+        if n == 1:
+            dec[nd] = r
+            nd += 1
+        else:
+            for q0 in range(0, n, QUERY_TILE):
+                m = min(QUERY_TILE, n - q0)
+                tiles[4 * nt:4 * nt + 4] = (r + q0, m, e.slot, start + q0)
+                nt += 1
+        max_ctx = max(max_ctx, start + n)
+        r += n
+    T = r
+    if pad_rows > T:
+        tok[T:pad_rows] = 0
+        pos[T:pad_rows] = 0
+        rs[T:pad_rows] = -1
+        for i in range(T, pad_rows):
+            dec[nd] = i
+            nd += 1
+        T = pad_rows
+    return T, nw, nd, nt, max_ctx
+
+
+def make_context(buf: StepBuffers, T, R, nd, nt, max_ctx, ws, entries=None, starts=None) -> StepContext:
+    return StepContext(
+        T=T, R=R,
+        token_ids=buf.dev_section("token_ids", T),
+        positions=buf.dev_section("positions", T),
+        row_slot=buf.dev_section("row_slot", T),
+        want_rows=buf.dev_section("want_rows", R),
+        decode_rows=buf.dev_section("decode_rows", nd),
+        n_decode=nd,
+        tiles=buf.dev_section("tiles", 4 * nt).view(-1, 4) if nt else buf.dev_section("tiles", 0).view(0, 4),
+        n_tiles=nt,
+        max_context=max_ctx,
+        ws=ws, entries=list(entries) if entries is not None else None, starts=list(starts) if starts else None,
+    )
+
+
+class Workspace:
+    """Named scratch buffers, allocated once at their largest first dimension."""
+
+    def __init__(self, max_rows: int, device):
+        self.max_rows = max_rows
+        self.device = torch.device(device)
+        self._bufs = {}
+
+    def get(self, name: str, shape, dtype, cap=None) -> torch.Tensor:
+        """A [rows, ...] view of the buffer ``name``.  The buffer is made for ``cap`` rows
+        (default: the step's row limit) the first time and only ever grows."""
+        rows = shape[0]
+        rest = tuple(shape[1:])
+        key = (name, rest, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.shape[0] < rows:
+            cap = max(rows, self.max_rows if cap is None else cap)
+            buf = torch.empty((cap, *rest), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:rows]
+
+    def bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())

@@ -1,0 +1,268 @@
+"""The step function: one batch of (request, its next tokens) through the model,
+from the cache, logits at the wanted places.
+
+After the reference's ``BatchedDecoder`` step (zllm src/backend/gpu/mod.rs:2180-2243:
+write inputs -> prepare paging -> layers -> final norm -> head -> select) and its
+prefill chunk (mod.rs:2383-2421), with one difference: portions of prompts and
+single decoded tokens of other requests go through ONE forward, cut anywhere.
+A step runs only the tokens it is given; every earlier position comes from the
+cache.  Pool exhaustion is an error return (MemoryError_) raised before
+anything is launched, where the reference panics (mod.rs:2508-2509).
+
+Decode-only steps replay a captured CUDA graph per (rows, split-count) bucket,
+since at small batch the step is bound by launches, not by memory.
+"""
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.engine_config import EngineConfig
+from ..config.model_config import read_config_json
+from ..config.registry import architecture_of
+from ..errors import BackendError, ConfigError, MemoryError_, RequestError
+from ..models.decoder import DecoderModel, Runtime
+from ..weights.loader import load_checked, target_dtype
+from ..weights.random_init import random_tensor
+from .batch import StepBuffers, StepContext, StepEntry, Workspace, fill_step, make_context
+
+_TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+def _default_ops(device):
+    from ..kernels.ops import CudaOps
+    return CudaOps(device)
+
+
+class ModelRunner:
+    """Model + cache + step function on one device."""
+
+    def __init__(self, model_dir=None, *, config=None, seed: Optional[int] = None,
+                 engine_config: Optional[EngineConfig] = None, ops=None, init_std=None, norm_std=None):
+        self.ecfg = (engine_config or EngineConfig()).validate()
+        self.device = torch.device(self.ecfg.device)
+        self.dtype = _TORCH_DTYPE[self.ecfg.dtype]
+        if ops is None:
+            if self.device.type != "cuda":
+                raise BackendError("the engine runs on a CUDA device only; there is no CPU path")
+            ops = _default_ops(self.device)
+        self.ops = ops
+        ops.configure(self.dtype)
+        if model_dir is not None:
+            raw = read_config_json(model_dir)
+            arch = architecture_of(raw)
+            self.config = arch.read_config(raw)
+        elif config is not None:
+            from ..config.registry import architecture
+            arch = architecture(config.architecture)
+            self.config = config
+        else:
+            raise ConfigError("ModelRunner needs a model folder or a configuration")
+        self.spec = arch.build_spec(self.config)
+        rt = Runtime(self.dtype, self.device, ops)
+        self.model = DecoderModel(self.spec, rt)
+        expected = self.model.expected_tensors()
+        if model_dir is not None:
+            tensors = load_checked(model_dir, expected, self.dtype, self.device)
+        else:
+            tensors = {}
+            for name, ws in expected.items():
+                dt = target_dtype(torch.bfloat16 if self.dtype == torch.bfloat16 else torch.float32, ws.role, self.dtype)
+                tensors[name] = random_tensor(name, ws, seed or 0, dt, self.device, init_std, norm_std)
+        self.model.load_weights(tensors)
+        del tensors
+
+        self.max_len = min(self.ecfg.max_model_len or self.spec.max_position, self.spec.max_position)
+        bs = self.ecfg.block_size
+        needs = self.model.cache_needs()
+        num_blocks = self.ecfg.num_blocks
+        if num_blocks is None:
+            num_blocks = self.ecfg.max_num_seqs * (-(-self.max_len // bs))
+            num_blocks = min(num_blocks, self._blocks_that_fit(needs, bs))
+        self.cache = CacheManager(needs, bs, num_blocks, self.ecfg.max_num_seqs, self.max_len, self.dtype, self.device)
+        self.max_rows = self.ecfg.max_num_batched_tokens
+        self.ws = Workspace(self.max_rows, self.device)
+        self.buffers = StepBuffers(self.max_rows, self.max_rows, self.device)
+        self._graphs: Dict[tuple, dict] = {}
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ------------------------------------------------------------------
+    def _blocks_that_fit(self, needs, bs) -> int:
+        if self.device.type != "cuda":
+            return 1 << 30
+        per_block = 0
+        el = 2 if self.dtype == torch.bfloat16 else 4
+        for spec, cache_of in needs:
+            if cache_of is None and spec is not None and hasattr(spec, "n_kv_heads"):
+                per_block += 2 * bs * spec.n_kv_heads * spec.head_dim * el
+        if per_block == 0:
+            return 1
+        free, _ = torch.cuda.mem_get_info(self.device)
+        return max(1, int(free * 0.6) // per_block)
+
+    # ---- slots -----------------------------------------------------------
+    def admit(self) -> Optional[int]:
+        return self.cache.admit()
+
+    def release(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    def cached_len(self, slot: int) -> int:
+        return self.cache.length[slot]
+
+    # ---- the step ----------------------------------------------------------
+    def _prepare(self, entries: Sequence[StepEntry]):
+        if not entries:
+            raise RequestError("a step needs at least one entry")
+        total = 0
+        seen = set()
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise RequestError(f"slot {e.slot}: an entry needs at least one token")
+            if e.slot in seen:
+                raise RequestError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if not self.cache.live[e.slot]:
+                raise RequestError(f"slot {e.slot} is not live")
+            if self.cache.length[e.slot] + n > self.max_len:
+                raise RequestError(f"slot {e.slot}: position {self.cache.length[e.slot] + n} exceeds the "
+                                   f"maximum length {self.max_len}")
+            total += n
+        if total > self.max_rows:
+            raise RequestError(f"step of {total} tokens exceeds max_num_batched_tokens {self.max_rows}")
+        # pages for everything, or nothing is run
+        if not self.cache.can_fit([(e.slot, self.cache.length[e.slot] + len(e.tokens)) for e in entries]):
+            raise MemoryError_(f"cache pool exhausted: free pages {self.cache.free_pages()} do not cover this step")
+        starts = []
+        for e in entries:
+            start = self.cache.length[e.slot]
+            ok = self.cache.ensure(e.slot, start + len(e.tokens))
+            assert ok
+            starts.append(start)
+        return starts
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries as one batch.  Returns float32 logits [wanted, vocab] on the
+        device, in the order of the entries and of their ``want`` (None if nothing is wanted).
+        The tensor is a view of a reused buffer: read it before the next step."""
+        starts = self._prepare(entries)
+        buf = self.buffers
+        T, R, nd, nt, max_ctx = fill_step(buf, entries, starts)
+        buf.upload()
+        self.cache.sync_tables()
+        ctx = make_context(buf, T, R, nd, nt, max_ctx, self.ws, entries, starts)
+        logits = self.model.forward(ctx, self.cache.views)
+        for e, s in zip(entries, starts):
+            self.cache.advance(e.slot, s + len(e.tokens))
+        self.steps += 1
+        self.tokens_run += T
+        return logits
+
+    # ---- decode-only steps through a captured graph ----------------------------
+    def decode_step(self, slots: Sequence[int], tokens: Sequence[int], temps: Sequence[float],
+                    seeds: Sequence[int]) -> torch.Tensor:
+        """One decoded token for each slot; samples on the device (temperature <= 0: argmax)
+        and returns the int32 token ids [len(slots)] on the device.  The logits of the step
+        stay in ``self.last_logits`` ([bucket, vocab], first len(slots) rows valid)."""
+        entries = [StepEntry(s, (t,), (0,)) for s, t in zip(slots, tokens)]
+        starts = self._prepare(entries)
+        n = len(entries)
+        use_graph = self.ecfg.cuda_graphs and self.device.type == "cuda"
+        bucket = _bucket(n) if use_graph else n
+        max_ctx = max(starts) + 1
+        split_bucket = _bucket(self.ops.decode_splits(max_ctx)) if use_graph else 0
+        key = (bucket, split_bucket)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._make_decode_graph(bucket, split_bucket, use_graph)
+            self._graphs[key] = g
+        buf = g["buf"]
+        T, R, nd, nt, _ = fill_step(buf, entries, starts, pad_rows=bucket)
+        # every row of the bucket is "wanted" so that the graph's shapes never change
+        want = buf.host_section("want_rows")
+        want[:bucket] = range(bucket)
+        tf = buf.host_section("temps").view("float32")
+        tf[:bucket] = 0.0
+        tf[:n] = temps
+        sd = buf.host_section("seeds").view("uint32")
+        sd[:bucket] = 0
+        sd[:n] = [s & 0xFFFFFFFF for s in seeds]
+        buf.upload()
+        self.cache.sync_tables()
+        if use_graph:
+            g["graph"].replay()
+        else:
+            self._decode_body(g)
+        for e, s in zip(entries, starts):
+            self.cache.advance(e.slot, s + 1)
+        self.steps += 1
+        self.tokens_run += n
+        self.last_logits = g["logits"]
+        return g["out"][:n]
+
+    def _decode_body(self, g):
+        ctx = g["ctx"]
+        logits = self.model.forward(ctx, self.cache.views)
+        g["logits"] = logits
+        buf = g["buf"]
+        B = ctx.T
+        self.ops.sample(logits, buf.dev_section("temps", B).view(torch.float32), buf.dev_section("seeds", B), g["out"])
+
+    def _make_decode_graph(self, bucket: int, split_bucket: int, use_graph: bool):
+        buf = StepBuffers(bucket, bucket, self.device)
+        ctx = make_context(buf, bucket, bucket, bucket, 0, 0, self.ws)
+        ctx.max_context = split_bucket * self.ops.decode_split_keys if split_bucket else 0
+        ctx.fixed_splits = split_bucket
+        out = torch.zeros(bucket, dtype=torch.int32, device=self.device)
+        g = {"buf": buf, "ctx": ctx, "out": out, "logits": None, "graph": None}
+        if not use_graph:
+            return g
+        # neutral contents for warm-up and capture: every row is padding
+        buf.begin_fill()
+        buf.host_section("row_slot")[:] = -1
+        buf.host_section("decode_rows")[:bucket] = range(bucket)
+        buf.host_section("want_rows")[:bucket] = range(bucket)
+        buf.upload()
+        torch.cuda.synchronize(self.device)
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._decode_body(g)          # warm-up: sizes every workspace buffer
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._decode_body(g)
+        g["graph"] = graph
+        return g
+
+    # ---- numbers for measurement ------------------------------------------------
+    def weight_bytes(self) -> int:
+        seen = set()
+        total = 0
+        def add(t):
+            nonlocal total
+            if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        add(self.model.embedding if self.model.head is not self.model.embedding else None)
+        add(self.model.head)
+        for layer in self.model.layers:
+            for part in layer.parts().values():
+                for v in vars(part).values():
+                    add(v)
+        for v in vars(self.model.final_norm).values():
+            add(v)
+        return total
+
+
+def _bucket(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b

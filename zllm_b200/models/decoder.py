@@ -1,0 +1,132 @@
+"""A decoder assembled from a ``ModelSpec``: embedding, layers in their run
+order, final norm, output head.
+
+Order of one forward as in zllm src/backend/candle/quantized_llama_fork.rs:920-987:
+embed (935), layers (936-968), final norm (971), select the wanted rows (972),
+head (980).  The reference computes logits only for the last row of a call;
+here only for the rows the batch asks for.  A missing head tensor means the
+head is the embedding table (fork.rs:761-764).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from ..errors import ConfigError
+from ..parts.base import ModelSpec, PartSpec, WeightSpec, build_part, _REGISTRIES
+from ..parts.block import Layer
+
+
+@dataclass
+class Runtime:
+    """What parts get at bind time: compute dtype, device and the kernel table."""
+
+    dtype: torch.dtype
+    device: torch.device
+    ops: object
+
+
+def _build_layers(spec: ModelSpec):
+    memo: Dict[str, object] = {}
+
+    def build(group, pspec: PartSpec):
+        params = dict(pspec.params)
+        pe = params.get("position_encoding")
+        if isinstance(pe, PartSpec):
+            key = repr((pe.kind, sorted(pe.params.items(), key=lambda kv: kv[0])))
+            if key not in memo:
+                memo[key] = build_part("position_encoding", pe)
+            params["position_encoding"] = memo[key]
+        return build_part(group, PartSpec(pspec.kind, params))
+
+    layers = []
+    for ls in spec.layers:
+        if ls.arrangement not in _REGISTRIES["arrangement"]:
+            raise ConfigError(f"unknown arrangement {ls.arrangement!r}")
+        layers.append(Layer(build("norm", ls.norm1), build("mixer", ls.mixer), build("norm", ls.norm2),
+                            build("feed_forward", ls.ffn), _REGISTRIES["arrangement"][ls.arrangement]))
+    final_norm = build("norm", spec.final_norm)
+    return layers, final_norm
+
+
+def _named_specs(spec: ModelSpec, layers: List[Layer], final_norm) -> Dict[str, WeightSpec]:
+    out: Dict[str, WeightSpec] = {}
+    out[spec.embedding_name] = WeightSpec((spec.vocab_size, spec.hidden_size), "embedding", ("normal", spec.init_std))
+    for li, (ls, layer) in enumerate(zip(spec.layers, layers)):
+        for pname, part in layer.parts().items():
+            for local, ws in part.weight_specs().items():
+                key = f"{pname}.{local}"
+                if key not in ls.tensor_names:
+                    raise ConfigError(f"layer {li}: no tensor name given for {key}")
+                out[ls.tensor_names[key]] = ws
+    for local, ws in final_norm.weight_specs().items():
+        out[spec.final_norm_names[local]] = ws
+    if spec.head_name is not None:
+        out[spec.head_name] = WeightSpec((spec.vocab_size, spec.hidden_size), "matrix", ("normal", spec.init_std))
+    return out
+
+
+def expected_tensors(spec: ModelSpec) -> Dict[str, WeightSpec]:
+    """Every tensor the model folder must hold: name -> shape, role, init."""
+    layers, final_norm = _build_layers(spec)
+    return _named_specs(spec, layers, final_norm)
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+        self.layers, self.final_norm = _build_layers(spec)
+        for i, e in enumerate(spec.run_order):
+            if not 0 <= e.layer < len(self.layers):
+                raise ConfigError(f"run order entry {i} names layer {e.layer}, the model has {len(self.layers)}")
+            if e.cache_of is not None and not (0 <= e.cache_of < i and spec.run_order[e.cache_of].cache_of is None):
+                raise ConfigError(f"run order entry {i}: cache_of must name an earlier entry that owns its cache")
+        for layer in self.layers:
+            for part in layer.parts().values():
+                part.bind(rt)
+        self.final_norm.bind(rt)
+        self.embedding = None
+        self.head = None
+
+    # ---- weights -------------------------------------------------------
+    def expected_tensors(self) -> Dict[str, WeightSpec]:
+        return _named_specs(self.spec, self.layers, self.final_norm)
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        spec = self.spec
+        self.embedding = tensors[spec.embedding_name]
+        for ls, layer in zip(spec.layers, self.layers):
+            for pname, part in layer.parts().items():
+                local = {name: tensors[ls.tensor_names[f"{pname}.{name}"]] for name in part.weight_specs()}
+                part.load(local)
+        self.final_norm.load({n: tensors[spec.final_norm_names[n]] for n in self.final_norm.weight_specs()})
+        self.head = tensors[spec.head_name] if spec.head_name is not None else self.embedding
+
+    # ---- cache needs ---------------------------------------------------
+    def cache_needs(self):
+        """Per run entry: (cache spec of its mixer or None, cache_of)."""
+        return [(self.layers[e.layer].mixer.cache_spec(), e.cache_of) for e in self.spec.run_order]
+
+    # ---- one forward over the step's rows ------------------------------
+    def forward(self, ctx, cache_views) -> Optional[torch.Tensor]:
+        """Runs the rows of ``ctx``; returns float32 logits [R, V] for ``ctx.want_rows`` (None if R == 0)."""
+        ops, rt = self.rt.ops, self.rt
+        T = ctx.T
+        x = ctx.ws.get("residual", (T, self.spec.hidden_size), torch.float32)
+        ops.embedding(ctx.token_ids, self.embedding, x)
+        for i, e in enumerate(self.spec.run_order):
+            owner = i if e.cache_of is None else e.cache_of
+            self.layers[e.layer].run(x, ctx, cache_views[owner], write_cache=e.cache_of is None)
+        R = ctx.R
+        if R == 0:
+            return None
+        rows = ctx.ws.get("head_rows", (R, self.spec.hidden_size), torch.float32, cap=R)
+        ops.gather_rows(x, ctx.want_rows, rows)
+        hn = ctx.ws.get("head_in", (R, self.spec.hidden_size), rt.dtype, cap=R)
+        self.final_norm.forward(rows, hn, ctx)
+        logits = ctx.ws.get("logits", (R, self.spec.vocab_size), torch.float32, cap=R)
+        ops.linear(hn, self.head, logits, "store")
+        return logits
