@@ -1,0 +1,160 @@
+// Row-wise kernels: embedding gather, RMSNorm, SiLU-mul, row gather, rotary
+// encoding fused with the write of keys and values into cache pages.
+//
+// Counterparts in zllm (WGSL, src/backend/gpu/shaders.rs): BNORM 545-564, BROPE
+// 566-587, BKV_PACK 727-756, SILU_MUL 976-990; the embedding gather is done on
+// the host there (src/backend/gpu/mod.rs:2450-2458).  The fusion of rotation and
+// cache write follows its Vulkan path (decode_matvec_q4k_rope.comp).
+// All sums, roots and rotations are float32 whatever the activation dtype.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename WT>
+__global__ void embedding_kernel(const int* __restrict__ tok, const WT* __restrict__ table, float* __restrict__ out,
+                                 int H, int V) {
+    const int t = blockIdx.x;
+    const int id = tok[t];
+    float* o = out + (size_t)t * H;
+    if (id < 0 || id >= V) {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const WT* row = table + (size_t)id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+ZLLM_API int zllm_embedding(const int* tok, const void* table, float* out, int T, int H, int V, int table_bf16,
+                            void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (table_bf16) embedding_kernel<bf16><<<T, 256, 0, s>>>(tok, (const bf16*)table, out, H, V);
+    else embedding_kernel<float><<<T, 256, 0, s>>>(tok, (const float*)table, out, H, V);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- rmsnorm
+// y = x * rsqrt(mean(x^2) + eps) * w ; x float32 [T,H]; w float32 or bf16; y AT.
+template <typename WT, typename OT>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict__ w, OT* __restrict__ y, int H,
+                               float eps) {
+    __shared__ float red[33];
+    const float* xr = x + (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    OT* yr = y + (size_t)blockIdx.x * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_f32<OT>(xr[i] * inv * to_f32(w[i]));
+}
+
+ZLLM_API int zllm_rmsnorm(const float* x, const void* w, void* y, int T, int H, float eps, int w_bf16, int out_bf16,
+                          void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int th = H >= 1024 ? 256 : 128;
+    if (w_bf16 && out_bf16) rmsnorm_kernel<bf16, bf16><<<T, th, 0, s>>>(x, (const bf16*)w, (bf16*)y, H, eps);
+    else if (w_bf16) rmsnorm_kernel<bf16, float><<<T, th, 0, s>>>(x, (const bf16*)w, (float*)y, H, eps);
+    else if (out_bf16) rmsnorm_kernel<float, bf16><<<T, th, 0, s>>>(x, (const float*)w, (bf16*)y, H, eps);
+    else rmsnorm_kernel<float, float><<<T, th, 0, s>>>(x, (const float*)w, (float*)y, H, eps);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- silu * up
+template <typename AT>
+__global__ void silu_mul_kernel(const AT* __restrict__ g, const AT* __restrict__ u, AT* __restrict__ o, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        float a = to_f32(g[i]);
+        o[i] = from_f32<AT>(a / (1.f + expf(-a)) * to_f32(u[i]));
+    }
+}
+
+ZLLM_API int zllm_silu_mul(const void* g, const void* u, void* o, long long n, int is_bf16, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (is_bf16) silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)g, (const bf16*)u, (bf16*)o, (size_t)n);
+    else silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)g, (const float*)u, (float*)o, (size_t)n);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- gather rows (float32)
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, float* __restrict__ out,
+                                   int H) {
+    const float* src = x + (size_t)rows[blockIdx.x] * H;
+    float* dst = out + (size_t)blockIdx.x * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+}
+
+ZLLM_API int zllm_gather_rows(const float* x, const int* rows, float* out, int R, int H, void* stream) {
+    if (R <= 0) return 0;
+    gather_rows_kernel<<<R, 256, 0, (cudaStream_t)stream>>>(x, rows, out, H);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- rotary + cache write
+// qkv [T, (nq + 2 nkv) * hd]: q heads, then k heads, then v heads.  q and k are
+// rotated in place over their first rot_dim entries; then (store != 0 and slot >= 0)
+// k and v of the row go to the page of its position:
+//   page = table[slot * max_blocks + pos / bs];  element [page][kv head][pos % bs][d].
+// cos/sin: [max_pos, rot_dim/2] float32 tables of pos * theta_j (null: no rotation).
+template <typename AT>
+__global__ void rope_kv_store_kernel(AT* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ row_slot, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, int rot_dim, int interleaved,
+                                     AT* __restrict__ k_pages, AT* __restrict__ v_pages,
+                                     const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, int hd,
+                                     int store) {
+    const int t = blockIdx.x;
+    const int slot = row_slot[t];
+    if (slot < 0) return;                       // padding row of a graph bucket
+    const int pos = positions[t];
+    AT* row = qkv + (size_t)t * (nq + 2 * nkv) * hd;
+    const int half = rot_dim >> 1;
+    if (cos_t != nullptr) {
+        const float* c = cos_t + (size_t)pos * half;
+        const float* s = sin_t + (size_t)pos * half;
+        const int pairs = (nq + nkv) * half;
+        for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+            const int head = i / half, j = i - head * half;
+            AT* h = row + (size_t)head * hd;
+            const int ia = interleaved ? 2 * j : j;
+            const int ib = interleaved ? 2 * j + 1 : j + half;
+            const float a = to_f32(h[ia]), b = to_f32(h[ib]);
+            const float cj = c[j], sj = s[j];
+            h[ia] = from_f32<AT>(a * cj - b * sj);
+            h[ib] = from_f32<AT>(a * sj + b * cj);
+        }
+    }
+    if (!store) return;
+    __syncthreads();                            // rotated k visible to all threads of the row
+    const int page = table[(size_t)slot * max_blocks + pos / bs];
+    if (page < 0) return;                       // host guarantees a page; never write through a bad id
+    const int off = pos % bs;
+    const AT* k = row + (size_t)nq * hd;
+    const AT* v = k + (size_t)nkv * hd;
+    for (int i = threadIdx.x; i < nkv * hd; i += blockDim.x) {
+        const int kvh = i / hd, d = i - kvh * hd;
+        const size_t dst = (((size_t)page * nkv + kvh) * bs + off) * hd + d;
+        k_pages[dst] = k[i];
+        v_pages[dst] = v[i];
+    }
+}
+
+ZLLM_API int zllm_rope_kv_store(void* qkv, const int* positions, const int* row_slot, const float* cos_t,
+                                const float* sin_t, int rot_dim, int interleaved, void* k_pages, void* v_pages,
+                                const int* table, int max_blocks, int bs, int T, int nq, int nkv, int hd, int store,
+                                int is_bf16, void* stream) {
+    if (T <= 0) return 0;
+    if (rot_dim > hd || (rot_dim & 1)) return ZLLM_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (is_bf16)
+        rope_kv_store_kernel<bf16><<<T, 256, 0, s>>>((bf16*)qkv, positions, row_slot, cos_t, sin_t, rot_dim, interleaved,
+                                                     (bf16*)k_pages, (bf16*)v_pages, table, max_blocks, bs, nq, nkv, hd,
+                                                     store);
+    else
+        rope_kv_store_kernel<float><<<T, 256, 0, s>>>((float*)qkv, positions, row_slot, cos_t, sin_t, rot_dim,
+                                                      interleaved, (float*)k_pages, (float*)v_pages, table, max_blocks,
+                                                      bs, nq, nkv, hd, store);
+    return launch_status();
+}

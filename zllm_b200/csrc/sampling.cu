@@ -1,0 +1,139 @@
+// Sampling on the device, so that only token ids go back to the host.
+//
+// zllm's kernels (src/backend/gpu/shaders.rs): BARGMAX 758-789 (strict '>' keeps
+// the lowest index), BSAMPLE 791-850 (Gumbel-max: argmax_i(logit_i/temp -
+// log(-log u_i)), u_i = ((hash(seed ^ hash(i)) >> 8) + 0.5) / 2^24, temp <= 0 ->
+// plain argmax), BTOPK 852-905 (K rounds of "largest strictly below the previous
+// winner", value descending, index ascending).  Ties here ALWAYS resolve to the
+// lowest index, also across threads (the reference's tree reduction keeps the
+// lower thread, which is not always the lower index).
+#include "common.cuh"
+#include <math.h>
+
+__device__ __forceinline__ unsigned hash_u32(unsigned h) {
+    h ^= h >> 16; h *= 0x7feb352du;
+    h ^= h >> 15; h *= 0x846ca68bu;
+    h ^= h >> 16;
+    return h;
+}
+__device__ __forceinline__ float rand01(unsigned seed, unsigned i) {
+    const unsigned r = hash_u32(seed ^ hash_u32(i));
+    return ((float)(r >> 8) + 0.5f) / 16777216.0f;
+}
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+    return v > bv || (v == bv && i < bi);
+}
+
+#define SAMPLE_THREADS 1024
+
+// one block per row; out[row] = sampled token
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __restrict__ logits,
+                                                                const float* __restrict__ temps,
+                                                                const unsigned* __restrict__ seeds,
+                                                                int* __restrict__ out, int V) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int row = blockIdx.x;
+    const float* lg = logits + (size_t)row * V;
+    const float temp = temps ? temps[row] : 0.f;
+    const bool greedy = !(temp > 0.f);
+    const float inv_t = greedy ? 1.f : 1.f / temp;
+    const unsigned seed = seeds ? seeds[row] : 0u;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int k = threadIdx.x; k < V; k += blockDim.x) {
+        float v = lg[k];
+        if (!greedy) v = v * inv_t + (-logf(-logf(rand01(seed, (unsigned)k))));
+        if (better(v, k, bv, bi)) { bv = v; bi = k; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) { sv[w] = bv; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+        const int nw = blockDim.x >> 5;
+        bv = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) out[row] = (bi == 0x7fffffff) ? 0 : bi;   // all-NaN row: token 0
+    }
+}
+
+ZLLM_API int zllm_sample(const float* logits, const float* temps, const unsigned* seeds, int* out, int R, int V,
+                         void* stream) {
+    if (R <= 0) return 0;
+    if (V <= 0) return ZLLM_ERR_UNSUPPORTED;
+    sample_kernel<<<R, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, temps, seeds, out, V);
+    return launch_status();
+}
+
+// top-k candidates in descending order (value desc, index asc); fewer than k distinct
+// entries leave (-3e38, -1) sentinels.
+__global__ void __launch_bounds__(SAMPLE_THREADS) topk_kernel(const float* __restrict__ logits, float* __restrict__ vals,
+                                                              int* __restrict__ idxs, int V, int k) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    __shared__ float win_v;
+    __shared__ int win_i;
+    const int row = blockIdx.x;
+    const float* lg = logits + (size_t)row * V;
+    float prev_v = INFINITY;
+    int prev_i = -1;
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int c = threadIdx.x; c < V; c += blockDim.x) {
+            const float v = lg[c];
+            const bool below = (v < prev_v) || (v == prev_v && c > prev_i);
+            if (below && better(v, c, bv, bi)) { bv = v; bi = c; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+        if (lane == 0) { sv[w] = bv; si[w] = bi; }
+        __syncthreads();
+        if (w == 0) {
+            const int nw = blockDim.x >> 5;
+            bv = lane < nw ? sv[lane] : -INFINITY;
+            bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            }
+            if (lane == 0) {
+                const bool none = (bi == 0x7fffffff);
+                vals[(size_t)row * k + r] = none ? -3.0e38f : bv;
+                idxs[(size_t)row * k + r] = none ? -1 : bi;
+                win_v = none ? -INFINITY : bv;
+                win_i = none ? 0x7fffffff : bi;
+            }
+        }
+        __syncthreads();
+        prev_v = win_v;
+        prev_i = win_i;
+        __syncthreads();
+    }
+}
+
+ZLLM_API int zllm_topk(const float* logits, float* vals, int* idxs, int R, int V, int k, void* stream) {
+    if (R <= 0) return 0;
+    if (V <= 0 || k <= 0) return ZLLM_ERR_UNSUPPORTED;
+    topk_kernel<<<R, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, vals, idxs, V, k);
+    return launch_status();
+}

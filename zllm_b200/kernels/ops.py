@@ -1,0 +1,247 @@
+"""The kernel table: every device operation the engine performs, bound to the
+hand-written CUDA kernels of ``zllm_b200/csrc``.
+
+Each method checks on the host what the kernel relies on (device, dtype,
+contiguity, sizes, capacities), picks the kernel by sizes and precision alone
+-- never by trying and falling back -- and raises BackendError when a launch
+reports an error.  The reference has one ``record_*`` per operation on its GPU
+context (zllm src/backend/gpu/mod.rs:205-376) and can call each alone from a
+test; the same holds here.
+
+Precision: with float32 activations every product runs on CUDA cores in float32
+(no tensor cores, no reduced-precision mode).  With bfloat16 activations the
+products and attention use tensor-core kernels where their sizes allow and the
+plain kernels otherwise; softmax, norms, rotations and the residual sum are
+float32 in both.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..errors import BackendError
+from . import build
+
+MODES = {"store": 0, "add": 1, "swiglu": 2}
+ERR_UNSUPPORTED = 10001
+
+
+def _ptr(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+class CudaOps:
+    decode_split_keys = 256
+
+    def __init__(self, device="cuda:0"):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise BackendError(f"CudaOps needs a CUDA device, got {device}")
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device is available; this engine has no CPU path")
+        major, minor = torch.cuda.get_device_capability(self.device)
+        if major != 10:
+            raise BackendError(f"the kernels are built for sm_100a (B200); this device is sm_{major}{minor}")
+        self.dtype = torch.bfloat16
+        self._libs = {}
+        self.launches = 0
+
+    # ------------------------------------------------------------------
+    def configure(self, dtype):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise BackendError(f"unsupported activation dtype {dtype}")
+        self.dtype = dtype
+        names = ["elementwise", "gemm_plain", "attention_plain", "sampling"]
+        if dtype == torch.bfloat16:
+            names += [n for n in ("gemm_bf16", "attention_bf16") if (build.CSRC / f"{n}.cu").exists()]
+        build.build(names)
+        for n in names:
+            self._libs[n] = build.load(n)
+
+    def lib(self, name):
+        lib = self._libs.get(name)
+        if lib is None:
+            lib = self._libs[name] = build.load(name)
+        return lib
+
+    def _stream(self):
+        return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _check(self, code, what):
+        self.launches += 1
+        if code != 0:
+            if code == ERR_UNSUPPORTED:
+                raise BackendError(f"{what}: sizes not supported by this kernel")
+            raise BackendError(f"{what}: CUDA error {code}")
+
+    def _dev(self, *tensors):
+        for t in tensors:
+            if t is None:
+                continue
+            if t.device != self.device:
+                raise BackendError(f"tensor on {t.device}, kernels run on {self.device}")
+            if not t.is_contiguous():
+                raise BackendError("kernel operands must be contiguous")
+
+    def decode_splits(self, max_ctx: int) -> int:
+        return max(1, -(-int(max_ctx) // self.decode_split_keys))
+
+    # ---- embedding -----------------------------------------------------
+    def embedding(self, token_ids, table, out):
+        self._dev(token_ids, table, out)
+        T, H = out.shape
+        V = table.shape[0]
+        if token_ids.dtype != torch.int32 or out.dtype != torch.float32 or table.shape[1] != H \
+                or token_ids.numel() != T:
+            raise BackendError("embedding: bad operand types or shapes")
+        code = self.lib("elementwise").zllm_embedding(_ptr(token_ids), _ptr(table), _ptr(out), c_int(T), c_int(H),
+                                                      c_int(V), c_int(table.dtype == torch.bfloat16), self._stream())
+        self._check(code, "embedding")
+
+    # ---- rmsnorm -------------------------------------------------------
+    def rmsnorm(self, x, weight, eps, out):
+        self._dev(x, weight, out)
+        T, H = x.shape
+        if x.dtype != torch.float32 or weight.numel() != H or tuple(out.shape) != (T, H) \
+                or weight.dtype not in (torch.float32, torch.bfloat16) or out.dtype not in (torch.float32, torch.bfloat16):
+            raise BackendError("rmsnorm: bad operand types or shapes")
+        code = self.lib("elementwise").zllm_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), c_int(T), c_int(H), c_float(eps),
+                                                    c_int(weight.dtype == torch.bfloat16),
+                                                    c_int(out.dtype == torch.bfloat16), self._stream())
+        self._check(code, "rmsnorm")
+
+    # ---- products ------------------------------------------------------
+    def linear(self, x, w, out, mode: str):
+        """out = x w^T with epilogue ``mode``: "store", "add" (into a float32 out) or "swiglu"
+        (w = gate/up rows interleaved in groups of eight, out = silu(gate) * up)."""
+        self._dev(x, w, out)
+        M, K = x.shape
+        N = out.shape[1]
+        wn = w.shape[0]
+        if mode not in MODES:
+            raise BackendError(f"linear: unknown epilogue {mode!r}")
+        if w.shape[1] != K or out.shape[0] != M or wn != (2 * N if mode == "swiglu" else N) or x.dtype != w.dtype:
+            raise BackendError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} mode {mode}")
+        if mode == "add" and out.dtype != torch.float32:
+            raise BackendError("linear: the 'add' epilogue accumulates into float32")
+        if x.dtype == torch.bfloat16 and "gemm_bf16" in self._libs and self._linear_bf16(x, w, out, mode, M, N, K):
+            return
+        code = self.lib("gemm_plain").zllm_gemm_plain(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                                      c_int(MODES[mode]), c_int(x.dtype == torch.bfloat16),
+                                                      c_int(out.dtype == torch.bfloat16), self._stream())
+        self._check(code, "gemm_plain")
+
+    def linear_plain(self, x, w, out, mode: str):
+        M, K = x.shape
+        N = out.shape[1]
+        code = self.lib("gemm_plain").zllm_gemm_plain(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                                      c_int(MODES[mode]), c_int(x.dtype == torch.bfloat16),
+                                                      c_int(out.dtype == torch.bfloat16), self._stream())
+        self._check(code, "gemm_plain")
+
+    def _linear_bf16(self, x, w, out, mode, M, N, K) -> bool:
+        return False
+
+    # ---- silu * up -----------------------------------------------------
+    def silu_mul(self, a, b, out):
+        self._dev(a, b, out)
+        if a.shape != b.shape or a.shape != out.shape or a.dtype != b.dtype or a.dtype != out.dtype:
+            raise BackendError("silu_mul: operands differ in shape or dtype")
+        code = self.lib("elementwise").zllm_silu_mul(_ptr(a), _ptr(b), _ptr(out), c_longlong(a.numel()),
+                                                     c_int(a.dtype == torch.bfloat16), self._stream())
+        self._check(code, "silu_mul")
+
+    # ---- rows of the float32 residual ----------------------------------
+    def gather_rows(self, x, rows, out):
+        self._dev(x, rows, out)
+        R, H = out.shape
+        if x.dtype != torch.float32 or out.dtype != torch.float32 or rows.dtype != torch.int32 or rows.numel() != R \
+                or x.shape[1] != H:
+            raise BackendError("gather_rows: bad operand types or shapes")
+        code = self.lib("elementwise").zllm_gather_rows(_ptr(x), _ptr(rows), _ptr(out), c_int(R), c_int(H),
+                                                        self._stream())
+        self._check(code, "gather_rows")
+
+    # ---- rotary + cache write ------------------------------------------
+    def _check_cache(self, cache, nkv, hd, dtype, what):
+        kp, vp = cache.k_pages, cache.v_pages
+        self._dev(kp, vp, cache.block_table)
+        if kp.dtype != dtype or tuple(kp.shape[1:]) != (nkv, cache.block_size, hd) or kp.shape != vp.shape \
+                or cache.block_table.dtype != torch.int32:
+            raise BackendError(f"{what}: cache pages {tuple(kp.shape)} {kp.dtype} do not match "
+                               f"(kv heads {nkv}, block {cache.block_size}, head_dim {hd}, {dtype})")
+
+    def rope_kv_store(self, qkv, ctx, rot, cache, nq, nkv, hd, write_cache=True):
+        self._dev(qkv, ctx.positions, ctx.row_slot)
+        T = qkv.shape[0]
+        if qkv.shape[1] != (nq + 2 * nkv) * hd or ctx.positions.numel() != T or ctx.row_slot.numel() != T:
+            raise BackendError("rope_kv_store: qkv does not match the head counts or the step's rows")
+        if rot is not None:
+            self._dev(rot.cos, rot.sin)
+            if rot.cos.dtype != torch.float32 or rot.cos.shape[1] * 2 != rot.rot_dim or rot.rot_dim > hd:
+                raise BackendError("rope_kv_store: rotary tables do not match rot_dim")
+        if write_cache:
+            self._check_cache(cache, nkv, hd, qkv.dtype, "rope_kv_store")
+            kp, vp, tb, mb, bs = cache.k_pages, cache.v_pages, cache.block_table, cache.block_table.shape[1], cache.block_size
+        else:
+            kp = vp = tb = None
+            mb, bs = 1, 1
+        code = self.lib("elementwise").zllm_rope_kv_store(
+            _ptr(qkv), _ptr(ctx.positions), _ptr(ctx.row_slot), _ptr(rot.cos if rot is not None else None),
+            _ptr(rot.sin if rot is not None else None), c_int(rot.rot_dim if rot is not None else 0),
+            c_int(int(rot.interleaved) if rot is not None else 0), _ptr(kp), _ptr(vp), _ptr(tb), c_int(mb), c_int(bs),
+            c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(1 if write_cache else 0),
+            c_int(qkv.dtype == torch.bfloat16), self._stream())
+        self._check(code, "rope_kv_store")
+
+    # ---- attention over the cache ----------------------------------------
+    def paged_attention(self, qkv, out, ctx, cache, nq, nkv, hd, scale, window):
+        self._dev(qkv, out, ctx.positions, ctx.row_slot)
+        T = qkv.shape[0]
+        self._check_cache(cache, nkv, hd, qkv.dtype, "paged_attention")
+        if tuple(out.shape) != (T, nq * hd) or out.dtype != qkv.dtype:
+            raise BackendError("paged_attention: output does not match")
+        if qkv.dtype == torch.bfloat16 and "attention_bf16" in self._libs and \
+                self._attention_bf16(qkv, out, ctx, cache, nq, nkv, hd, scale, window):
+            return
+        self.attention_plain(qkv, out, ctx.positions, ctx.row_slot, cache, nq, nkv, hd, scale, window)
+
+    def attention_plain(self, qkv, out, positions, row_slot, cache, nq, nkv, hd, scale, window):
+        T = qkv.shape[0]
+        code = self.lib("attention_plain").zllm_attention_plain(
+            _ptr(qkv), _ptr(out), _ptr(positions), _ptr(row_slot), _ptr(cache.k_pages), _ptr(cache.v_pages),
+            _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(cache.block_size), c_int(T), c_int(nq),
+            c_int(nkv), c_int(hd), c_float(scale), c_int(window or 0), c_int(qkv.dtype == torch.bfloat16),
+            self._stream())
+        self._check(code, "attention_plain")
+
+    def _attention_bf16(self, qkv, out, ctx, cache, nq, nkv, hd, scale, window) -> bool:
+        return False
+
+    # ---- sampling --------------------------------------------------------
+    def sample(self, logits, temps, seeds, out):
+        """out[r] = argmax_i(logits[r,i]/temp_r + Gumbel(seed_r, i)); temp <= 0: plain argmax,
+        lowest index on ties."""
+        self._dev(logits, temps, seeds, out)
+        R, V = logits.shape
+        if logits.dtype != torch.float32 or out.dtype != torch.int32 or out.numel() < R:
+            raise BackendError("sample: bad operand types or shapes")
+        if temps is not None and (temps.dtype != torch.float32 or temps.numel() < R):
+            raise BackendError("sample: temps must be float32 [rows]")
+        if seeds is not None and (seeds.dtype not in (torch.int32, torch.uint32) or seeds.numel() < R):
+            raise BackendError("sample: seeds must be 32-bit [rows]")
+        code = self.lib("sampling").zllm_sample(_ptr(logits), _ptr(temps), _ptr(seeds), _ptr(out), c_int(R), c_int(V),
+                                                self._stream())
+        self._check(code, "sample")
+
+    def topk(self, logits, k, vals, idx):
+        self._dev(logits, vals, idx)
+        R, V = logits.shape
+        if logits.dtype != torch.float32 or vals.dtype != torch.float32 or idx.dtype != torch.int32 \
+                or tuple(vals.shape) != (R, k) or tuple(idx.shape) != (R, k):
+            raise BackendError("topk: bad operand types or shapes")
+        code = self.lib("sampling").zllm_topk(_ptr(logits), _ptr(vals), _ptr(idx), c_int(R), c_int(V), c_int(k),
+                                              self._stream())
+        self._check(code, "topk")
