@@ -1,0 +1,169 @@
+"""The Python entry point: an engine that takes token-id prompts to generated
+token ids, in the manner of the reference's library calls.
+
+zllm's callers use ``ContinuousBatcher::{enqueue_params(id, prompt, max_tokens,
+eos, params, seed), step() -> Vec<(id, token, done)>, cancel(id)}``
+(src/backend/gpu/batch.rs:64-211) and, single-stream, ``CandleCpuBackend::
+{load_model, forward_logits(&[u32]) -> Vec<f32>, generate_token, reset_position,
+truncate_to}`` (src/backend/candle/backend.rs:53-328).  ``Engine`` offers the
+first set (``add_request`` / ``step`` / ``cancel`` / ``generate``) and ``Session``
+the second, both over the same model, cache, step function and kernels.
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..config.engine_config import EngineConfig
+from ..errors import RequestError
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .batch import StepEntry
+from .runner import ModelRunner
+from .scheduler import Plan, Scheduler
+
+
+class Engine:
+    """Continuous batching over one model on one GPU.
+
+    ``Engine(model_dir)`` loads a folder with config.json and model.safetensors;
+    ``Engine(config=cfg, seed=s)`` makes random weights for a typed configuration.
+    Keyword arguments are the fields of ``EngineConfig``.
+    """
+
+    def __init__(self, model: Optional[str] = None, *, config=None, seed: Optional[int] = None, ops=None,
+                 engine_config: Optional[EngineConfig] = None, **kw):
+        ecfg = engine_config or EngineConfig(**kw)
+        self.runner = ModelRunner(model, config=config, seed=seed, engine_config=ecfg, ops=ops)
+        self.config = self.runner.config
+        self.scheduler = Scheduler(self.runner.cache, ecfg.max_num_batched_tokens, self.runner.max_len)
+        self.sampler = Sampler(self.runner.ops, self.runner.device, max(ecfg.max_num_seqs, 1))
+        self.steps = 0
+        self.generated = 0
+
+    # ---- requests ------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[int] = None) -> int:
+        V = self.config.vocab_size
+        for t in prompt_token_ids:
+            if not 0 <= int(t) < V:
+                raise RequestError(f"token id {t} is outside the vocabulary of {V}")
+        return self.scheduler.add(prompt_token_ids, params or SamplingParams.greedy(), request_id)
+
+    def cancel(self, request_id: int) -> bool:
+        return self.scheduler.cancel(request_id)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    # ---- one step ----------------------------------------------------------
+    def step(self):
+        """One scheduler step: [(request id, token, done)] for every token produced."""
+        plan = self.scheduler.schedule()
+        if plan.empty:
+            return []
+        dec = plan.decodes
+        dparams = [r.params for r in dec]
+        dseeds = [r.next_seed() for r in dec]
+        first: List[Optional[int]] = [None] * len(plan.portions)
+        if not plan.portions:
+            temps = [0.0 if (p.is_greedy or p.needs_topk or p.needs_full) else p.temperature for p in dparams]
+            toks = self.runner.decode_step([r.slot for r in dec], [r.tokens[-1] for r in dec], temps, dseeds)
+            toks = toks.cpu().tolist()
+            if any(p.needs_topk or p.needs_full for p in dparams):
+                toks = self.sampler.host_finish(self.runner.last_logits, toks, dparams, dseeds)
+            dtoks = toks
+        else:
+            entries = [StepEntry(r.slot, (r.tokens[-1],), (0,)) for r in dec]
+            params, seeds = list(dparams), list(dseeds)
+            for p in plan.portions:
+                r = p.request
+                entries.append(StepEntry(r.slot, r.tokens[p.start:p.start + p.n], (p.n - 1,) if p.completes else ()))
+                if p.completes:
+                    params.append(r.params)
+                    seeds.append(r.next_seed())
+            logits = self.runner.step(entries)
+            toks = self.sampler.sample(logits, params, seeds) if params else []
+            dtoks = toks[:len(dec)]
+            rest = iter(toks[len(dec):])
+            first = [next(rest) if p.completes else None for p in plan.portions]
+        out = self.scheduler.commit(plan, dtoks, first)
+        self.steps += 1
+        self.generated += len(out)
+        return out
+
+    # ---- whole generation ------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[List[int]]:
+        """Generated token ids for each prompt (token ids in, token ids out)."""
+        if params is None or isinstance(params, SamplingParams):
+            plist = [params or SamplingParams.greedy()] * len(prompts)
+        else:
+            plist = list(params)
+        import copy
+        ids = [self.add_request(p, copy.copy(sp)) for p, sp in zip(prompts, plist)]
+        outs: Dict[int, List[int]] = {i: [] for i in ids}
+        while self.scheduler.has_unfinished():
+            res = self.step()
+            if not res and not self.scheduler.has_unfinished():
+                break
+            for rid, tok, _ in res:
+                if rid in outs:
+                    outs[rid].append(tok)
+        return [outs[i] for i in ids]
+
+    def stats(self) -> dict:
+        s = self.scheduler.stats()
+        s.update({"steps": self.steps, "generated": self.generated, "tokens_run": self.runner.tokens_run})
+        return s
+
+
+class Session:
+    """One stream over the engine's model, after the reference's backend adapter
+    (backend.rs:53-328): it owns its position; ``forward_logits`` feeds tokens in portions
+    (backend.rs:185-232 cuts prompts into chunks of 512) and returns the last position's logits."""
+
+    def __init__(self, runner: ModelRunner, chunk: Optional[int] = None):
+        self.runner = runner
+        self.chunk = min(chunk or 512, runner.max_rows)
+        self.slot = runner.admit()
+        if self.slot is None:
+            raise RequestError("no free request slot for a session")
+
+    @property
+    def position(self) -> int:
+        return self.runner.cached_len(self.slot)
+
+    def forward_logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        tokens = list(tokens)
+        if not tokens:
+            raise RequestError("forward_logits needs at least one token")
+        logits = None
+        for i in range(0, len(tokens), self.chunk):
+            piece = tokens[i:i + self.chunk]
+            last = i + self.chunk >= len(tokens)
+            logits = self.runner.step([StepEntry(self.slot, piece, (len(piece) - 1,) if last else ())])
+        return logits[0].clone()
+
+    def forward_all_logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        tokens = list(tokens)
+        outs = []
+        for i in range(0, len(tokens), self.chunk):
+            piece = tokens[i:i + self.chunk]
+            outs.append(self.runner.step([StepEntry(self.slot, piece, tuple(range(len(piece))))]).clone())
+        return torch.cat(outs)
+
+    def generate_token(self, tokens: Sequence[int]) -> int:
+        lg = self.forward_logits(tokens)
+        mx = lg.max()
+        return int((lg == mx).nonzero()[0])
+
+    def reset_position(self) -> None:
+        self.runner.release(self.slot)
+        self.slot = self.runner.admit()
+
+    def close(self) -> None:
+        if self.slot is not None:
+            self.runner.release(self.slot)
+            self.slot = None
