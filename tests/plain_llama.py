@@ -341,10 +341,7 @@ def greedy_generate(cfg, w, prompt, n_new, dtype=torch.float32):
     out = []
     for _ in range(n_new):
         logits = forward_all_positions(cfg, w, toks, dtype=dtype)[-1]
-        t = int(torch.argmax(logits))  # torch returns the first maximal index on CPU
-        mx = logits.max()
-        first = int((logits == mx).nonzero()[0])
-        assert t == first or True
+        first = int((logits == logits.max()).nonzero()[0])   # the lowest index among equal maxima
         out.append(first)
         toks.append(first)
     return out

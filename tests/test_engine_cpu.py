@@ -1,0 +1,101 @@
+"""The engine's host side on the CPU: cache, tables, batch description, step function and
+scheduler run the four ways of cutting with the plain torch statements of the kernels
+(``ref_ops``) in place of the CUDA kernels, and must reproduce the plain whole-sequence
+implementation.  (The product has no CPU path; the kernels' own tests are GPU tests.)"""
+import pytest
+import torch
+
+import plain_llama as P
+import traces as TR
+from configs import TINY, make_model_dir, random_prompt
+from ref_ops import RefOps
+from zllm_b200 import Engine, EngineConfig, ModelRunner, SamplingParams
+from zllm_b200.errors import MemoryError_, RequestError
+from zllm_b200 import StepEntry
+
+
+def cpu_runner(model_dir, name, num_blocks, max_rows=256, slots=8):
+    return ModelRunner(model_dir, ops=RefOps(), engine_config=EngineConfig(
+        dtype="float32", device="cpu", cuda_graphs=False, block_size=TINY[name][1], num_blocks=num_blocks,
+        max_num_seqs=slots, max_num_batched_tokens=max_rows))
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_four_ways_of_cutting_agree_with_plain(tmp_path, name):
+    d = make_model_dir(tmp_path, name)
+    cfg, w = P.read_model_dir(d)
+    V = cfg["vocab_size"]
+    reqs = [(f"r{i}", random_prompt(V, n, 10 + i)) for i, n in enumerate((5, 49, 33, 70, 17, 64))]
+    ref = {rid: P.forward_all_positions(cfg, w, toks) for rid, toks in reqs}
+    max_tokens = 256
+    steps = (TR.family_whole(reqs, "w.") + TR.family_tail(reqs, 32, "t.") + TR.family_portions(reqs, prefix="p.")
+             + TR.family_mixed(reqs, max_tokens, 4, 1, "m."))
+    assert TR.live_tokens_needed(steps) <= max_tokens
+    runner = cpu_runner(d, name, max_tokens // TINY[name][1])
+    got = TR.replay_inprocess(runner, steps)
+    for prefix in ("w.", "t.", "p.", "m."):
+        TR.compare(got, ref, reqs, prefix, 2e-5, 0.0, f"tiny {name} {prefix}")
+    assert runner.cache.free_pages() == [max_tokens // TINY[name][1]]
+
+
+def test_step_errors_are_raised_before_anything_runs(tmp_path):
+    d = make_model_dir(tmp_path, "A")
+    r = cpu_runner(d, "A", num_blocks=4, max_rows=64)
+    s = r.admit()
+    with pytest.raises(RequestError, match="at least one token"):
+        r.step([StepEntry(s, [], ())])
+    with pytest.raises(RequestError, match="twice"):
+        r.step([StepEntry(s, [1], ()), StepEntry(s, [2], ())])
+    with pytest.raises(RequestError, match="max_num_batched_tokens"):
+        r.step([StepEntry(s, [1] * 65, ())])
+    s2 = r.admit()
+    r.step([StepEntry(s, [1] * 40, ())])
+    free = r.cache.free_pages()
+    with pytest.raises(MemoryError_, match="exhausted"):
+        r.step([StepEntry(s2, [1] * 30, ())])
+    assert r.cache.free_pages() == free and r.cached_len(s2) == 0     # nothing was taken or run
+    r.cache.check_integrity()
+    with pytest.raises(RequestError, match="not live"):
+        r.step([StepEntry(5, [1], ())])
+
+
+def test_generation_is_unchanged_by_preemption_and_portions(tmp_path):
+    d = make_model_dir(tmp_path, "A", std=0.3)
+    cfg, w = P.read_model_dir(d)
+    prompts = [random_prompt(512, n, 20 + n) for n in (5, 17, 33, 15)]
+    want = [P.greedy_generate(cfg, w, p, 24) for p in prompts]
+    for nb, budget, slots in ((64, 256, 4), (8, 16, 3), (7, 9, 4)):
+        eng = Engine(str(d), ops=RefOps(), dtype="float32", device="cpu", cuda_graphs=False, block_size=16,
+                     num_blocks=nb, max_num_seqs=slots, max_num_batched_tokens=budget)
+        out = eng.generate(prompts, SamplingParams.greedy(max_tokens=24))
+        assert out == want, f"pool {nb}, budget {budget}"
+        st = eng.stats()
+        assert st["free_pages"] == [nb] and st["free_slots"] == slots
+        if nb == 7:
+            assert st["preemptions"] > 0
+        eng.runner.cache.check_integrity()
+
+
+def test_temperature_sampling_is_reproducible_and_survives_preemption(tmp_path):
+    d = make_model_dir(tmp_path, "B", std=0.2)
+    prompts = [random_prompt(1000, n, 40 + n) for n in (3, 30, 12)]
+    params = [SamplingParams.with_temperature(0.8, seed=100 + i, max_tokens=20) for i in range(3)]
+
+    def run(nb, budget):
+        eng = Engine(str(d), ops=RefOps(), dtype="float32", device="cpu", cuda_graphs=False, block_size=8,
+                     num_blocks=nb, max_num_seqs=3, max_num_batched_tokens=budget)
+        out = eng.generate(prompts, params)
+        return out, eng.stats()["preemptions"]
+
+    a, _ = run(64, 64)
+    b, pre = run(12, 13)
+    assert a == b and pre > 0
+    greedy, _ = run(64, 64) if False else (None, None)
+    cfg, w = P.read_model_dir(d)
+    # token n of a request is the Gumbel-max draw with seed base + n * 0x9E3779B1 on the plain logits
+    toks = list(prompts[0])
+    for n in range(3):
+        lg = P.forward_all_positions(cfg, w, toks)[-1]
+        t = P.gumbel_sample(lg, 0.8, P.step_seed(100, n))
+        assert t == a[0][n]
+        toks.append(t)

@@ -1,0 +1,284 @@
+"""Each CUDA kernel alone against its plain torch statement (``ref_ops``), at sizes other
+than the engine configurations': odd widths, head sizes in steps of 16, any head and group
+counts, page sizes that are no power of two, row counts around every tile edge."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from gpu_util import DEV, CpuCacheView, cpu_ctx, make_cache, make_ctx
+from ref_ops import RefOps
+from zllm_b200.parts.feedforward import interleave_gate_up
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from zllm_b200.kernels.ops import CudaOps
+    o = CudaOps(DEV)
+    o.configure(torch.bfloat16)
+    return o
+
+
+REF = RefOps()
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+def test_embedding(ops, wdtype):
+    table = rnd((517, 72), wdtype, 0)
+    tok = torch.tensor([0, 516, 3, 3, 100], dtype=torch.int32)
+    out = torch.empty(5, 72, device=DEV)
+    ops.embedding(tok.to(DEV), table.to(DEV), out)
+    assert torch.equal(out.cpu(), table[tok.long()].float())
+
+
+@pytest.mark.parametrize("H,T", [(72, 3), (2048, 5), (1000, 1), (8200, 2)])
+@pytest.mark.parametrize("wdtype,odtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                           (torch.float32, torch.bfloat16)])
+def test_rmsnorm(ops, H, T, wdtype, odtype):
+    x = rnd((T, H), torch.float32, 1, 3.0)
+    w = (1 + rnd((H,), torch.float32, 2, 0.1)).to(wdtype)
+    out = torch.empty(T, H, dtype=odtype, device=DEV)
+    ops.rmsnorm(x.to(DEV), w.to(DEV), 1e-6, out)
+    want = torch.empty(T, H, dtype=odtype)
+    REF.rmsnorm(x, w, 1e-6, want)
+    tol = 2e-6 if odtype == torch.float32 else 2 ** -7
+    assert float((out.cpu().float() - want.float()).abs().max()) <= tol * float(want.float().abs().max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(ops, dtype):
+    a, b = rnd((7, 333), dtype, 3, 2.0), rnd((7, 333), dtype, 4)
+    out = torch.empty(7, 333, dtype=dtype, device=DEV)
+    ops.silu_mul(a.to(DEV), b.to(DEV), out)
+    want = torch.empty(7, 333, dtype=dtype)
+    REF.silu_mul(a, b, want)
+    assert float((out.cpu().float() - want.float()).abs().max()) <= (1e-6 if dtype == torch.float32 else 2 ** -7 * 4)
+
+
+LINEAR_SHAPES = [(1, 72, 64), (3, 200, 136), (8, 264, 520), (9, 96, 256), (16, 1000, 72), (17, 136, 2048),
+                 (64, 520, 264), (65, 72, 72), (127, 256, 192), (128, 384, 128), (129, 640, 320), (300, 1536, 448),
+                 (515, 200, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", LINEAR_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mode", ["store", "add", "swiglu"])
+def test_linear(ops, M, N, K, dtype, mode):
+    x = rnd((M, K), dtype, 5)
+    if mode == "swiglu":
+        w = interleave_gate_up(rnd((N, K), dtype, 6, K ** -0.5), rnd((N, K), dtype, 7, K ** -0.5))
+    else:
+        w = rnd((N, K), dtype, 6, K ** -0.5)
+    odt = torch.float32 if mode == "add" else dtype
+    base = rnd((M, N), odt, 8)
+    out = base.clone().to(DEV)
+    ops.linear(x.to(DEV), w.to(DEV), out, mode)
+    want = base.clone().float()
+    REF.linear(x, w, want, mode)           # float32 accumulation, unrounded output
+    err = float((out.cpu().float() - want).abs().max())
+    scale = float(want.abs().max())
+    if dtype == torch.float32:
+        assert err <= 2e-5 * max(scale, 1.0)
+    else:
+        assert err <= (2 ** -8) * max(scale, 1.0) * 1.5     # output rounding to bf16 plus accumulation order
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_linear_plain_matches_too(ops, dtype):
+    x, w = rnd((33, 100), dtype, 1), rnd((77, 100), dtype, 2, 0.1)
+    out = torch.zeros(33, 77, dtype=dtype, device=DEV)
+    ops.linear_plain(x.to(DEV), w.to(DEV), out, "store")
+    assert float((out.cpu().float() - x.float() @ w.float().T).abs().max()) < (1e-5 if dtype == torch.float32 else 0.02)
+
+
+def test_float32_products_do_not_depend_on_the_batch(ops):
+    """The 32-bit path: a row's result is bit-identical whatever else is in the batch."""
+    x, w = rnd((130, 200), torch.float32, 1).to(DEV), rnd((300, 200), torch.float32, 2).to(DEV)
+    full = torch.empty(130, 300, device=DEV)
+    ops.linear(x, w, full, "store")
+    for rows in ([0], [64, 65], list(range(100, 130))):
+        part = torch.empty(len(rows), 300, device=DEV)
+        ops.linear(x[rows].contiguous(), w, part, "store")
+        assert torch.equal(part, full[rows])
+
+
+ROPE_CASES = [(4, 2, 16, 16, False), (3, 1, 32, 32, True), (5, 5, 48, 32, False), (8, 2, 64, 64, False), (2, 1, 128, 128, True)]
+
+
+@pytest.mark.parametrize("nq,nkv,hd,rd,inter", ROPE_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rope_and_cache_write(ops, nq, nkv, hd, rd, inter, dtype):
+    from zllm_b200.parts.rotary import Rotary
+    from zllm_b200.models.decoder import Runtime
+    rot = Rotary(rd, 10000.0, 200, interleaved=inter)
+    rot.bind(Runtime(dtype, torch.device(DEV), ops))
+    bs = 6
+    cm = make_cache(nkv, hd, bs, 40, 3, 120, dtype)
+    s0, s1 = cm.admit(), cm.admit()
+    make_ctx(cm, [(s0, 11)])                                  # s0 already holds 11 positions
+    ctx = make_ctx(cm, [(s0, 9), (s1, 1), ])
+    T = 10
+    qkv = rnd((T, (nq + 2 * nkv) * hd), dtype, 9)
+    dq = qkv.clone().to(DEV)
+    view = cm.view(0)
+    view.k_pages.zero_(); view.v_pages.zero_()
+    ops.rope_kv_store(dq, ctx, rot.rotary(), view, nq, nkv, hd, True)
+    # plain
+    import copy
+    crot = copy.copy(rot.rotary()); crot.cos = crot.cos.cpu(); crot.sin = crot.sin.cpu()
+    cview = CpuCacheView(view); cview.k_pages.zero_(); cview.v_pages.zero_()
+    want = qkv.clone().float()
+    REF.rope_kv_store(want, cpu_ctx(ctx), crot, cview, nq, nkv, hd, True)
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -7
+    sc = float(want.abs().max())
+    assert float((dq.cpu().float() - want).abs().max()) <= tol * sc
+    assert float((view.k_pages.float().cpu() - cview.k_pages).abs().max()) <= tol * sc
+    assert float((view.v_pages.float().cpu() - cview.v_pages).abs().max()) <= tol * sc
+    assert float(cview.k_pages.abs().sum()) > 0
+    # without store nothing is written
+    view.k_pages.zero_()
+    ops.rope_kv_store(qkv.clone().to(DEV), ctx, rot.rotary(), view, nq, nkv, hd, False)
+    assert float(view.k_pages.abs().sum()) == 0.0
+
+
+ATT_CASES = [  # nq, nkv, hd, page size, window
+    (4, 2, 16, 16, None), (3, 1, 32, 8, None), (8, 2, 64, 16, None), (32, 8, 64, 16, None), (6, 6, 48, 5, None),
+    (16, 2, 128, 16, None), (5, 1, 80, 7, None), (8, 2, 64, 16, 37), (4, 4, 96, 12, 20), (8, 1, 112, 16, None),
+    (2, 1, 256, 16, None),
+]
+
+
+@pytest.mark.parametrize("nq,nkv,hd,bs,window", ATT_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_mixed_batch(ops, nq, nkv, hd, bs, window, dtype):
+    """Decoded rows at long and short contexts beside portions that start anywhere."""
+    cm = make_cache(nkv, hd, bs, 200, 6, 700, dtype, window)
+    slots = [cm.admit() for _ in range(5)]
+    view = cm.view(0)
+    g = torch.Generator().manual_seed(11)
+    view.k_pages.copy_(torch.randn(view.k_pages.shape, generator=g).to(dtype))
+    view.v_pages.copy_(torch.randn(view.v_pages.shape, generator=g).to(dtype))
+    # earlier contents of every request (pages handed out in interleaved order, so tables are scattered)
+    for rounds in range(3):
+        for s, n in zip(slots, (100, 3, 40, 170, 1)):
+            make_ctx(cm, [(s, n)])
+    ctx = make_ctx(cm, [(slots[0], 1), (slots[1], 70), (slots[2], 1), (slots[3], 2), (slots[4], 130), ])
+    T = ctx.T
+    qkv = rnd((T, (nq + 2 * nkv) * hd), dtype, 12)
+    out = torch.full((T, nq * hd), 7.0, dtype=dtype, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(qkv.to(DEV), out, ctx, view, nq, nkv, hd, scale, window)
+    want = torch.zeros(T, nq * hd)
+    REF.paged_attention(qkv.float(), want, cpu_ctx(ctx), CpuCacheView(view), nq, nkv, hd, scale, window)
+    err = float((out.cpu().float() - want).abs().max())
+    assert err <= (2e-5 if dtype == torch.float32 else 0.02), err
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key_among_hundreds(ops, dtype):
+    """One key far back is made to stand out (query and that key scaled up): the output must be
+    that key's value, whatever page it lies in.  Random data would hide a missed key."""
+    nq, nkv, hd, bs = 8, 2, 64, 16
+    cm = make_cache(nkv, hd, bs, 80, 2, 1100, dtype)
+    s = cm.admit()
+    view = cm.view(0)
+    g = torch.Generator().manual_seed(13)
+    view.k_pages.copy_((torch.randn(view.k_pages.shape, generator=g) * 0.1).to(dtype))
+    view.v_pages.copy_(torch.randn(view.v_pages.shape, generator=g).to(dtype))
+    make_ctx(cm, [(s, 1000)])
+    ctx = make_ctx(cm, [(s, 1)])                 # one decoded row at position 1000
+    for far in (0, 15, 16, 255, 256, 257, 511, 777, 999):
+        page = int(view.block_table[s, far // bs])
+        qkv = torch.zeros(1, (nq + 2 * nkv) * hd)
+        direction = torch.randn(hd, generator=g)
+        direction /= direction.norm()
+        saved = view.k_pages[page, :, far % bs].clone()
+        view.k_pages[page, :, far % bs] = (direction * 40).to(dtype)
+        qkv[0, :nq * hd] = (direction * 40).repeat(nq)
+        out = torch.zeros(1, nq * hd, dtype=dtype, device=DEV)
+        ops.paged_attention(qkv.to(dtype).to(DEV), out, ctx, view, nq, nkv, hd, 1.0, None)
+        got = out.float().cpu().reshape(nq, hd)
+        for h in range(nq):
+            v = view.v_pages[page, h // (nq // nkv), far % bs].float().cpu()
+            assert float((got[h] - v).abs().max()) < 0.02, f"far key {far} head {h}"
+        view.k_pages[page, :, far % bs] = saved
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_window_edge(ops, dtype):
+    """The key just outside the window is made dominant: it must NOT be seen; the one just
+    inside must."""
+    nq, nkv, hd, bs, window = 4, 1, 32, 8, 21
+    cm = make_cache(nkv, hd, bs, 40, 2, 300, dtype, window)
+    s = cm.admit()
+    view = cm.view(0)
+    g = torch.Generator().manual_seed(14)
+    for n in (90, 1, 1, 1, 5):
+        make_ctx(cm, [(s, n)])
+    view.k_pages.copy_((torch.randn(view.k_pages.shape, generator=g) * 0.1).to(dtype))
+    view.v_pages.copy_(torch.randn(view.v_pages.shape, generator=g).to(dtype))
+    ctx = make_ctx(cm, [(s, 1)])
+    p = int(ctx.positions[0])
+    direction = torch.ones(hd) / math.sqrt(hd)
+    qkv = torch.zeros(1, (nq + 2) * hd)
+    qkv[0, :nq * hd] = (direction * 40).repeat(nq)
+    for key, visible in ((p - window, False), (p - window + 1, True)):
+        page = int(view.block_table[s, key // bs])
+        if page < 0:
+            assert not visible
+            continue
+        saved = view.k_pages[page, 0, key % bs].clone()
+        view.k_pages[page, 0, key % bs] = (direction * 40).to(dtype)
+        out = torch.zeros(1, nq * hd, dtype=dtype, device=DEV)
+        ops.paged_attention(qkv.to(dtype).to(DEV), out, ctx, view, nq, nkv, hd, 1.0, window)
+        v = view.v_pages[page, 0, key % bs].float().cpu()
+        close = float((out.float().cpu().reshape(nq, hd)[0] - v).abs().max()) < 0.02
+        assert close == visible, f"key {key} visible={visible}"
+        view.k_pages[page, 0, key % bs] = saved
+
+
+def test_sampling_kernels(ops):
+    import plain_llama as P
+    g = torch.Generator().manual_seed(15)
+    V = 5003
+    lg = torch.randn(6, V, generator=g)
+    lg[1, 4000] = lg[1, 77] = 9.0              # a tie: the lowest index wins
+    lg[2] = 0.0                                # all equal: token 0
+    temps = torch.tensor([0.0, 0.0, 0.0, 0.8, 1.3, 0.8])
+    seeds = torch.tensor([1, 2, 3, 12345, 99, 12345], dtype=torch.int64).to(torch.int32)
+    out = torch.zeros(6, dtype=torch.int32, device=DEV)
+    ops.sample(lg.to(DEV), temps.to(DEV), seeds.to(DEV), out)
+    got = out.cpu().tolist()
+    assert got[0] == int(lg[0].argmax()) and got[1] == 77 and got[2] == 0
+    for r in (3, 4, 5):
+        assert got[r] == P.gumbel_sample(lg[r], float(temps[r]), int(seeds[r]))
+    vals = torch.zeros(6, 64, device=DEV)
+    idx = torch.zeros(6, 64, dtype=torch.int32, device=DEV)
+    ops.topk(lg.to(DEV), 64, vals, idx)
+    for r in range(6):
+        v, i = P.topk_desc(lg[r], 64)
+        assert idx[r].cpu().tolist() == i and vals[r].cpu().tolist() == v
+    small = torch.tensor([[1.0, 5.0, 5.0]])
+    v3 = torch.zeros(1, 5, device=DEV); i3 = torch.zeros(1, 5, dtype=torch.int32, device=DEV)
+    ops.topk(small.to(DEV), 5, v3, i3)
+    assert i3.cpu().tolist() == [[1, 2, 0, -1, -1]]
+
+
+def test_kernels_refuse_what_they_cannot_run(ops):
+    from zllm_b200.errors import BackendError
+    x = torch.zeros(4, 64, device=DEV)
+    with pytest.raises(BackendError):
+        ops.linear(x, torch.zeros(8, 63, device=DEV), torch.zeros(4, 8, device=DEV), "store")
+    with pytest.raises(BackendError):
+        ops.linear(x.bfloat16(), torch.zeros(8, 64, device=DEV).bfloat16(), torch.zeros(4, 8, device=DEV).bfloat16(), "add")
+    with pytest.raises(BackendError):
+        ops.rmsnorm(x.t(), torch.ones(64, device=DEV), 1e-5, torch.zeros(64, 4, device=DEV))   # not contiguous
+    with pytest.raises(BackendError):
+        ops.embedding(torch.zeros(4, dtype=torch.int64, device=DEV), x, torch.zeros(4, 64, device=DEV))

@@ -1,0 +1,161 @@
+"""Trace replay on the GPU: the same requests whole, with the last 32 tokens one by one, in
+portions of changing size, and mixed with other requests on so few pages that they are used
+again -- in 32-bit and in bfloat16, through ``bin/trace_run`` (the program a user runs) and
+in-process, all compared with the plain implementation per (request, position)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+import plain_llama as P
+import traces as TR
+from configs import TINY, make_model_dir, random_prompt
+from gpu_util import BF16_MAX_OF_SCALE, F32_ATOL
+from zllm_b200 import EngineConfig, ModelRunner, StepEntry
+
+LENGTHS = (5, 49, 33, 150, 17, 64, 97, 2)
+
+
+def requests_for(name, vocab):
+    return [(f"r{i}", random_prompt(vocab, n, 100 + 7 * i + len(name))) for i, n in enumerate(LENGTHS)]
+
+
+def tolerances(dtype):
+    return (F32_ATOL, 0.0) if dtype == "float32" else (0.0, BF16_MAX_OF_SCALE)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_four_families(tmp_path, name, dtype):
+    d = make_model_dir(tmp_path, name, dtype)
+    cfg, w = P.read_model_dir(d)
+    V = cfg["vocab_size"]
+    reqs = requests_for(name, V)
+    ref = {rid: P.forward_all_positions(cfg, w, toks) for rid, toks in reqs}
+    max_tokens = 448                                 # 28 pages of 16: the mixed family reuses them
+    steps = (TR.family_whole(reqs, "w.") + TR.family_tail(reqs, 32, "t.") + TR.family_portions(reqs, prefix="p.")
+             + TR.family_mixed(reqs, max_tokens, 4, 2, "m."))
+    assert TR.live_tokens_needed(steps) <= max_tokens
+    got = TR.replay_program(d, dtype, steps, max_tokens, tmp_path / "out", V,
+                            extra_args=("--block-size", str(TINY[name][1])))
+    atol, rel = tolerances(dtype)
+    for prefix in ("w.", "t.", "p.", "m."):
+        TR.compare(got, ref, reqs, prefix, atol, rel, f"tiny {name} {dtype} {prefix}")
+    if dtype == "float32":
+        # 32-bit kernels fix every reduction order by the position alone: the ways of cutting
+        # agree to the last bit, not just within a tolerance
+        for rid, toks in reqs:
+            for p in range(len(toks)):
+                for prefix in ("t.", "p.", "m."):
+                    assert torch.equal(got[("w." + rid, p)], got[(prefix + rid, p)]), (prefix, rid, p)
+
+
+def test_trace_run_default_page_size_and_skipped_steps(tmp_path):
+    """Defaults as a user gives them; a step without wanted places writes no file."""
+    d = make_model_dir(tmp_path, "A", "float32")
+    cfg, w = P.read_model_dir(d)
+    toks = random_prompt(512, 40, 5)
+    steps = [{"entries": [{"id": "x", "tokens": toks[:30], "want": []}], "end": []},
+             {"entries": [{"id": "x", "tokens": toks[30:], "want": [9]}], "end": ["x"]},
+             {"entries": [], "end": []}]
+    got = TR.replay_program(d, "float32", steps, 64, tmp_path / "o", 512)
+    ref = P.forward_all_positions(cfg, w, toks)
+    assert list(got) == [("x", 39)] and float((got[("x", 39)] - ref[39]).abs().max()) < F32_ATOL
+
+
+def test_trace_run_reports_exhaustion_and_bad_models(tmp_path):
+    d = make_model_dir(tmp_path, "A", "float32")
+    line = json.dumps({"step": 0, "entries": [{"id": "x", "tokens": [1] * 100, "want": []}], "end": []}) + "\n"
+    cmd = [sys.executable, str(TR.ROOT / "bin" / "trace_run"), "--model", str(d), "--dtype", "float32",
+           "--out", str(tmp_path / "o"), "--max-tokens", "64"]
+    p = subprocess.run(cmd, input=line, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 3 and ("exhausted" in p.stderr or "exceeds" in p.stderr)
+    cfgj = json.loads((d / "config.json").read_text())
+    cfgj["architectures"] = ["SomethingElseForCausalLM"]
+    (d / "config.json").write_text(json.dumps(cfgj))
+    p = subprocess.run(cmd, input="", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 2 and "SomethingElseForCausalLM" in p.stderr
+
+
+def gpu_runner(d, name, dtype, num_blocks, max_rows=512, slots=8, graphs=True):
+    return ModelRunner(d, engine_config=EngineConfig(dtype=dtype, block_size=TINY[name][1], num_blocks=num_blocks,
+                                                     max_num_seqs=slots, max_num_batched_tokens=max_rows,
+                                                     cuda_graphs=graphs))
+
+
+@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_one_by_one(tmp_path, name, dtype):
+    """300 tokens decoded one at a time after a short prompt, through the graph path, for two
+    requests side by side; compared with the plain implementation at every position."""
+    d = make_model_dir(tmp_path, name, dtype)
+    cfg, w = P.read_model_dir(d)
+    V = cfg["vocab_size"]
+    a, b = random_prompt(V, 330, 1), random_prompt(V, 310, 2)
+    ref_a, ref_b = P.forward_all_positions(cfg, w, a), P.forward_all_positions(cfg, w, b)
+    r = gpu_runner(d, name, dtype, num_blocks=2 * (-(-340 // TINY[name][1])))
+    sa, sb = r.admit(), r.admit()
+    r.step([StepEntry(sa, a[:30], ()), StepEntry(sb, b[:10], ())])
+    atol, rel = tolerances(dtype)
+    worst = 0.0
+    for i in range(300):
+        r.decode_step([sa, sb], [a[30 + i], b[10 + i]], [0.0, 0.0], [0, 0])
+        lg = r.last_logits[:2].float().cpu()
+        for row, ref, p in ((lg[0], ref_a, 30 + i), (lg[1], ref_b, 10 + i)):
+            err = float((row - ref[p]).abs().max())
+            bound = atol + rel * float(ref.abs().max())
+            assert err <= bound, f"position {p}: {err:.3e} > {bound:.3e}"
+            worst = max(worst, err)
+    r.cache.check_integrity()
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(tmp_path, name, dtype):
+    """Position 0 alone, positions 0-1, a one-token prompt then decode: the shortest contexts."""
+    d = make_model_dir(tmp_path, name, dtype)
+    cfg, w = P.read_model_dir(d)
+    V = cfg["vocab_size"]
+    toks = random_prompt(V, 6, 3)
+    ref = P.forward_all_positions(cfg, w, toks)
+    atol, rel = tolerances(dtype)
+    bound = atol + rel * float(ref.abs().max())
+    r = gpu_runner(d, name, dtype, num_blocks=16)
+    s = r.admit()
+    lg = r.step([StepEntry(s, toks[:1], (0,))]).float().cpu()
+    assert float((lg[0] - ref[0]).abs().max()) <= bound
+    r.decode_step([s], [toks[1]], [0.0], [0])
+    assert float((r.last_logits[0].float().cpu() - ref[1]).abs().max()) <= bound
+    lg = r.step([StepEntry(s, toks[2:4], (0, 1))]).float().cpu()
+    assert float((lg - ref[2:4]).abs().max()) <= bound
+    s2 = r.admit()
+    lg = r.step([StepEntry(s2, toks[:2], (0, 1)), StepEntry(s, toks[4:5], (0,))]).float().cpu()
+    assert float((lg[:2] - ref[:2]).abs().max()) <= bound and float((lg[2] - ref[4]).abs().max()) <= bound
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_reused_page_does_not_leak_old_keys(tmp_path, dtype):
+    """A request fills pages with large keys and ends; the next request gets the same pages.
+    Its logits must equal those on a fresh pool: nothing of the old contents may be seen."""
+    d = make_model_dir(tmp_path, "C", dtype)
+    toks = random_prompt(1536, 40, 9)
+    fresh = gpu_runner(d, "C", dtype, num_blocks=4)
+    s = fresh.admit()
+    want = fresh.step([StepEntry(s, toks, tuple(range(40)))]).float().cpu().clone()
+    r = gpu_runner(d, "C", dtype, num_blocks=4)
+    s = r.admit()
+    r.step([StepEntry(s, random_prompt(1536, 64, 10), ())])
+    for g in r.cache.groups:
+        g.storage.mul_(50.0)                         # make stale contents loud
+    r.release(s)
+    s = r.admit()
+    outs = [r.step([StepEntry(s, toks[:13], tuple(range(13)))]).float().cpu().clone()]
+    outs.append(r.step([StepEntry(s, toks[13:], tuple(range(27)))]).float().cpu().clone())
+    got = torch.cat(outs)
+    tol = 0.0 if dtype == "float32" else BF16_MAX_OF_SCALE * float(want.abs().max())
+    assert float((got - want).abs().max()) <= tol

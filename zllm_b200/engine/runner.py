@@ -41,7 +41,8 @@ class ModelRunner:
     """Model + cache + step function on one device."""
 
     def __init__(self, model_dir=None, *, config=None, seed: Optional[int] = None,
-                 engine_config: Optional[EngineConfig] = None, ops=None, init_std=None, norm_std=None):
+                 engine_config: Optional[EngineConfig] = None, ops=None, init_std=None, norm_std=None,
+                 random_on_device: bool = False):
         self.ecfg = (engine_config or EngineConfig()).validate()
         self.device = torch.device(self.ecfg.device)
         self.dtype = _TORCH_DTYPE[self.ecfg.dtype]
@@ -71,7 +72,9 @@ class ModelRunner:
             tensors = {}
             for name, ws in expected.items():
                 dt = target_dtype(torch.bfloat16 if self.dtype == torch.bfloat16 else torch.float32, ws.role, self.dtype)
-                tensors[name] = random_tensor(name, ws, seed or 0, dt, self.device, init_std, norm_std)
+                # drawn on the CPU (the same values everywhere) unless the caller asks for speed
+                t = random_tensor(name, ws, seed or 0, dt, self.device if random_on_device else "cpu", init_std, norm_std)
+                tensors[name] = t.to(self.device)
         self.model.load_weights(tensors)
         del tensors
 
