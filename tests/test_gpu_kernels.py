@@ -159,7 +159,7 @@ ATT_CASES = [  # nq, nkv, hd, page size, window
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_mixed_batch(ops, nq, nkv, hd, bs, window, dtype):
     """Decoded rows at long and short contexts beside portions that start anywhere."""
-    cm = make_cache(nkv, hd, bs, 200, 6, 700, dtype, window)
+    cm = make_cache(nkv, hd, bs, 1300 // bs + 12, 6, 700, dtype, window)
     slots = [cm.admit() for _ in range(5)]
     view = cm.view(0)
     g = torch.Generator().manual_seed(11)
