@@ -1,0 +1,463 @@
+// bfloat16 attention over the paged cache on tensor cores (mma.sync m16n8k16), float32
+// softmax and accumulation.
+//
+// Two kernels with one inner loop:
+//  * decode: one CTA per (decoded row, kv head, split of 256 keys).  The query heads that
+//    share the kv head are the 16 rows of the tensor-core tile, so keys and values are read
+//    once for the whole group; each of the 4 warps takes 64 keys of the split; the warps'
+//    partial (max, sum, accumulator) are merged in warp order and written as the split's
+//    partial; a second kernel merges the splits in split order.  This is zllm's
+//    flash-decode scheme (partial + log-sum-exp combine, src/backend/vulkan/shaders/
+//    sdpa_flash_partial2.comp:1-56, sdpa_flash_combine_h.comp:1-41) on the math of its paged
+//    kernel (src/backend/gpu/shaders.rs:670-725).  The split size is fixed, so how a row is
+//    split depends on its own position only, never on the batch.
+//  * prefill: one CTA per (tile of 64 query rows of a portion, query head); K/V tiles of 64
+//    keys are gathered through the block table into shared memory (double buffered) and
+//    shared by the 4 warps (16 query rows each); a portion that starts at position p
+//    attends the whole prefix 0..p-1 from the cache plus its own rows causally (zllm's
+//    coopmat_flash_attn.comp with its query offset, src/backend/vulkan/mod.rs:1758-1777).
+//
+// Scratch: the decode kernel's per-split partials live in global memory given by the
+// caller: part_o [rows][nq][max_splits][hd] and part_ml [rows][nq][max_splits][2] float32.
+#include "common.cuh"
+#include <cuda_pipeline.h>
+#include <math.h>
+
+#define SPLIT_KEYS 256
+#define DEC_WARPS 4
+#define DEC_BLOCK 32            // keys per warp iteration in the decode kernel
+#define PF_QROWS 64             // query rows per prefill CTA
+#define PF_KEYS 64              // keys per prefill tile
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Running softmax state of one warp's 16-row tile: rows g and g + 8 of the lane.
+template <int HD>
+struct TileState {
+    float m[2], l[2];
+    float o[HD / 8][4];
+    __device__ __forceinline__ void init() {
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    }
+};
+
+// Gather NKEYS rows of K or V (keys key0 .. key0+NKEYS-1 of one request and kv head) into a
+// shared tile [NKEYS][HD + 8] with 16-byte async copies by NTHREADS threads.  Keys outside
+// [0, n_keys) or without a page are zero-filled.
+template <int HD, int NKEYS, int NTHREADS>
+__device__ __forceinline__ void gather_tile(bf16* __restrict__ tile, const bf16* __restrict__ pages,
+                                            const int* __restrict__ trow, int key0, int n_keys, int bs, int nkv,
+                                            int kvh, int tid) {
+    constexpr int CH = HD / 8;                       // 16-byte chunks per row
+    for (int i = tid; i < NKEYS * CH; i += NTHREADS) {
+        const int r = i / CH, c = i - r * CH;
+        const int key = key0 + r;
+        bf16* dst = tile + (size_t)r * (HD + 8) + c * 8;
+        int page = -1;
+        if (key >= 0 && key < n_keys) page = trow[key / bs];
+        if (page >= 0) {
+            const bf16* src = pages + ((((size_t)page * nkv + kvh) * bs + (key % bs)) * HD + c * 8);
+            __pipeline_memcpy_async(dst, src, 16);
+        } else {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// One block of NB keys (NB multiple of 16) against the warp's 16 rows.
+//   qf      : A fragments of the 16 x HD query tile
+//   ks, vs  : shared tiles [NB][HD + 8] of the block's keys / values
+//   key0    : absolute index of the block's first key
+//   lo_r/hi_r : per row (index 0: row g, 1: row g + 8) the visible key range [lo, hi]
+template <int HD, int NB>
+__device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], const bf16* __restrict__ ks,
+                                             const bf16* __restrict__ vs, int key0, const int (&lo_r)[2],
+                                             const int (&hi_r)[2], float scale, TileState<HD>& st, int lane) {
+    constexpr int STR = HD + 8;
+    const int t = lane & 3;
+    float s[NB / 8][4];
+#pragma unroll
+    for (int j = 0; j < NB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    // S = Q K^T: B fragments of K by ldmatrix (rows = keys, 8 x 8 tiles along dims)
+    const int lrow = lane & 7, lmat = lane >> 3;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int j = 0; j < NB / 8; j += 2) {
+            // matrices: (keys 8j.., dims 16kk..), (keys 8j.., dims 16kk+8..), (keys 8j+8.., dims 16kk..), (.., +8)
+            unsigned b[4];
+            const bf16* p = ks + (size_t)(8 * j + (lmat >> 1) * 8 + lrow) * STR + 16 * kk + (lmat & 1) * 8;
+            ldmatrix_x4(b, p);
+            mma16816(s[j], qf[kk], b[0], b[1]);
+            mma16816(s[j + 1], qf[kk], b[2], b[3]);
+        }
+    }
+    // scale, mask, running max
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NB / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int key = key0 + 8 * j + 2 * t + (e & 1);
+            const float v = (key >= lo_r[r] && key <= hi_r[r]) ? s[j][e] * scale : -INFINITY;
+            s[j][e] = v;
+            mx[r] = fmaxf(mx[r], v);
+        }
+    }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(st.m[r], mx[r]);
+        corr[r] = (m_new == -INFINITY) ? 1.f : expf(st.m[r] - m_new);
+        msafe[r] = (m_new == -INFINITY) ? 0.f : m_new;
+        st.m[r] = m_new;
+    }
+    float rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NB / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const float p = expf(s[j][e] - msafe[r]);        // exp(-inf) = 0 for hidden keys
+            s[j][e] = p;
+            rs[r] += p;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+        st.l[r] = st.l[r] * corr[r] + rs[r];
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
+        st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
+    }
+    // O += P V: A fragments from the probabilities, B fragments of V by transposed ldmatrix
+#pragma unroll
+    for (int kk = 0; kk < NB / 16; ++kk) {
+        unsigned pa[4];
+        pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int i = 0; i < HD / 8; i += 2) {
+            // matrices: (keys 16kk.., dims 8i..), (keys 16kk+8.., dims 8i..), (keys 16kk.., dims 8i+8..), (.., +8)
+            unsigned b[4];
+            const bf16* p = vs + (size_t)(16 * kk + (lmat & 1) * 8 + lrow) * STR + 8 * i + (lmat >> 1) * 8;
+            ldmatrix_x4_trans(b, p);
+            mma16816(st.o[i], pa, b[0], b[1]);
+            mma16816(st.o[i + 1], pa, b[2], b[3]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------ decode
+template <int HD>
+__global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
+    const bf16* __restrict__ qkv, const int* __restrict__ rows, const int* __restrict__ positions,
+    const int* __restrict__ row_slot, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+    const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, float scale, int window,
+    float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits) {
+    constexpr int STR = HD + 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int row = rows[blockIdx.x];
+    const int slot = row_slot[row];
+    if (slot < 0) return;
+    const int kvh = blockIdx.y, split = blockIdx.z;
+    const int pos = positions[row];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int k_first = lo + split * SPLIT_KEYS;
+    if (k_first > pos) return;                               // this split holds no key of the row
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int G = nq / nkv;
+    const int* trow = table + (size_t)slot * max_blocks;
+    bf16* ks = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * 2 * DEC_BLOCK * STR;
+    bf16* vs = ks + DEC_BLOCK * STR;
+    // query fragments: row g of the tile is query head kvh * G + g (rows beyond the group are zero)
+    unsigned qf[HD / 16][4];
+    {
+        const bf16* qrow = qkv + (size_t)row * (nq + 2 * nkv) * HD + (size_t)kvh * G * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            const int d = 16 * kk + 2 * t;
+            qf[kk][0] = g < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)g * HD + d) : 0u;
+            qf[kk][1] = g + 8 < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)(g + 8) * HD + d) : 0u;
+            qf[kk][2] = g < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)g * HD + d + 8) : 0u;
+            qf[kk][3] = g + 8 < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)(g + 8) * HD + d + 8) : 0u;
+        }
+    }
+    TileState<HD> st;
+    st.init();
+    const int lo_r[2] = {lo, lo}, hi_r[2] = {pos, pos};
+    const int w_first = k_first + warp * (SPLIT_KEYS / DEC_WARPS);
+#pragma unroll 1
+    for (int it = 0; it < SPLIT_KEYS / DEC_WARPS / DEC_BLOCK; ++it) {
+        const int key0 = w_first + it * DEC_BLOCK;
+        if (key0 > pos) break;                               // warp-uniform
+        gather_tile<HD, DEC_BLOCK, 32>(ks, k_pages, trow, key0, pos + 1, bs, nkv, kvh, lane);
+        gather_tile<HD, DEC_BLOCK, 32>(vs, v_pages, trow, key0, pos + 1, bs, nkv, kvh, lane);
+        __pipeline_commit();
+        __pipeline_wait_prior(0);
+        __syncwarp();
+        attend_block<HD, DEC_BLOCK>(qf, ks, vs, key0, lo_r, hi_r, scale, st, lane);
+        __syncwarp();                                        // tile is reused by the next iteration
+    }
+    // merge the warps' partials in warp order
+    __syncthreads();                                         // all warps are done with their K/V tiles
+    float* wm = reinterpret_cast<float*>(smem_raw);          // [warps][16]
+    float* wl = wm + DEC_WARPS * 16;                         // [warps][16]
+    float* wo = wl + DEC_WARPS * 16;                         // [warps][16][HD]
+    if (t == 0) {
+        wm[warp * 16 + g] = st.m[0]; wm[warp * 16 + g + 8] = st.m[1];
+        wl[warp * 16 + g] = st.l[0]; wl[warp * 16 + g + 8] = st.l[1];
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        float* o0 = wo + ((size_t)warp * 16 + g) * HD + 8 * i + 2 * t;
+        float* o1 = wo + ((size_t)warp * 16 + g + 8) * HD + 8 * i + 2 * t;
+        o0[0] = st.o[i][0]; o0[1] = st.o[i][1];
+        o1[0] = st.o[i][2]; o1[1] = st.o[i][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < G * HD && G <= 16; i += blockDim.x) {
+        const int h = i / HD, d = i - h * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, wm[w * 16 + h]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float mw = wm[w * 16 + h];
+            const float f = (mw == -INFINITY) ? 0.f : expf(mw - M);
+            L += wl[w * 16 + h] * f;
+            O += wo[((size_t)w * 16 + h) * HD + d] * f;
+        }
+        const size_t pi = ((size_t)blockIdx.x * nq + kvh * G + h) * max_splits + split;
+        part_o[pi * HD + d] = O;
+        if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+    }
+}
+
+// out[row][head][:] = sum_s O_s e^{m_s - M} / sum_s l_s e^{m_s - M} over the row's splits, in split order
+template <int HD>
+__global__ void decode_combine_kernel(const int* __restrict__ rows, const int* __restrict__ positions,
+                                      const int* __restrict__ row_slot, const float* __restrict__ part_o,
+                                      const float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int window,
+                                      int max_splits) {
+    const int row = rows[blockIdx.x];
+    const int h = blockIdx.y;
+    bf16* o = out + ((size_t)row * nq + h) * HD;
+    if (row_slot[row] < 0) {
+        for (int d = threadIdx.x; d < HD; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int pos = positions[row];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int ns = (pos - lo) / SPLIT_KEYS + 1;
+    const size_t base = ((size_t)blockIdx.x * nq + h) * max_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    float L = 0.f;
+    for (int s = 0; s < ns; ++s) {
+        const float ms = part_ml[(base + s) * 2];
+        L += part_ml[(base + s) * 2 + 1] * ((ms == -INFINITY) ? 0.f : expf(ms - M));
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < ns; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            acc += part_o[(base + s) * HD + d] * ((ms == -INFINITY) ? 0.f : expf(ms - M));
+        }
+        o[d] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+template <int HD>
+static int launch_decode(const void* qkv, void* out, const int* rows, int n_rows, const int* positions,
+                         const int* row_slot, const void* k_pages, const void* v_pages, const int* table,
+                         int max_blocks, int bs, int nq, int nkv, float scale, int window, float* part_o,
+                         float* part_ml, int n_splits, int max_splits, cudaStream_t s) {
+    constexpr int STR = HD + 8;
+    size_t smem = (size_t)DEC_WARPS * 2 * DEC_BLOCK * STR * sizeof(bf16);
+    const size_t merge = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
+    if (merge > smem) smem = merge;
+    auto kern = decode_split_kernel<HD>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid(n_rows, nkv, n_splits);
+    kern<<<grid, DEC_WARPS * 32, smem, s>>>((const bf16*)qkv, rows, positions, row_slot, (const bf16*)k_pages,
+                                            (const bf16*)v_pages, table, max_blocks, bs, nq, nkv, scale, window,
+                                            part_o, part_ml, max_splits);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    decode_combine_kernel<HD><<<dim3(n_rows, nq), HD <= 64 ? 64 : 128, 0, s>>>(rows, positions, row_slot, part_o, part_ml,
+                                                                             (bf16*)out, nq, window, max_splits);
+    return launch_status();
+}
+
+#define DISPATCH_HD(HDV, CALL)                                                     \
+    switch (HDV) {                                                                 \
+        case 16: { constexpr int H_ = 16; return CALL; }                           \
+        case 32: { constexpr int H_ = 32; return CALL; }                           \
+        case 48: { constexpr int H_ = 48; return CALL; }                           \
+        case 64: { constexpr int H_ = 64; return CALL; }                           \
+        case 80: { constexpr int H_ = 80; return CALL; }                           \
+        case 96: { constexpr int H_ = 96; return CALL; }                           \
+        case 112: { constexpr int H_ = 112; return CALL; }                         \
+        case 128: { constexpr int H_ = 128; return CALL; }                         \
+        default: return ZLLM_ERR_UNSUPPORTED;                                      \
+    }
+
+// Decode rows ``rows[0..n_rows)`` of the step.  n_splits: grid size along the splits (>= the
+// splits of the longest row; a captured graph passes its bucket); max_splits: stride of the
+// partial buffers.  Takes head sizes 16..128 in steps of 16 and groups nq/nkv <= 16.
+ZLLM_API int zllm_attention_decode_bf16(const void* qkv, void* out, const int* rows, int n_rows, const int* positions,
+                                        const int* row_slot, const void* k_pages, const void* v_pages,
+                                        const int* table, int max_blocks, int bs, int nq, int nkv, int hd, float scale,
+                                        int window, float* part_o, float* part_ml, int n_splits, int max_splits,
+                                        void* stream) {
+    if (n_rows <= 0) return 0;
+    if (nkv <= 0 || nq % nkv || nq / nkv > 16 || n_splits <= 0 || n_splits > max_splits || n_splits > 65535 ||
+        nkv > 65535)
+        return ZLLM_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    DISPATCH_HD(hd, (launch_decode<H_>(qkv, out, rows, n_rows, positions, row_slot, k_pages, v_pages, table,
+                                       max_blocks, bs, nq, nkv, scale, window, part_o, part_ml, n_splits, max_splits,
+                                       s)))
+}
+
+// ------------------------------------------------------------------------------------ prefill
+// tiles [n_tiles][4] = (first row, rows (<= 64), slot, position of first row)
+template <int HD>
+__global__ void __launch_bounds__(128) prefill_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out,
+                                                      const int* __restrict__ tiles, const bf16* __restrict__ k_pages,
+                                                      const bf16* __restrict__ v_pages, const int* __restrict__ table,
+                                                      int max_blocks, int bs, int nq, int nkv, float scale,
+                                                      int window) {
+    constexpr int STR = HD + 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);          // [2][PF_KEYS][STR]
+    bf16* vbuf = kbuf + 2 * PF_KEYS * STR;                   // [2][PF_KEYS][STR]
+    const int* tl = tiles + 4 * blockIdx.x;
+    const int row0 = tl[0], n_rows = tl[1], slot = tl[2], pos0 = tl[3];
+    const int h = blockIdx.y;
+    const int kvh = h / (nq / nkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int* trow = table + (size_t)slot * max_blocks;
+    const int last_pos = pos0 + n_rows - 1;                  // last key any row of the tile sees
+    const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int kb_first = first_key / PF_KEYS;
+    const int kb_last = last_pos / PF_KEYS;
+    // query fragments of the warp's 16 rows
+    const int r_a = warp * 16 + g, r_b = r_a + 8;            // rows within the tile
+    unsigned qf[HD / 16][4];
+    {
+        const size_t stride = (size_t)(nq + 2 * nkv) * HD;
+        const bf16* qa = qkv + (size_t)(row0 + r_a) * stride + (size_t)h * HD;
+        const bf16* qb = qkv + (size_t)(row0 + r_b) * stride + (size_t)h * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            const int d = 16 * kk + 2 * t;
+            qf[kk][0] = r_a < n_rows ? *reinterpret_cast<const unsigned*>(qa + d) : 0u;
+            qf[kk][1] = r_b < n_rows ? *reinterpret_cast<const unsigned*>(qb + d) : 0u;
+            qf[kk][2] = r_a < n_rows ? *reinterpret_cast<const unsigned*>(qa + d + 8) : 0u;
+            qf[kk][3] = r_b < n_rows ? *reinterpret_cast<const unsigned*>(qb + d + 8) : 0u;
+        }
+    }
+    TileState<HD> st;
+    st.init();
+    int lo_r[2], hi_r[2];
+    hi_r[0] = r_a < n_rows ? pos0 + r_a : -1;                // rows beyond the tile see nothing
+    hi_r[1] = r_b < n_rows ? pos0 + r_b : -1;
+    lo_r[0] = window > 0 ? max(0, hi_r[0] - window + 1) : 0;
+    lo_r[1] = window > 0 ? max(0, hi_r[1] - window + 1) : 0;
+    const int w_hi = pos0 + min(n_rows - 1, warp * 16 + 15);  // last key this warp's rows see
+    const int w_lo = window > 0 ? max(0, pos0 + warp * 16 - window + 1) : 0;
+
+    gather_tile<HD, PF_KEYS, 128>(kbuf, k_pages, trow, kb_first * PF_KEYS, last_pos + 1, bs, nkv, kvh, threadIdx.x);
+    gather_tile<HD, PF_KEYS, 128>(vbuf, v_pages, trow, kb_first * PF_KEYS, last_pos + 1, bs, nkv, kvh, threadIdx.x);
+    __pipeline_commit();
+    for (int kb = kb_first; kb <= kb_last; ++kb) {
+        const int cur = (kb - kb_first) & 1;
+        if (kb < kb_last) {
+            gather_tile<HD, PF_KEYS, 128>(kbuf + (size_t)(cur ^ 1) * PF_KEYS * STR, k_pages, trow, (kb + 1) * PF_KEYS,
+                                          last_pos + 1, bs, nkv, kvh, threadIdx.x);
+            gather_tile<HD, PF_KEYS, 128>(vbuf + (size_t)(cur ^ 1) * PF_KEYS * STR, v_pages, trow, (kb + 1) * PF_KEYS,
+                                          last_pos + 1, bs, nkv, kvh, threadIdx.x);
+        }
+        __pipeline_commit();
+        __pipeline_wait_prior(1);
+        __syncthreads();
+        const int key0 = kb * PF_KEYS;
+        if (key0 <= w_hi && key0 + PF_KEYS - 1 >= w_lo)      // warp-uniform: some key of the tile is visible
+            attend_block<HD, PF_KEYS>(qf, kbuf + (size_t)cur * PF_KEYS * STR, vbuf + (size_t)cur * PF_KEYS * STR,
+                                      key0, lo_r, hi_r, scale, st, lane);
+        __syncthreads();
+    }
+    __pipeline_wait_prior(0);
+    // normalise and store
+    const float inv0 = st.l[0] > 0.f ? 1.f / st.l[0] : 0.f;
+    const float inv1 = st.l[1] > 0.f ? 1.f / st.l[1] : 0.f;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        const int d = 8 * i + 2 * t;
+        if (r_a < n_rows)
+            *reinterpret_cast<unsigned*>(out + ((size_t)(row0 + r_a) * nq + h) * HD + d) =
+                pack_bf16(st.o[i][0] * inv0, st.o[i][1] * inv0);
+        if (r_b < n_rows)
+            *reinterpret_cast<unsigned*>(out + ((size_t)(row0 + r_b) * nq + h) * HD + d) =
+                pack_bf16(st.o[i][2] * inv1, st.o[i][3] * inv1);
+    }
+}
+
+template <int HD>
+static int launch_prefill(const void* qkv, void* out, const int* tiles, int n_tiles, const void* k_pages,
+                          const void* v_pages, const int* table, int max_blocks, int bs, int nq, int nkv, float scale,
+                          int window, cudaStream_t s) {
+    constexpr int STR = HD + 8;
+    const size_t smem = (size_t)4 * PF_KEYS * STR * sizeof(bf16);
+    auto kern = prefill_kernel<HD>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<dim3(n_tiles, nq), 128, smem, s>>>((const bf16*)qkv, (bf16*)out, tiles, (const bf16*)k_pages,
+                                              (const bf16*)v_pages, table, max_blocks, bs, nq, nkv, scale, window);
+    return launch_status();
+}
+
+ZLLM_API int zllm_attention_prefill_bf16(const void* qkv, void* out, const int* tiles, int n_tiles,
+                                         const void* k_pages, const void* v_pages, const int* table, int max_blocks,
+                                         int bs, int nq, int nkv, int hd, float scale, int window, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (nkv <= 0 || nq % nkv || nq > 65535) return ZLLM_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    DISPATCH_HD(hd, (launch_prefill<H_>(qkv, out, tiles, n_tiles, k_pages, v_pages, table, max_blocks, bs, nq, nkv,
+                                        scale, window, s)))
+}

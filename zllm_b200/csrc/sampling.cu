@@ -137,3 +137,35 @@ ZLLM_API int zllm_topk(const float* logits, float* vals, int* idxs, int R, int V
     topk_kernel<<<R, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, vals, idxs, V, k);
     return launch_status();
 }
+
+// After a decode step sampled ``out``: make the step's own inputs those of the next step, so
+// that a captured decode graph can be replayed several times without the host in between.
+// tok <- out, pos += 1, seed += 0x9E3779B1 (the per-token seed rule of
+// zllm src/backend/gpu/sampling.rs:9); the sampled tokens are also appended to a history ring
+// [hist_cap, B] that the host reads once at the end.  One block; B <= 1024.
+__global__ void advance_decode_kernel(int* __restrict__ tok, int* __restrict__ pos, const int* __restrict__ row_slot,
+                                      unsigned* __restrict__ seeds, const int* __restrict__ out,
+                                      int* __restrict__ hist, int* __restrict__ counter, int hist_cap, int B) {
+    const int r = threadIdx.x;
+    const int c = counter[0];
+    if (r < B) {
+        const int t = out[r];
+        if (row_slot[r] >= 0) {
+            tok[r] = t;
+            pos[r] += 1;
+            seeds[r] += 0x9E3779B1u;
+        }
+        hist[(size_t)(c % hist_cap) * B + r] = t;
+    }
+    __syncthreads();
+    if (r == 0) counter[0] = c + 1;
+}
+
+ZLLM_API int zllm_advance_decode(int* tok, int* pos, const int* row_slot, unsigned* seeds, const int* out, int* hist,
+                                 int* counter, int hist_cap, int B, void* stream) {
+    if (B <= 0) return 0;
+    if (B > 1024 || hist_cap <= 0) return ZLLM_ERR_UNSUPPORTED;
+    advance_decode_kernel<<<1, ((B + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(tok, pos, row_slot, seeds, out, hist,
+                                                                              counter, hist_cap, B);
+    return launch_status();
+}

@@ -214,7 +214,61 @@ class ModelRunner:
         g["logits"] = logits
         buf = g["buf"]
         B = ctx.T
-        self.ops.sample(logits, buf.dev_section("temps", B).view(torch.float32), buf.dev_section("seeds", B), g["out"])
+        seeds = buf.dev_section("seeds", B)
+        self.ops.sample(logits, buf.dev_section("temps", B).view(torch.float32), seeds, g["out"])
+        if hasattr(self.ops, "advance_decode"):
+            # the step's inputs become those of the next step: a burst replays without the host
+            self.ops.advance_decode(ctx.token_ids, ctx.positions, ctx.row_slot, seeds, g["out"], g["hist"], g["counter"])
+
+    def decode_burst(self, slots: Sequence[int], tokens: Sequence[int], temps: Sequence[float],
+                     seeds: Sequence[int], n_steps: int) -> torch.Tensor:
+        """``n_steps`` decode steps back to back on the device: each step's sampled token is the
+        next step's input, positions and seeds advance on the device, and the host reads the
+        tokens [n_steps, len(slots)] once at the end.  Pages for all steps are taken up front.
+        Stop tokens are not looked at in between: the caller cuts the streams afterwards."""
+        if not (self.ecfg.cuda_graphs and self.device.type == "cuda"):
+            raise BackendError("decode_burst needs CUDA graphs")
+        if n_steps < 1 or n_steps > self.BURST_CAP:
+            raise RequestError(f"a burst has 1..{self.BURST_CAP} steps")
+        entries = [StepEntry(s, (t,), (0,)) for s, t in zip(slots, tokens)]
+        # pages for the whole burst, or nothing is run
+        if not self.cache.can_fit([(s, self.cache.length[s] + n_steps) for s in slots]):
+            raise MemoryError_(f"cache pool exhausted: free pages {self.cache.free_pages()} do not cover the burst")
+        starts = self._prepare(entries)
+        for s in slots:
+            if self.cache.length[s] + n_steps > self.max_len:
+                raise RequestError(f"slot {s}: the burst exceeds the maximum length {self.max_len}")
+            ok = self.cache.ensure(s, self.cache.length[s] + n_steps)
+            assert ok
+        n = len(entries)
+        bucket = _bucket(n)
+        split_bucket = _bucket(self.ops.decode_splits(max(starts) + n_steps))
+        key = (bucket, split_bucket)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = self._make_decode_graph(bucket, split_bucket, True)
+        buf = g["buf"]
+        fill_step(buf, entries, starts, pad_rows=bucket)
+        buf.host_section("want_rows")[:bucket] = range(bucket)
+        tf = buf.host_section("temps").view("float32")
+        tf[:bucket] = 0.0
+        tf[:n] = temps
+        sd = buf.host_section("seeds").view("uint32")
+        sd[:bucket] = 0
+        sd[:n] = [s & 0xFFFFFFFF for s in seeds]
+        buf.upload()
+        self.cache.sync_tables()
+        g["counter"].zero_()
+        for _ in range(n_steps):
+            g["graph"].replay()
+        for s, st in zip(slots, starts):
+            self.cache.advance(s, st + n_steps)
+        self.steps += n_steps
+        self.tokens_run += n * n_steps
+        self.last_logits = g["logits"]
+        return g["hist"][:n_steps, :n]
+
+    BURST_CAP = 1024
 
     def _make_decode_graph(self, bucket: int, split_bucket: int, use_graph: bool):
         buf = StepBuffers(bucket, bucket, self.device)
@@ -222,7 +276,9 @@ class ModelRunner:
         ctx.max_context = split_bucket * self.ops.decode_split_keys if split_bucket else 0
         ctx.fixed_splits = split_bucket
         out = torch.zeros(bucket, dtype=torch.int32, device=self.device)
-        g = {"buf": buf, "ctx": ctx, "out": out, "logits": None, "graph": None}
+        g = {"buf": buf, "ctx": ctx, "out": out, "logits": None, "graph": None,
+             "hist": torch.zeros((self.BURST_CAP, bucket), dtype=torch.int32, device=self.device),
+             "counter": torch.zeros(1, dtype=torch.int32, device=self.device), "launches": 0}
         if not use_graph:
             return g
         # neutral contents for warm-up and capture: every row is padding
@@ -239,8 +295,10 @@ class ModelRunner:
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        before = getattr(self.ops, "launches", 0)
         with torch.cuda.graph(graph):
             self._decode_body(g)
+        g["launches"] = getattr(self.ops, "launches", 0) - before     # kernels in one replay
         g["graph"] = graph
         return g
 

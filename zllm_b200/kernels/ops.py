@@ -141,7 +141,19 @@ class CudaOps:
                                                       c_int(out.dtype == torch.bfloat16), self._stream())
         self._check(code, "gemm_plain")
 
+    SKINNY_MAX_ROWS = 64
+
     def _linear_bf16(self, x, w, out, mode, M, N, K) -> bool:
+        """Tensor-core products for bfloat16 operands; False: these sizes go to the plain kernel.
+        The choice depends on the sizes only."""
+        if K % 8 or (mode == "swiglu" and N % 8) or (x.data_ptr() | w.data_ptr()) & 15:
+            return False
+        if M <= self.SKINNY_MAX_ROWS:
+            code = self.lib("gemm_bf16").zllm_gemm_skinny_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                                               c_int(MODES[mode]), c_int(out.dtype == torch.bfloat16),
+                                                               self._stream())
+            self._check(code, "gemm_skinny_bf16")
+            return True
         return False
 
     # ---- silu * up -----------------------------------------------------
@@ -218,7 +230,32 @@ class CudaOps:
         self._check(code, "attention_plain")
 
     def _attention_bf16(self, qkv, out, ctx, cache, nq, nkv, hd, scale, window) -> bool:
-        return False
+        """Tensor-core attention: decoded rows by the split kernel, portions by the tiled kernel.
+        False: head size or group not taken, every row goes to the plain kernel."""
+        if hd % 16 or hd > 128 or nq // nkv > 16:
+            return False
+        lib = self.lib("attention_bf16")
+        tb = cache.block_table
+        if ctx.n_decode > 0:
+            max_splits = max(1, -(-tb.shape[1] * cache.block_size // self.decode_split_keys))
+            n_splits = ctx.fixed_splits or min(max_splits, self.decode_splits(ctx.max_context))
+            nd = ctx.n_decode
+            part_o = ctx.ws.get("attn_part_o", (nd, nq * max_splits * hd), torch.float32, cap=nd)
+            part_ml = ctx.ws.get("attn_part_ml", (nd, nq * max_splits * 2), torch.float32, cap=nd)
+            code = lib.zllm_attention_decode_bf16(
+                _ptr(qkv), _ptr(out), _ptr(ctx.decode_rows), c_int(nd), _ptr(ctx.positions), _ptr(ctx.row_slot),
+                _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(tb), c_int(tb.shape[1]), c_int(cache.block_size),
+                c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window or 0), _ptr(part_o), _ptr(part_ml),
+                c_int(n_splits), c_int(max_splits), self._stream())
+            self._check(code, "attention_decode_bf16")
+            self.launches += 1                  # split kernel + combine kernel
+        if ctx.n_tiles > 0:
+            code = lib.zllm_attention_prefill_bf16(
+                _ptr(qkv), _ptr(out), _ptr(ctx.tiles), c_int(ctx.n_tiles), _ptr(cache.k_pages), _ptr(cache.v_pages),
+                _ptr(tb), c_int(tb.shape[1]), c_int(cache.block_size), c_int(nq), c_int(nkv), c_int(hd),
+                c_float(scale), c_int(window or 0), self._stream())
+            self._check(code, "attention_prefill_bf16")
+        return True
 
     # ---- sampling --------------------------------------------------------
     def sample(self, logits, temps, seeds, out):
@@ -235,6 +272,17 @@ class CudaOps:
         code = self.lib("sampling").zllm_sample(_ptr(logits), _ptr(temps), _ptr(seeds), _ptr(out), c_int(R), c_int(V),
                                                 self._stream())
         self._check(code, "sample")
+
+    def advance_decode(self, tok, pos, row_slot, seeds, out, hist, counter):
+        """tok <- out, pos += 1, seed += 0x9E3779B1 for live rows; out appended to the history ring."""
+        self._dev(tok, pos, row_slot, seeds, out, hist, counter)
+        B = tok.numel()
+        if hist.shape[1] != B or pos.numel() != B or out.numel() < B:
+            raise BackendError("advance_decode: shapes do not match the bucket")
+        code = self.lib("sampling").zllm_advance_decode(_ptr(tok), _ptr(pos), _ptr(row_slot), _ptr(seeds), _ptr(out),
+                                                        _ptr(hist), _ptr(counter), c_int(hist.shape[0]), c_int(B),
+                                                        self._stream())
+        self._check(code, "advance_decode")
 
     def topk(self, logits, k, vals, idx):
         self._dev(logits, vals, idx)
