@@ -34,9 +34,10 @@ class Engine:
     """
 
     def __init__(self, model: Optional[str] = None, *, config=None, seed: Optional[int] = None, ops=None,
-                 engine_config: Optional[EngineConfig] = None, **kw):
+                 engine_config: Optional[EngineConfig] = None, random_on_device: bool = False, **kw):
         ecfg = engine_config or EngineConfig(**kw)
-        self.runner = ModelRunner(model, config=config, seed=seed, engine_config=ecfg, ops=ops)
+        self.runner = ModelRunner(model, config=config, seed=seed, engine_config=ecfg, ops=ops,
+                                  random_on_device=random_on_device)
         self.config = self.runner.config
         self.scheduler = Scheduler(self.runner.cache, ecfg.max_num_batched_tokens, self.runner.max_len)
         self.sampler = Sampler(self.runner.ops, self.runner.device, max(ecfg.max_num_seqs, 1))

@@ -238,7 +238,7 @@ class CudaOps:
         tb = cache.block_table
         if ctx.n_decode > 0:
             max_splits = max(1, -(-tb.shape[1] * cache.block_size // self.decode_split_keys))
-            n_splits = ctx.fixed_splits or min(max_splits, self.decode_splits(ctx.max_context))
+            n_splits = min(max_splits, ctx.fixed_splits or self.decode_splits(ctx.max_context))
             nd = ctx.n_decode
             part_o = ctx.ws.get("attn_part_o", (nd, nq * max_splits * hd), torch.float32, cap=nd)
             part_ml = ctx.ws.get("attn_part_ml", (nd, nq * max_splits * 2), torch.float32, cap=nd)
