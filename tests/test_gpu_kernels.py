@@ -83,6 +83,7 @@ def test_linear(ops, M, N, K, dtype, mode):
     want = base.clone().float()
     REF.linear(x, w, want, mode)           # float32 accumulation, unrounded output
     err = float((out.cpu().float() - want).abs().max())
+    ops.check_async_errors()
     scale = float(want.abs().max())
     if dtype == torch.float32:
         assert err <= 2e-5 * max(scale, 1.0)

@@ -1,0 +1,332 @@
+// bfloat16 products for MANY rows (prompt portions) on the 5th-generation tensor cores:
+// out[m][n] = sum_k x[m][k] w[n][k], float32 accumulation in tensor memory.
+//
+// One CTA computes a 128 x 256 tile.  Operands come by TMA (cp.async.bulk.tensor, 128-byte
+// swizzle) into a 4-stage ring of shared-memory tiles [128][64] and [256][64]; one elected
+// thread issues tcgen05.mma (M = 128, N = 256, K = 16, four per stage) with the accumulator
+// in TMEM; tcgen05.commit hands stages back to the TMA warp and finally the accumulator to
+// the four epilogue warps, which read it with tcgen05.ld (each warp its 32 lanes) and apply
+// the epilogue straight from registers: store, add into the float32 residual, or
+// silu(gate) * up on weights interleaved in groups of 8 gate + 8 up rows.  Rows beyond M and
+// k beyond K are zero-filled by TMA; columns beyond N are not stored.
+//
+// zllm's counterpart is its cooperative-matrix GEMM for prefill (128 x 128 register-blocked,
+// BK = 32: src/backend/vulkan/shaders/coopmat_q4k_gemm.comp:1-41) with the residual add and
+// the gate/up concatenation folded in (src/backend/vulkan/mod.rs:1000-1021,1141-1167).
+//
+// Every wait on an mbarrier is bounded: when a limit runs out the kernel records where in
+// a device flag, drains what it started, frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+#define MODE_STORE 0
+#define MODE_ADD 1
+#define MODE_SWIGLU 2
+
+#define TC_BM 128
+#define TC_BN 256
+#define TC_BK 64
+#define TC_STAGES 4
+#define TC_A_BYTES (TC_BM * TC_BK * 2)
+#define TC_B_BYTES (TC_BN * TC_BK * 2)
+#define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
+#define TC_SMEM (TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */)
+#define TC_WAIT_LIMIT (1u << 24)
+
+__device__ int g_tc_error = 0;       // 0 ok; else 1 + index of the wait that gave up
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait: false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int where) {
+    for (unsigned i = 0; i < TC_WAIT_LIMIT; ++i) {
+        unsigned done;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    atomicCAS(&g_tc_error, 0, 1 + where);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                       unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, groups of 8 rows
+// 1024 bytes apart.  Fields: start address >> 4 [0,14), leading offset [16,30) (unused with
+// swizzle, 1), stride offset >> 4 [32,46) = 64, version 1 [46,48), layout SWIZZLE_128B = 2 [61,64).
+__device__ __forceinline__ unsigned long long umma_desc(unsigned saddr) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((saddr >> 4) & 0x3FFF);
+    d |= (unsigned long long)1 << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                         const __grid_constant__ CUtensorMap map_w,
+                                                         void* __restrict__ out, int M, int N, int K, int mode,
+                                                         int out_bf16) {
+    extern __shared__ unsigned char smem_raw[];
+    const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;         // swizzled tiles need 1024-byte alignment
+    unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const unsigned bars = base + TC_STAGES * TC_STAGE_BYTES;             // full[4], empty[4], accum, tmem slot
+    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(base_ptr + TC_STAGES * TC_STAGE_BYTES + 128);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TC_BN;                                   // first weight row of the tile
+    const int m0 = blockIdx.y * TC_BM;
+    const int k_iters = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            mbar_init(bars + 8 * s, 1);                                  // full: one arrive (expect_tx) + bytes
+            mbar_init(bars + 8 * (TC_STAGES + s), 1);                    // empty: one tcgen05.commit
+        }
+        mbar_init(bars + 8 * (2 * TC_STAGES), 1);                        // accumulator ready
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {                                                     // this warp owns the tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_acc = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            bool ok = true;
+            int issued = 0;
+            for (int it = 0; it < k_iters && ok; ++it) {
+                const int s = it % TC_STAGES;
+                const unsigned ph = (it / TC_STAGES) & 1;
+                ok = mbar_wait(bars + 8 * (TC_STAGES + s), ph ^ 1, 0);  // stage is free
+                if (!ok) break;
+                const unsigned full = bars + 8 * s;
+                mbar_expect_tx(full, TC_STAGE_BYTES);
+                const unsigned a_dst = base + s * TC_STAGE_BYTES;
+                tma_load_2d(a_dst, &map_x, it * TC_BK, m0, full);
+                tma_load_2d(a_dst + TC_A_BYTES, &map_w, it * TC_BK, n0, full);
+                issued = it + 1;
+            }
+            if (!ok) {
+                // drain: the copies already issued must land before the CTA may exit
+                for (int it = max(0, issued - TC_STAGES); it < issued; ++it)
+                    mbar_wait(bars + 8 * (it % TC_STAGES), (it / TC_STAGES) & 1, 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // instruction descriptor: D float32 [4,6) = 1, A and B bfloat16 [7,10) = [10,13) = 1, both
+            // K-major, N >> 3 at [17,23), M >> 4 at [24,29)
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TC_BN >> 3) << 17) |
+                                   ((unsigned)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int it = 0; it < k_iters && ok; ++it) {
+                const int s = it % TC_STAGES;
+                const unsigned ph = (it / TC_STAGES) & 1;
+                ok = mbar_wait(bars + 8 * s, ph, 2);                     // operands have landed
+                if (!ok) break;
+                tc_fence_after();
+                const unsigned a_addr = base + s * TC_STAGE_BYTES;
+                const unsigned long long adesc = umma_desc(a_addr);
+                const unsigned long long bdesc = umma_desc(a_addr + TC_A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)                     // 32 bytes along K per step: +2 in the address field
+                    tc_mma(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                tc_commit(bars + 8 * (TC_STAGES + s));                   // stage free when these MMAs have read it
+            }
+            tc_commit(bars + 8 * (2 * TC_STAGES));                       // accumulator complete
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, lane quadrant = warp % 4 ----------------
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const int m = m0 + row;
+        const bool ok = mbar_wait(bars + 8 * (2 * TC_STAGES), 0, 3);
+        tc_fence_after();
+        if (ok) {
+            const unsigned t_row = tmem_acc + ((unsigned)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < TC_BN; c += 32) {
+                if (n0 + c >= (mode == MODE_SWIGLU ? 2 * N : N)) break;  // warp-uniform
+                unsigned r[32];
+                tmem_ld32(t_row + c, r);
+                if (m >= M) continue;
+                if (mode == MODE_SWIGLU) {
+                    // columns c .. c+31 = two groups of (8 gate, 8 up) -> 16 outputs
+                    const int o0 = (n0 + c) / 2;
+                    float v[16];
+#pragma unroll
+                    for (int gi = 0; gi < 2; ++gi)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float g = __uint_as_float(r[gi * 16 + j]);
+                            const float u = __uint_as_float(r[gi * 16 + 8 + j]);
+                            v[gi * 8 + j] = g / (1.f + expf(-g)) * u;
+                        }
+                    if (out_bf16) {
+                        bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * N + o0;
+#pragma unroll
+                        for (int j = 0; j < 16; j += 8) {
+                            if (o0 + j >= N) break;
+                            uint4 pk;
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                            pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+                            pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+                            *reinterpret_cast<uint4*>(o + j) = pk;
+                        }
+                    } else {
+                        float* o = reinterpret_cast<float*>(out) + (size_t)m * N + o0;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (o0 + j < N) o[j] = v[j];
+                    }
+                } else if (mode == MODE_ADD) {
+                    float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n0 + c;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        if (n0 + c + j >= N) break;
+                        float4 cur = *reinterpret_cast<float4*>(o + j);
+                        cur.x += __uint_as_float(r[j]); cur.y += __uint_as_float(r[j + 1]);
+                        cur.z += __uint_as_float(r[j + 2]); cur.w += __uint_as_float(r[j + 3]);
+                        *reinterpret_cast<float4*>(o + j) = cur;
+                    }
+                } else if (out_bf16) {
+                    bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * N + n0 + c;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (n0 + c + j >= N) break;
+                        uint4 pk;
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                        pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+                        pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+                        *reinterpret_cast<uint4*>(o + j) = pk;
+                    }
+                } else {
+                    float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n0 + c;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        if (n0 + c + j >= N) break;
+                        *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                        __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TC_BN) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// [rows, K] bfloat16 row-major; box = box_rows x 64 elements, 128-byte swizzle, zero fill outside
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return ZLLM_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : ZLLM_ERR_UNSUPPORTED;
+}
+
+// x [M,K] bf16, w [N,K] bf16 ([2N,K] for swiglu), out [M,N].  K % 8 == 0, N % 8 == 0, operands 16-byte aligned.
+ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_bf16,
+                               void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K % 8) || (N % 8) || mode < 0 || mode > 2) return ZLLM_ERR_UNSUPPORTED;
+    if (mode == MODE_ADD && out_bf16) return ZLLM_ERR_UNSUPPORTED;
+    if ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15)) return ZLLM_ERR_UNSUPPORTED;
+    const int w_rows = mode == MODE_SWIGLU ? 2 * N : N;
+    CUtensorMap map_x, map_w;
+    int e = make_map(&map_x, x, M, K, TC_BM);
+    if (e) return e;
+    e = make_map(&map_w, w, w_rows, K, TC_BN);
+    if (e) return e;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t ce = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        if (ce != cudaSuccess) return (int)ce;
+        attr_set = true;
+    }
+    dim3 grid((w_rows + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
+    gemm_tc_kernel<<<grid, 192, TC_SMEM, (cudaStream_t)stream>>>(map_x, map_w, out, M, N, K, mode, out_bf16);
+    return launch_status();
+}
+
+// The device flag that a bounded wait sets when it gives up (0: none); reading clears it.
+ZLLM_API int zllm_gemm_tc_error(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    return v;
+}

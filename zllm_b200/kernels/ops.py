@@ -55,7 +55,7 @@ class CudaOps:
         self.dtype = dtype
         names = ["elementwise", "gemm_plain", "attention_plain", "sampling"]
         if dtype == torch.bfloat16:
-            names += [n for n in ("gemm_bf16", "attention_bf16") if (build.CSRC / f"{n}.cu").exists()]
+            names += ["gemm_bf16", "gemm_tc", "attention_bf16"]
         build.build(names)
         for n in names:
             self._libs[n] = build.load(n)
@@ -154,7 +154,21 @@ class CudaOps:
                                                                self._stream())
             self._check(code, "gemm_skinny_bf16")
             return True
+        if N % 8 == 0 and out.data_ptr() % 16 == 0 and "gemm_tc" in self._libs:
+            code = self.lib("gemm_tc").zllm_gemm_tc_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                                         c_int(MODES[mode]), c_int(out.dtype == torch.bfloat16),
+                                                         self._stream())
+            self._check(code, "gemm_tc_bf16")
+            return True
         return False
+
+    def check_async_errors(self):
+        """Raise if a kernel's bounded wait gave up since the last call (synchronises the device)."""
+        lib = self._libs.get("gemm_tc")
+        if lib is not None:
+            v = lib.zllm_gemm_tc_error()
+            if v != 0:
+                raise BackendError(f"gemm_tc: a bounded wait ran out (code {v}); results of that launch are invalid")
 
     # ---- silu * up -----------------------------------------------------
     def silu_mul(self, a, b, out):
