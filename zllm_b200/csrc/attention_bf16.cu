@@ -44,6 +44,12 @@ __device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* 
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
+// 2^x on the special-function unit (float32 in, float32 out; 2^-inf = 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<unsigned*>(&v);
@@ -64,23 +70,33 @@ struct TileState {
 
 // Gather NKEYS rows of K or V (keys key0 .. key0+NKEYS-1 of one request and kv head) into a
 // shared tile [NKEYS][HD + 8] with 16-byte async copies by NTHREADS threads.  Keys outside
-// [0, n_keys) or without a page are zero-filled.
+// [0, n_keys) or without a page are zero-filled.  Each thread looks up the page of its row
+// once; bs_shift >= 0 when the page size is a power of two (no division).
 template <int HD, int NKEYS, int NTHREADS>
 __device__ __forceinline__ void gather_tile(bf16* __restrict__ tile, const bf16* __restrict__ pages,
-                                            const int* __restrict__ trow, int key0, int n_keys, int bs, int nkv,
-                                            int kvh, int tid) {
+                                            const int* __restrict__ trow, int key0, int n_keys, int bs, int bs_shift,
+                                            int nkv, int kvh, int tid) {
     constexpr int CH = HD / 8;                       // 16-byte chunks per row
-    for (int i = tid; i < NKEYS * CH; i += NTHREADS) {
-        const int r = i / CH, c = i - r * CH;
+    constexpr int TPR = NTHREADS >= NKEYS ? NTHREADS / NKEYS : 1;     // threads per row
+    constexpr int ROWS_PER_PASS = NTHREADS / TPR;
+    const int part = tid % TPR;
+#pragma unroll
+    for (int r = tid / TPR; r < NKEYS; r += ROWS_PER_PASS) {
         const int key = key0 + r;
-        bf16* dst = tile + (size_t)r * (HD + 8) + c * 8;
-        int page = -1;
-        if (key >= 0 && key < n_keys) page = trow[key / bs];
-        if (page >= 0) {
-            const bf16* src = pages + ((((size_t)page * nkv + kvh) * bs + (key % bs)) * HD + c * 8);
-            __pipeline_memcpy_async(dst, src, 16);
+        bf16* dst = tile + (size_t)r * (HD + 8);
+        const bf16* src = nullptr;
+        if (key >= 0 && key < n_keys) {
+            const int blk = bs_shift >= 0 ? (key >> bs_shift) : key / bs;
+            const int off = bs_shift >= 0 ? (key & (bs - 1)) : key - blk * bs;
+            const int page = trow[blk];
+            if (page >= 0) src = pages + (((size_t)page * nkv + kvh) * bs + off) * HD;
+        }
+        if (src != nullptr) {
+#pragma unroll
+            for (int c = part; c < CH; c += TPR) __pipeline_memcpy_async(dst + c * 8, src + c * 8, 16);
         } else {
-            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int c = part; c < CH; c += TPR) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0, 0, 0, 0);
         }
     }
 }
@@ -90,7 +106,7 @@ __device__ __forceinline__ void gather_tile(bf16* __restrict__ tile, const bf16*
 //   ks, vs  : shared tiles [NB][HD + 8] of the block's keys / values
 //   key0    : absolute index of the block's first key
 //   lo_r/hi_r : per row (index 0: row g, 1: row g + 8) the visible key range [lo, hi]
-template <int HD, int NB>
+template <int HD, int NB, bool MASKED>
 __device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], const bf16* __restrict__ ks,
                                              const bf16* __restrict__ vs, int key0, const int (&lo_r)[2],
                                              const int (&hi_r)[2], float scale, TileState<HD>& st, int lane) {
@@ -113,17 +129,25 @@ __device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], c
             mma16816(s[j + 1], qf[kk], b[2], b[3]);
         }
     }
-    // scale, mask, running max
+    // running max in the scaled log2 domain (scale > 0 holds log2(e): max commutes with it);
+    // only blocks that touch a row's edge of visibility pay for the masking
     float mx[2] = {-INFINITY, -INFINITY};
+    if (MASKED) {
 #pragma unroll
-    for (int j = 0; j < NB / 8; ++j) {
+        for (int j = 0; j < NB / 8; ++j) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int r = e >> 1;
-            const int key = key0 + 8 * j + 2 * t + (e & 1);
-            const float v = (key >= lo_r[r] && key <= hi_r[r]) ? s[j][e] * scale : -INFINITY;
-            s[j][e] = v;
-            mx[r] = fmaxf(mx[r], v);
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const int key = key0 + 8 * j + 2 * t + (e & 1);
+                if (!(key >= lo_r[r] && key <= hi_r[r])) s[j][e] = -INFINITY;
+                mx[r] = fmaxf(mx[r], s[j][e]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NB / 8; ++j) {
+            mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+            mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
         }
     }
     float corr[2], msafe[2];
@@ -131,8 +155,8 @@ __device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], c
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(st.m[r], mx[r]);
-        corr[r] = (m_new == -INFINITY) ? 1.f : expf(st.m[r] - m_new);
+        const float m_new = fmaxf(st.m[r], mx[r] * scale);
+        corr[r] = (m_new == -INFINITY) ? 1.f : ex2_approx(st.m[r] - m_new);
         msafe[r] = (m_new == -INFINITY) ? 0.f : m_new;
         st.m[r] = m_new;
     }
@@ -142,7 +166,7 @@ __device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], c
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
-            const float p = expf(s[j][e] - msafe[r]);        // exp(-inf) = 0 for hidden keys
+            const float p = ex2_approx(fmaf(s[j][e], scale, -msafe[r]));     // 2^(-inf) = 0 for hidden keys
             s[j][e] = p;
             rs[r] += p;
         }
@@ -183,7 +207,7 @@ template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
     const bf16* __restrict__ qkv, const int* __restrict__ rows, const int* __restrict__ positions,
     const int* __restrict__ row_slot, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
-    const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, float scale, int window,
+    const int* __restrict__ table, int max_blocks, int bs, int bs_shift, int nq, int nkv, float scale, int window,
     float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits) {
     constexpr int STR = HD + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -221,12 +245,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
     for (int it = 0; it < SPLIT_KEYS / DEC_WARPS / DEC_BLOCK; ++it) {
         const int key0 = w_first + it * DEC_BLOCK;
         if (key0 > pos) break;                               // warp-uniform
-        gather_tile<HD, DEC_BLOCK, 32>(ks, k_pages, trow, key0, pos + 1, bs, nkv, kvh, lane);
-        gather_tile<HD, DEC_BLOCK, 32>(vs, v_pages, trow, key0, pos + 1, bs, nkv, kvh, lane);
+        gather_tile<HD, DEC_BLOCK, 32>(ks, k_pages, trow, key0, pos + 1, bs, bs_shift, nkv, kvh, lane);
+        gather_tile<HD, DEC_BLOCK, 32>(vs, v_pages, trow, key0, pos + 1, bs, bs_shift, nkv, kvh, lane);
         __pipeline_commit();
         __pipeline_wait_prior(0);
         __syncwarp();
-        attend_block<HD, DEC_BLOCK>(qf, ks, vs, key0, lo_r, hi_r, scale, st, lane);
+        if (key0 >= lo && key0 + DEC_BLOCK - 1 <= pos)
+            attend_block<HD, DEC_BLOCK, false>(qf, ks, vs, key0, lo_r, hi_r, scale, st, lane);
+        else
+            attend_block<HD, DEC_BLOCK, true>(qf, ks, vs, key0, lo_r, hi_r, scale, st, lane);
         __syncwarp();                                        // tile is reused by the next iteration
     }
     // merge the warps' partials in warp order
@@ -255,7 +282,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) {
             const float mw = wm[w * 16 + h];
-            const float f = (mw == -INFINITY) ? 0.f : expf(mw - M);
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
             L += wl[w * 16 + h] * f;
             O += wo[((size_t)w * 16 + h) * HD + d] * f;
         }
@@ -287,14 +314,14 @@ __global__ void decode_combine_kernel(const int* __restrict__ rows, const int* _
     float L = 0.f;
     for (int s = 0; s < ns; ++s) {
         const float ms = part_ml[(base + s) * 2];
-        L += part_ml[(base + s) * 2 + 1] * ((ms == -INFINITY) ? 0.f : expf(ms - M));
+        L += part_ml[(base + s) * 2 + 1] * ((ms == -INFINITY) ? 0.f : exp2f(ms - M));
     }
     const float inv = L > 0.f ? 1.f / L : 0.f;
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < ns; ++s) {
             const float ms = part_ml[(base + s) * 2];
-            acc += part_o[(base + s) * HD + d] * ((ms == -INFINITY) ? 0.f : expf(ms - M));
+            acc += part_o[(base + s) * HD + d] * ((ms == -INFINITY) ? 0.f : exp2f(ms - M));
         }
         o[d] = __float2bfloat16_rn(acc * inv);
     }
@@ -313,9 +340,10 @@ static int launch_decode(const void* qkv, void* out, const int* rows, int n_rows
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(n_rows, nkv, n_splits);
+    const int bs_shift = (bs & (bs - 1)) == 0 ? __builtin_ctz(bs) : -1;
     kern<<<grid, DEC_WARPS * 32, smem, s>>>((const bf16*)qkv, rows, positions, row_slot, (const bf16*)k_pages,
-                                            (const bf16*)v_pages, table, max_blocks, bs, nq, nkv, scale, window,
-                                            part_o, part_ml, max_splits);
+                                            (const bf16*)v_pages, table, max_blocks, bs, bs_shift, nq, nkv,
+                                            scale * 1.4426950408889634f, window, part_o, part_ml, max_splits);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     decode_combine_kernel<HD><<<dim3(n_rows, nq), HD <= 64 ? 64 : 128, 0, s>>>(rows, positions, row_slot, part_o, part_ml,
@@ -360,13 +388,13 @@ template <int HD>
 __global__ void __launch_bounds__(128) prefill_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out,
                                                       const int* __restrict__ tiles, const bf16* __restrict__ k_pages,
                                                       const bf16* __restrict__ v_pages, const int* __restrict__ table,
-                                                      int max_blocks, int bs, int nq, int nkv, float scale,
-                                                      int window) {
+                                                      int max_blocks, int bs, int bs_shift, int nq, int nkv,
+                                                      float scale, int window) {
     constexpr int STR = HD + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);          // [2][PF_KEYS][STR]
     bf16* vbuf = kbuf + 2 * PF_KEYS * STR;                   // [2][PF_KEYS][STR]
-    const int* tl = tiles + 4 * blockIdx.x;
+    const int* tl = tiles + 4 * (gridDim.x - 1 - blockIdx.x);   // later tiles see more keys: start them first
     const int row0 = tl[0], n_rows = tl[1], slot = tl[2], pos0 = tl[3];
     const int h = blockIdx.y;
     const int kvh = h / (nq / nkv);
@@ -401,25 +429,33 @@ __global__ void __launch_bounds__(128) prefill_kernel(const bf16* __restrict__ q
     lo_r[1] = window > 0 ? max(0, hi_r[1] - window + 1) : 0;
     const int w_hi = pos0 + min(n_rows - 1, warp * 16 + 15);  // last key this warp's rows see
     const int w_lo = window > 0 ? max(0, pos0 + warp * 16 - window + 1) : 0;
+    // the range every row of the warp sees in full (empty when the warp holds rows beyond the tile)
+    const int w_min_hi = (warp * 16 + 15 < n_rows) ? pos0 + warp * 16 : -1;
+    const int w_max_lo = window > 0 ? max(0, pos0 + warp * 16 + 15 - window + 1) : 0;
 
-    gather_tile<HD, PF_KEYS, 128>(kbuf, k_pages, trow, kb_first * PF_KEYS, last_pos + 1, bs, nkv, kvh, threadIdx.x);
-    gather_tile<HD, PF_KEYS, 128>(vbuf, v_pages, trow, kb_first * PF_KEYS, last_pos + 1, bs, nkv, kvh, threadIdx.x);
+    gather_tile<HD, PF_KEYS, 128>(kbuf, k_pages, trow, kb_first * PF_KEYS, last_pos + 1, bs, bs_shift, nkv, kvh, threadIdx.x);
+    gather_tile<HD, PF_KEYS, 128>(vbuf, v_pages, trow, kb_first * PF_KEYS, last_pos + 1, bs, bs_shift, nkv, kvh, threadIdx.x);
     __pipeline_commit();
     for (int kb = kb_first; kb <= kb_last; ++kb) {
         const int cur = (kb - kb_first) & 1;
         if (kb < kb_last) {
             gather_tile<HD, PF_KEYS, 128>(kbuf + (size_t)(cur ^ 1) * PF_KEYS * STR, k_pages, trow, (kb + 1) * PF_KEYS,
-                                          last_pos + 1, bs, nkv, kvh, threadIdx.x);
+                                          last_pos + 1, bs, bs_shift, nkv, kvh, threadIdx.x);
             gather_tile<HD, PF_KEYS, 128>(vbuf + (size_t)(cur ^ 1) * PF_KEYS * STR, v_pages, trow, (kb + 1) * PF_KEYS,
-                                          last_pos + 1, bs, nkv, kvh, threadIdx.x);
+                                          last_pos + 1, bs, bs_shift, nkv, kvh, threadIdx.x);
         }
         __pipeline_commit();
         __pipeline_wait_prior(1);
         __syncthreads();
         const int key0 = kb * PF_KEYS;
-        if (key0 <= w_hi && key0 + PF_KEYS - 1 >= w_lo)      // warp-uniform: some key of the tile is visible
-            attend_block<HD, PF_KEYS>(qf, kbuf + (size_t)cur * PF_KEYS * STR, vbuf + (size_t)cur * PF_KEYS * STR,
-                                      key0, lo_r, hi_r, scale, st, lane);
+        if (key0 <= w_hi && key0 + PF_KEYS - 1 >= w_lo) {    // warp-uniform: some key of the tile is visible
+            if (key0 + PF_KEYS - 1 <= w_min_hi && key0 >= w_max_lo)   // every key visible to every row of the warp
+                attend_block<HD, PF_KEYS, false>(qf, kbuf + (size_t)cur * PF_KEYS * STR,
+                                                 vbuf + (size_t)cur * PF_KEYS * STR, key0, lo_r, hi_r, scale, st, lane);
+            else
+                attend_block<HD, PF_KEYS, true>(qf, kbuf + (size_t)cur * PF_KEYS * STR,
+                                                vbuf + (size_t)cur * PF_KEYS * STR, key0, lo_r, hi_r, scale, st, lane);
+        }
         __syncthreads();
     }
     __pipeline_wait_prior(0);
@@ -447,8 +483,10 @@ static int launch_prefill(const void* qkv, void* out, const int* tiles, int n_ti
     auto kern = prefill_kernel<HD>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+    const int bs_shift = (bs & (bs - 1)) == 0 ? __builtin_ctz(bs) : -1;
     kern<<<dim3(n_tiles, nq), 128, smem, s>>>((const bf16*)qkv, (bf16*)out, tiles, (const bf16*)k_pages,
-                                              (const bf16*)v_pages, table, max_blocks, bs, nq, nkv, scale, window);
+                                              (const bf16*)v_pages, table, max_blocks, bs, bs_shift, nq, nkv,
+                                              scale * 1.4426950408889634f, window);
     return launch_status();
 }
 

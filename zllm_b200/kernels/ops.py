@@ -246,7 +246,7 @@ class CudaOps:
     def _attention_bf16(self, qkv, out, ctx, cache, nq, nkv, hd, scale, window) -> bool:
         """Tensor-core attention: decoded rows by the split kernel, portions by the tiled kernel.
         False: head size or group not taken, every row goes to the plain kernel."""
-        if hd % 16 or hd > 128 or nq // nkv > 16:
+        if hd % 16 or hd > 128 or nq // nkv > 16 or not scale > 0:
             return False
         lib = self.lib("attention_bf16")
         tb = cache.block_table
