@@ -131,6 +131,20 @@ class RefOps:
             o = torch.einsum("hn,nhd->hd", pr, V)
             out[t].copy_(o.reshape(-1).to(out.dtype))
 
+    # ---- fused forms (the compositions they stand for) ----------------------------------------
+    def linear_normed(self, x, norm_w, eps, w, out, mode, ws):
+        h = torch.empty(x.shape, dtype=w.dtype)
+        self.rmsnorm(x, norm_w, eps, h)
+        self.linear(h, w, out, mode)
+
+    def qkv_rope_store(self, x, norm, w_qkv, qkv, ctx, rot, cache, nq, nkv, hd, write_cache, ws):
+        if norm is not None:
+            h = torch.empty(x.shape, dtype=w_qkv.dtype)
+            self.rmsnorm(x, norm[0], norm[1], h)
+            x = h
+        self.linear(x, w_qkv, qkv, "store")
+        self.rope_kv_store(qkv, ctx, rot, cache, nq, nkv, hd, write_cache)
+
     def gather_rows(self, x, rows, out):
         out.copy_(x[rows.long()])
 

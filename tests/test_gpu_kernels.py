@@ -283,3 +283,78 @@ def test_kernels_refuse_what_they_cannot_run(ops):
         ops.rmsnorm(x.t(), torch.ones(64, device=DEV), 1e-5, torch.zeros(64, 4, device=DEV))   # not contiguous
     with pytest.raises(BackendError):
         ops.embedding(torch.zeros(4, dtype=torch.int64, device=DEV), x, torch.zeros(4, 64, device=DEV))
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 17, 40])
+@pytest.mark.parametrize("N,K,mode", [(72, 64, "store"), (136, 200, "add"), (96, 264, "swiglu"), (2048, 2304, "store"),
+                                      (264, 4104, "add"), (1000, 520, "store")])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+def test_linear_with_norm_prologue(ops, M, N, K, mode, wdtype):
+    """rmsnorm folded into the product (decode batches) against norm-then-product."""
+    from gpu_util import DEV
+    from zllm_b200.engine.batch import Workspace
+    x = rnd((M, K), torch.float32, 21, 3.0)
+    nw = (1 + rnd((K,), torch.float32, 22, 0.2)).to(wdtype)
+    w = rnd((N, K), torch.bfloat16, 23, K ** -0.5)
+    if mode == "swiglu":
+        w = interleave_gate_up(w, rnd((N, K), torch.bfloat16, 24, K ** -0.5))
+    odt = torch.float32 if mode == "add" else torch.bfloat16
+    base = rnd((M, N), odt, 25)
+    out = base.clone().to(DEV)
+    ops.linear_normed(x.to(DEV), nw.to(DEV), 1e-5, w.to(DEV), out, mode, Workspace(64, DEV))
+    want = base.clone().float()
+    h = torch.empty(M, K)
+    REF.rmsnorm(x, nw, 1e-5, h)
+    REF.linear(h, w, want, mode)
+    err = float((out.cpu().float() - want).abs().max())
+    assert err <= 2 ** -7 * max(1.0, float(want.abs().max())), err
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 13, 16, 20])
+@pytest.mark.parametrize("nq,nkv,hd,inter", [(4, 2, 16, False), (3, 1, 32, True), (8, 2, 64, False), (2, 1, 128, False),
+                                             (5, 5, 48, True)])
+@pytest.mark.parametrize("with_norm", [False, True])
+def test_qkv_product_with_rope_and_cache_write(ops, M, nq, nkv, hd, inter, with_norm):
+    """The fused QKV product (norm prologue, rotation and cache write in the epilogue) against
+    the composition of the separate kernels' plain statements."""
+    import copy
+    from zllm_b200.engine.batch import Workspace
+    from zllm_b200.models.decoder import Runtime
+    from zllm_b200.parts.rotary import Rotary
+    dtype = torch.bfloat16
+    H = 200
+    rot = Rotary(hd, 10000.0, 300, interleaved=inter)
+    rot.bind(Runtime(dtype, torch.device(DEV), ops))
+    bs = 6
+    cm = make_cache(nkv, hd, bs, 500, M + 1, 200, dtype)
+    slots = [cm.admit() for _ in range(M)]
+    for i, s in enumerate(slots):
+        make_ctx(cm, [(s, 3 + 5 * i)])                   # every request at another position
+    ctx = make_ctx(cm, [(s, 1) for s in slots])
+    N = (nq + 2 * nkv) * hd
+    w = rnd((N, H), dtype, 31, H ** -0.5)
+    x32 = rnd((M, H), torch.float32, 32, 2.0)
+    nw = 1 + rnd((H,), torch.float32, 33, 0.2)
+    view = cm.view(0)
+    view.k_pages.zero_(); view.v_pages.zero_()
+    qkv = torch.zeros(M, N, dtype=dtype, device=DEV)
+    ws = Workspace(64, DEV)
+    if with_norm:
+        ops.qkv_rope_store(x32.to(DEV), (nw.to(DEV), 1e-6), w.to(DEV), qkv, ctx, rot.rotary(), view, nq, nkv, hd, True, ws)
+        xin = torch.empty(M, H)
+        REF.rmsnorm(x32, nw, 1e-6, xin)
+    else:
+        xin = x32.to(dtype)
+        ops.qkv_rope_store(xin.to(DEV), None, w.to(DEV), qkv, ctx, rot.rotary(), view, nq, nkv, hd, True, ws)
+        xin = xin.float()
+    crot = copy.copy(rot.rotary()); crot.cos = crot.cos.cpu(); crot.sin = crot.sin.cpu()
+    cview = CpuCacheView(view); cview.k_pages.zero_(); cview.v_pages.zero_()
+    want = torch.zeros(M, N)
+    REF.linear(xin, w.float(), want, "store")
+    REF.rope_kv_store(want, cpu_ctx(ctx), crot, cview, nq, nkv, hd, True)
+    sc = max(1.0, float(want.abs().max()))
+    qk = (nq + nkv) * hd                                  # q and k are compared in the buffer, v in the cache
+    assert float((qkv.cpu().float()[:, :qk] - want[:, :qk]).abs().max()) <= 2 ** -7 * sc
+    assert float((view.k_pages.float().cpu() - cview.k_pages).abs().max()) <= 2 ** -7 * sc
+    assert float((view.v_pages.float().cpu() - cview.v_pages).abs().max()) <= 2 ** -7 * sc
+    assert float(cview.k_pages.abs().sum()) > 0 and float(cview.v_pages.abs().sum()) > 0

@@ -28,6 +28,7 @@
 #define DEC_BLOCK 32            // keys per warp iteration in the decode kernel
 #define PF_QROWS 64             // query rows per prefill CTA
 #define PF_KEYS 64              // keys per prefill tile
+#define PF_STAGES 3             // shared-memory tiles in flight
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -211,6 +212,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
     float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits) {
     constexpr int STR = HD + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    pdl_trigger();
+    pdl_wait();
     const int row = rows[blockIdx.x];
     const int slot = row_slot[row];
     if (slot < 0) return;
@@ -298,6 +301,8 @@ __global__ void decode_combine_kernel(const int* __restrict__ rows, const int* _
                                       const int* __restrict__ row_slot, const float* __restrict__ part_o,
                                       const float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int window,
                                       int max_splits) {
+    pdl_trigger();
+    pdl_wait();
     const int row = rows[blockIdx.x];
     const int h = blockIdx.y;
     bf16* o = out + ((size_t)row * nq + h) * HD;
@@ -341,14 +346,12 @@ static int launch_decode(const void* qkv, void* out, const int* rows, int n_rows
     if (e != cudaSuccess) return (int)e;
     dim3 grid(n_rows, nkv, n_splits);
     const int bs_shift = (bs & (bs - 1)) == 0 ? __builtin_ctz(bs) : -1;
-    kern<<<grid, DEC_WARPS * 32, smem, s>>>((const bf16*)qkv, rows, positions, row_slot, (const bf16*)k_pages,
-                                            (const bf16*)v_pages, table, max_blocks, bs, bs_shift, nq, nkv,
-                                            scale * 1.4426950408889634f, window, part_o, part_ml, max_splits);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return (int)e;
-    decode_combine_kernel<HD><<<dim3(n_rows, nq), HD <= 64 ? 64 : 128, 0, s>>>(rows, positions, row_slot, part_o, part_ml,
-                                                                             (bf16*)out, nq, window, max_splits);
-    return launch_status();
+    int rc = launch_pdl(kern, grid, dim3(DEC_WARPS * 32), smem, s, (const bf16*)qkv, rows, positions, row_slot,
+                        (const bf16*)k_pages, (const bf16*)v_pages, table, max_blocks, bs, bs_shift, nq, nkv,
+                        scale * 1.4426950408889634f, window, part_o, part_ml, max_splits);
+    if (rc) return rc;
+    return launch_pdl(decode_combine_kernel<HD>, dim3(n_rows, nq), dim3(HD <= 64 ? 64 : 128), 0, s, rows, positions,
+                      row_slot, (const float*)part_o, (const float*)part_ml, (bf16*)out, nq, window, max_splits);
 }
 
 #define DISPATCH_HD(HDV, CALL)                                                     \
@@ -385,15 +388,15 @@ ZLLM_API int zllm_attention_decode_bf16(const void* qkv, void* out, const int* r
 // ------------------------------------------------------------------------------------ prefill
 // tiles [n_tiles][4] = (first row, rows (<= 64), slot, position of first row)
 template <int HD>
-__global__ void __launch_bounds__(128) prefill_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out,
+__global__ void __launch_bounds__(128, HD <= 64 ? 4 : 2) prefill_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out,
                                                       const int* __restrict__ tiles, const bf16* __restrict__ k_pages,
                                                       const bf16* __restrict__ v_pages, const int* __restrict__ table,
                                                       int max_blocks, int bs, int bs_shift, int nq, int nkv,
                                                       float scale, int window) {
     constexpr int STR = HD + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);          // [2][PF_KEYS][STR]
-    bf16* vbuf = kbuf + 2 * PF_KEYS * STR;                   // [2][PF_KEYS][STR]
+    bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);          // [PF_STAGES][PF_KEYS][STR]
+    bf16* vbuf = kbuf + PF_STAGES * PF_KEYS * STR;           // [PF_STAGES][PF_KEYS][STR]
     const int* tl = tiles + 4 * (gridDim.x - 1 - blockIdx.x);   // later tiles see more keys: start them first
     const int row0 = tl[0], n_rows = tl[1], slot = tl[2], pos0 = tl[3];
     const int h = blockIdx.y;
@@ -433,19 +436,22 @@ __global__ void __launch_bounds__(128) prefill_kernel(const bf16* __restrict__ q
     const int w_min_hi = (warp * 16 + 15 < n_rows) ? pos0 + warp * 16 : -1;
     const int w_max_lo = window > 0 ? max(0, pos0 + warp * 16 + 15 - window + 1) : 0;
 
-    gather_tile<HD, PF_KEYS, 128>(kbuf, k_pages, trow, kb_first * PF_KEYS, last_pos + 1, bs, bs_shift, nkv, kvh, threadIdx.x);
-    gather_tile<HD, PF_KEYS, 128>(vbuf, v_pages, trow, kb_first * PF_KEYS, last_pos + 1, bs, bs_shift, nkv, kvh, threadIdx.x);
+    // three-stage ring: tiles kb + 1 and kb + 2 are in flight while tile kb is used
+    auto load_tile = [&](int kb, int stage) {
+        gather_tile<HD, PF_KEYS, 128>(kbuf + (size_t)stage * PF_KEYS * STR, k_pages, trow, kb * PF_KEYS, last_pos + 1,
+                                      bs, bs_shift, nkv, kvh, threadIdx.x);
+        gather_tile<HD, PF_KEYS, 128>(vbuf + (size_t)stage * PF_KEYS * STR, v_pages, trow, kb * PF_KEYS, last_pos + 1,
+                                      bs, bs_shift, nkv, kvh, threadIdx.x);
+    };
+    load_tile(kb_first, 0);
+    __pipeline_commit();
+    if (kb_first + 1 <= kb_last) load_tile(kb_first + 1, 1);
     __pipeline_commit();
     for (int kb = kb_first; kb <= kb_last; ++kb) {
-        const int cur = (kb - kb_first) & 1;
-        if (kb < kb_last) {
-            gather_tile<HD, PF_KEYS, 128>(kbuf + (size_t)(cur ^ 1) * PF_KEYS * STR, k_pages, trow, (kb + 1) * PF_KEYS,
-                                          last_pos + 1, bs, bs_shift, nkv, kvh, threadIdx.x);
-            gather_tile<HD, PF_KEYS, 128>(vbuf + (size_t)(cur ^ 1) * PF_KEYS * STR, v_pages, trow, (kb + 1) * PF_KEYS,
-                                          last_pos + 1, bs, bs_shift, nkv, kvh, threadIdx.x);
-        }
+        const int cur = (kb - kb_first) % PF_STAGES;
+        if (kb + 2 <= kb_last) load_tile(kb + 2, (kb - kb_first + 2) % PF_STAGES);
         __pipeline_commit();
-        __pipeline_wait_prior(1);
+        __pipeline_wait_prior(2);
         __syncthreads();
         const int key0 = kb * PF_KEYS;
         if (key0 <= w_hi && key0 + PF_KEYS - 1 >= w_lo) {    // warp-uniform: some key of the tile is visible
@@ -479,7 +485,7 @@ static int launch_prefill(const void* qkv, void* out, const int* tiles, int n_ti
                           const void* v_pages, const int* table, int max_blocks, int bs, int nq, int nkv, float scale,
                           int window, cudaStream_t s) {
     constexpr int STR = HD + 8;
-    const size_t smem = (size_t)4 * PF_KEYS * STR * sizeof(bf16);
+    const size_t smem = (size_t)2 * PF_STAGES * PF_KEYS * STR * sizeof(bf16);
     auto kern = prefill_kernel<HD>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

@@ -48,3 +48,37 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats *
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch -------------------------------------------------------
+// A decode step is a chain of ~100 small kernels, each waiting for the one before.  Launched
+// with the programmatic-serialization attribute, a kernel may start while its predecessor is
+// still running: it announces itself (pdl_trigger), does what does not depend on the
+// predecessor (fetching weights), and only then waits for the predecessor's results
+// (pdl_wait).  EVERY kernel launched through launch_pdl must call pdl_wait() before it reads
+// or writes anything another kernel of the step touches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+// ZLLM_NO_PDL=1 launches every kernel fully serialized (for measuring what the overlap buys)
+static inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("ZLLM_NO_PDL"); v = (e && e[0] == '1') ? 0 : 1; }
+    return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

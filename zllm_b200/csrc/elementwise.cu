@@ -12,6 +12,8 @@
 template <typename WT>
 __global__ void embedding_kernel(const int* __restrict__ tok, const WT* __restrict__ table, float* __restrict__ out,
                                  int H, int V) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = tok[t];
     float* o = out + (size_t)t * H;
@@ -27,9 +29,8 @@ ZLLM_API int zllm_embedding(const int* tok, const void* table, float* out, int T
                             void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (table_bf16) embedding_kernel<bf16><<<T, 256, 0, s>>>(tok, (const bf16*)table, out, H, V);
-    else embedding_kernel<float><<<T, 256, 0, s>>>(tok, (const float*)table, out, H, V);
-    return launch_status();
+    if (table_bf16) return launch_pdl(embedding_kernel<bf16>, dim3(T), dim3(256), 0, s, tok, (const bf16*)table, out, H, V);
+    return launch_pdl(embedding_kernel<float>, dim3(T), dim3(256), 0, s, tok, (const float*)table, out, H, V);
 }
 
 // ---------------------------------------------------------------- rmsnorm
@@ -38,6 +39,8 @@ template <typename WT, typename OT>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict__ w, OT* __restrict__ y, int H,
                                float eps) {
     __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
     const float* xr = x + (size_t)blockIdx.x * H;
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss += v * v; }
@@ -52,16 +55,17 @@ ZLLM_API int zllm_rmsnorm(const float* x, const void* w, void* y, int T, int H, 
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int th = H >= 1024 ? 256 : 128;
-    if (w_bf16 && out_bf16) rmsnorm_kernel<bf16, bf16><<<T, th, 0, s>>>(x, (const bf16*)w, (bf16*)y, H, eps);
-    else if (w_bf16) rmsnorm_kernel<bf16, float><<<T, th, 0, s>>>(x, (const bf16*)w, (float*)y, H, eps);
-    else if (out_bf16) rmsnorm_kernel<float, bf16><<<T, th, 0, s>>>(x, (const float*)w, (bf16*)y, H, eps);
-    else rmsnorm_kernel<float, float><<<T, th, 0, s>>>(x, (const float*)w, (float*)y, H, eps);
-    return launch_status();
+    if (w_bf16 && out_bf16) return launch_pdl(rmsnorm_kernel<bf16, bf16>, dim3(T), dim3(th), 0, s, x, (const bf16*)w, (bf16*)y, H, eps);
+    if (w_bf16) return launch_pdl(rmsnorm_kernel<bf16, float>, dim3(T), dim3(th), 0, s, x, (const bf16*)w, (float*)y, H, eps);
+    if (out_bf16) return launch_pdl(rmsnorm_kernel<float, bf16>, dim3(T), dim3(th), 0, s, x, (const float*)w, (bf16*)y, H, eps);
+    return launch_pdl(rmsnorm_kernel<float, float>, dim3(T), dim3(th), 0, s, x, (const float*)w, (float*)y, H, eps);
 }
 
 // ---------------------------------------------------------------- silu * up
 template <typename AT>
 __global__ void silu_mul_kernel(const AT* __restrict__ g, const AT* __restrict__ u, AT* __restrict__ o, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         float a = to_f32(g[i]);
@@ -73,14 +77,15 @@ ZLLM_API int zllm_silu_mul(const void* g, const void* u, void* o, long long n, i
     if (n <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     unsigned blocks = (unsigned)((n + 255) / 256);
-    if (is_bf16) silu_mul_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)g, (const bf16*)u, (bf16*)o, (size_t)n);
-    else silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)g, (const float*)u, (float*)o, (size_t)n);
-    return launch_status();
+    if (is_bf16) return launch_pdl(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (const bf16*)g, (const bf16*)u, (bf16*)o, (size_t)n);
+    return launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)g, (const float*)u, (float*)o, (size_t)n);
 }
 
 // ---------------------------------------------------------------- gather rows (float32)
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, float* __restrict__ out,
                                    int H) {
+    pdl_trigger();
+    pdl_wait();
     const float* src = x + (size_t)rows[blockIdx.x] * H;
     float* dst = out + (size_t)blockIdx.x * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
@@ -88,8 +93,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __res
 
 ZLLM_API int zllm_gather_rows(const float* x, const int* rows, float* out, int R, int H, void* stream) {
     if (R <= 0) return 0;
-    gather_rows_kernel<<<R, 256, 0, (cudaStream_t)stream>>>(x, rows, out, H);
-    return launch_status();
+    return launch_pdl(gather_rows_kernel, dim3(R), dim3(256), 0, (cudaStream_t)stream, x, rows, out, H);
 }
 
 // ---------------------------------------------------------------- rotary + cache write
@@ -105,6 +109,8 @@ __global__ void rope_kv_store_kernel(AT* __restrict__ qkv, const int* __restrict
                                      AT* __restrict__ k_pages, AT* __restrict__ v_pages,
                                      const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, int hd,
                                      int store) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int slot = row_slot[t];
     if (slot < 0) return;                       // padding row of a graph bucket
@@ -149,12 +155,10 @@ ZLLM_API int zllm_rope_kv_store(void* qkv, const int* positions, const int* row_
     if (rot_dim > hd || (rot_dim & 1)) return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (is_bf16)
-        rope_kv_store_kernel<bf16><<<T, 256, 0, s>>>((bf16*)qkv, positions, row_slot, cos_t, sin_t, rot_dim, interleaved,
-                                                     (bf16*)k_pages, (bf16*)v_pages, table, max_blocks, bs, nq, nkv, hd,
-                                                     store);
-    else
-        rope_kv_store_kernel<float><<<T, 256, 0, s>>>((float*)qkv, positions, row_slot, cos_t, sin_t, rot_dim,
-                                                      interleaved, (float*)k_pages, (float*)v_pages, table, max_blocks,
-                                                      bs, nq, nkv, hd, store);
-    return launch_status();
+        return launch_pdl(rope_kv_store_kernel<bf16>, dim3(T), dim3(256), 0, s, (bf16*)qkv, positions, row_slot, cos_t,
+                          sin_t, rot_dim, interleaved, (bf16*)k_pages, (bf16*)v_pages, table, max_blocks, bs, nq, nkv,
+                          hd, store);
+    return launch_pdl(rope_kv_store_kernel<float>, dim3(T), dim3(256), 0, s, (float*)qkv, positions, row_slot, cos_t,
+                      sin_t, rot_dim, interleaved, (float*)k_pages, (float*)v_pages, table, max_blocks, bs, nq, nkv, hd,
+                      store);
 }

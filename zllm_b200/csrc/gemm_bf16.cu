@@ -84,11 +84,9 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
     };
 
     const int n_chunks = (k_end > k_begin) ? (k_end - k_begin + SK_KC - 1) / SK_KC : 0;
-    if (n_chunks > 0) load_x_chunk(0, k_begin);
-    for (int c = 0; c < n_chunks; ++c) {
-        const int kc = k_begin + c * SK_KC;
-        // weights of this chunk: 4 steps of 64 k, two 16-byte loads per row per step
-        uint4 fa[4][2], fb[4][2];
+    // weights of a chunk: 4 steps of 64 k, two 16-byte loads per row per step
+    uint4 fa[4][2], fb[4][2];
+    auto load_w_chunk = [&](int kc) {
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
 #pragma unroll
@@ -99,6 +97,21 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
                 fb[s][hf] = (vb && in) ? ldg_stream(wb + k) : make_uint4(0, 0, 0, 0);
             }
         }
+    };
+    // Weights do not depend on the kernel before this one: let the next kernel start, fetch the
+    // first chunk into registers and ask L2 for the rest of this CTA's slice, and only then wait
+    // for x.
+    pdl_trigger();
+    if (n_chunks > 0) load_w_chunk(k_begin);
+    for (int k = k_begin + SK_KC + t * 64; k < k_end; k += 256) {      // one 128-byte line per lane and row
+        if (va) asm volatile("prefetch.global.L2 [%0];" ::"l"(wa + k));
+        if (vb) asm volatile("prefetch.global.L2 [%0];" ::"l"(wb + k));
+    }
+    pdl_wait();
+    if (n_chunks > 0) load_x_chunk(0, k_begin);
+    for (int c = 0; c < n_chunks; ++c) {
+        const int kc = k_begin + c * SK_KC;
+        if (c > 0) load_w_chunk(kc);
         if (c + 1 < n_chunks) load_x_chunk((c + 1) & 1, kc + SK_KC);
         else __pipeline_commit();
         __pipeline_wait_prior(1);                    // chunk c of x has landed
@@ -192,13 +205,15 @@ static int launch_skinny(const void* x, const void* w, void* out, int M, int N, 
     cfg.blockDim = dim3(256, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = csize;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     e = cudaLaunchKernelEx(&cfg, kern, (const bf16*)x, (const bf16*)w, out, M, N, K, kslice, mode, out_bf16, w_rows);
     return (int)e;
 }

@@ -1,0 +1,338 @@
+// The decode step's products, fused with what stands before and after them (M <= 16 rows).
+//
+//   out = epilogue( [rmsnorm](x) W^T )
+//
+// A decode step of a small model is a chain of ~10 dependent kernels per layer, each far
+// too short to fill the GPU; what it costs is the length of the chain.  zllm met the same
+// on its hardware and fused RoPE into the QKV matvec epilogue
+// (src/backend/vulkan/shaders/decode_matvec_q4k_rope.comp:1-51), the residual add into the
+// O and down products (src/backend/gpu/mod.rs:2492-2497) and SiLU-mul into the gate/up
+// product (src/backend/vulkan/mod.rs:1141-1167); folding RMSNorm into a matvec's consumer
+// lost there because it was recomputed per output row (BENCHMARKS.md:152-155).  Here a CTA
+// owns 16 output rows and ALL of K, so it sees whole rows of x: the norm costs one pass over
+// x per CTA (x is at most 16 rows), the sum of squares is taken while x is staged, and the
+// scalar 1/rms is applied to the accumulators at the end.
+//
+// Layout of the work: one CTA = 16 weight rows; its 8 warps split K (256 k per warp per pass
+// of 2048); each warp streams its weights straight from global memory into mma.sync
+// fragments (16 consecutive k per lane and row, see gemm_bf16.cu) and stages its own slice
+// of x in its own shared memory, so no CTA-wide barrier is needed until the 8 partial tiles
+// are summed, in warp order, through shared memory.  No cluster, no scratch, deterministic;
+// a row of x never mixes with another row.
+//
+// Epilogues: store, add into the float32 residual, swiglu (the 16 rows are 8 gate + 8 up
+// rows), and rope: the 16 rows of a tile are the 8 rotation pairs (j, j + hd/2) of one head,
+// so the pair sits in one thread after the reduction; the rotated q goes to the qkv buffer,
+// the rotated k and the v go straight to their cache page.
+#include "common.cuh"
+#include <cuda_pipeline.h>
+
+#define MODE_STORE 0
+#define MODE_ADD 1
+#define MODE_SWIGLU 2
+#define MODE_ROPE 3
+
+#define GD_WARPS 8
+#define GD_KW 256                       // k per warp per pass
+#define GD_PASS (GD_WARPS * GD_KW)      // k per pass of the CTA
+#define GD_XSTRIDE (GD_KW + 8)
+
+struct GemmDecodeParams {
+    const void* x;          // [M, K] bf16, or float32 when norm_w != nullptr
+    const void* norm_w;     // [K] rmsnorm weight (nullptr: x is used as it is)
+    int norm_w_bf16;
+    float eps;
+    const bf16* w;          // [w_rows, K]
+    void* out;
+    int M, N, K, mode, out_bf16, w_rows;
+    // rope epilogue
+    const int* positions;
+    const int* row_slot;
+    const float* cos_t;
+    const float* sin_t;
+    int interleaved, nq, nkv, hd;
+    bf16* k_pages;
+    bf16* v_pages;
+    const int* table;
+    int max_blocks, bs, store;
+};
+
+__device__ __forceinline__ void gd_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                       unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 gd_ldg(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ unsigned gd_pack(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Which weight rows the tile's fragment rows g and g + 8 are.  Plain: 16 consecutive rows.
+// Rope: tile = (head, part); q and k heads pair row j with j + hd/2 (or 2j with 2j + 1 when
+// interleaved); v heads are plain.
+__device__ __forceinline__ void gd_rows(const GemmDecodeParams& p, int tile, int g, int& ra, int& rb) {
+    if (p.mode != MODE_ROPE) {
+        ra = tile * 16 + g;
+        rb = ra + 8;
+        return;
+    }
+    const int tiles_per_head = p.hd / 16;
+    const int head = tile / tiles_per_head, part = tile - head * tiles_per_head;
+    const int base = head * p.hd;
+    if (head >= p.nq + p.nkv) {
+        ra = base + part * 16 + g;
+        rb = ra + 8;
+    } else if (p.interleaved) {
+        ra = base + part * 16 + 2 * g;
+        rb = ra + 1;
+    } else {
+        ra = base + part * 8 + g;
+        rb = ra + p.hd / 2;
+    }
+}
+
+template <int NT, bool FUSE_NORM>
+__global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const GemmDecodeParams p) {
+    constexpr int MP = NT * 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* xs_all = reinterpret_cast<bf16*>(smem_raw);                        // [warps][MP][GD_XSTRIDE]
+    float* red = reinterpret_cast<float*>(smem_raw);                         // [warps][16][MP + 1], after the loop
+    __shared__ float ss_part[GD_WARPS][MP];
+    __shared__ float inv_rms[MP];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int tile = blockIdx.x;
+    const int M = p.M, K = p.K;
+    int ra, rb;
+    gd_rows(p, tile, g, ra, rb);
+    const bool va = ra < p.w_rows, vb = rb < p.w_rows;
+    const bf16* wa = p.w + (size_t)(va ? ra : 0) * K;
+    const bf16* wb = p.w + (size_t)(vb ? rb : 0) * K;
+    bf16* xs = xs_all + (size_t)warp * MP * GD_XSTRIDE;
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    float ss[MP];                                                            // FUSE_NORM: this lane's share of sum x^2
+#pragma unroll
+    for (int m = 0; m < MP; ++m) ss[m] = 0.f;
+
+    uint4 fa[4][2], fb[4][2];
+    auto load_w = [&](int kb) {
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int k = kb + s * 64 + t * 16 + hf * 8;
+                fa[s][hf] = (va && k < K) ? gd_ldg(wa + k) : make_uint4(0, 0, 0, 0);
+                fb[s][hf] = (vb && k < K) ? gd_ldg(wb + k) : make_uint4(0, 0, 0, 0);
+            }
+    };
+    const int n_pass = (K + GD_PASS - 1) / GD_PASS;
+    // weights do not depend on the kernel before: fetch the first pass, ask L2 for the rest, then wait
+    pdl_trigger();
+    load_w(warp * GD_KW);
+    for (int ps = 1; ps < n_pass; ++ps) {
+        const int k = ps * GD_PASS + warp * GD_KW + t * 64;
+        if (k < K) {
+            if (va) asm volatile("prefetch.global.L2 [%0];" ::"l"(wa + k));
+            if (vb) asm volatile("prefetch.global.L2 [%0];" ::"l"(wb + k));
+        }
+    }
+    pdl_wait();
+
+    for (int ps = 0; ps < n_pass; ++ps) {
+        const int kb = ps * GD_PASS + warp * GD_KW;                          // this warp's 256 k of the pass
+        if (ps > 0) load_w(kb);
+        // stage x[0..M)[kb .. kb+256) as bf16; lane takes 8 consecutive k of every row
+        const int kx = kb + lane * 8;
+        if (FUSE_NORM) {
+            float gw[8];
+            if (kx < K) {
+                if (p.norm_w_bf16) {
+                    const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.norm_w) + kx);
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { float2 f = __bfloat1622float2(h[i]); gw[2 * i] = f.x; gw[2 * i + 1] = f.y; }
+                } else {
+                    const float4 g0 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm_w) + kx);
+                    const float4 g1 = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.norm_w) + kx + 4);
+                    gw[0] = g0.x; gw[1] = g0.y; gw[2] = g0.z; gw[3] = g0.w; gw[4] = g1.x; gw[5] = g1.y; gw[6] = g1.z; gw[7] = g1.w;
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < MP; ++m) {
+                uint4 pk = make_uint4(0, 0, 0, 0);
+                if (m < M && kx < K) {
+                    const float* xr = reinterpret_cast<const float*>(p.x) + (size_t)m * K + kx;
+                    const float4 a = *reinterpret_cast<const float4*>(xr);
+                    const float4 b = *reinterpret_cast<const float4*>(xr + 4);
+                    ss[m] += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+                    pk.x = gd_pack(a.x * gw[0], a.y * gw[1]);
+                    pk.y = gd_pack(a.z * gw[2], a.w * gw[3]);
+                    pk.z = gd_pack(b.x * gw[4], b.y * gw[5]);
+                    pk.w = gd_pack(b.z * gw[6], b.w * gw[7]);
+                }
+                *reinterpret_cast<uint4*>(xs + (size_t)m * GD_XSTRIDE + lane * 8) = pk;
+            }
+        } else {
+#pragma unroll
+            for (int m = 0; m < MP; ++m) {
+                bf16* d = xs + (size_t)m * GD_XSTRIDE + lane * 8;
+                if (m < M && kx < K)
+                    __pipeline_memcpy_async(d, reinterpret_cast<const bf16*>(p.x) + (size_t)m * K + kx, 16);
+                else
+                    *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+            }
+            __pipeline_commit();
+            __pipeline_wait_prior(0);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const uint4 A = fa[s][hf], B = fb[s][hf];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const uint4 X = *reinterpret_cast<const uint4*>(xs + (size_t)(nt * 8 + g) * GD_XSTRIDE + s * 64 +
+                                                                    t * 16 + hf * 8);
+                    gd_mma(acc[nt], A.x, B.x, A.y, B.y, X.x, X.y);
+                    gd_mma(acc[nt], A.z, B.z, A.w, B.w, X.z, X.w);
+                }
+            }
+        __syncwarp();                                                        // the slice is overwritten by the next pass
+    }
+    // ---- sum the 8 warps' partial tiles (and sums of squares) in warp order ----
+    if (FUSE_NORM) {
+#pragma unroll
+        for (int m = 0; m < MP; ++m) {
+            const float v = warp_sum(ss[m]);
+            if (lane == 0) ss_part[warp][m] = v;
+        }
+    }
+    __syncthreads();                                                         // every warp is done with its x slice
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int m = nt * 8 + 2 * t;
+        float* r0 = red + ((size_t)warp * 16 + g) * (MP + 1) + m;
+        float* r1 = red + ((size_t)warp * 16 + g + 8) * (MP + 1) + m;
+        r0[0] = acc[nt][0]; r0[1] = acc[nt][1];
+        r1[0] = acc[nt][2]; r1[1] = acc[nt][3];
+    }
+    if (FUSE_NORM && threadIdx.x < MP) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < GD_WARPS; ++w) tot += ss_part[w][threadIdx.x];
+        inv_rms[threadIdx.x] = rsqrtf(tot / (float)K + p.eps);
+    }
+    __syncthreads();
+    auto total = [&](int r16, int m) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < GD_WARPS; ++w) v += red[((size_t)w * 16 + r16) * (MP + 1) + m];
+        return FUSE_NORM ? v * inv_rms[m] : v;
+    };
+    const int mode = p.mode;
+    if (mode == MODE_STORE || mode == MODE_ADD) {
+        for (int i = threadIdx.x; i < 16 * M; i += blockDim.x) {
+            const int m = i >> 4, r = i & 15;
+            const int n = tile * 16 + r;
+            if (n >= p.N) continue;
+            const float v = total(r, m);
+            const size_t o = (size_t)m * p.N + n;
+            if (mode == MODE_ADD) reinterpret_cast<float*>(p.out)[o] += v;
+            else if (p.out_bf16) reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float*>(p.out)[o] = v;
+        }
+    } else if (mode == MODE_SWIGLU) {
+        for (int i = threadIdx.x; i < 8 * M; i += blockDim.x) {
+            const int m = i >> 3, j = i & 7;
+            const int col = tile * 8 + j;
+            if (col >= p.N) continue;
+            const float gt = total(j, m), up = total(j + 8, m);
+            const float v = gt / (1.f + expf(-gt)) * up;
+            if (p.out_bf16) reinterpret_cast<bf16*>(p.out)[(size_t)m * p.N + col] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float*>(p.out)[(size_t)m * p.N + col] = v;
+        }
+    } else {   // MODE_ROPE
+        const int tiles_per_head = p.hd / 16;
+        const int head = tile / tiles_per_head, part = tile - head * tiles_per_head;
+        const int half = p.hd / 2;
+        const bool rotated = head < p.nq + p.nkv;
+        for (int i = threadIdx.x; i < 8 * M; i += blockDim.x) {
+            const int m = i >> 3, j = i & 7;
+            const int slot = p.row_slot[m];
+            if (slot < 0) continue;                                          // padding row of a graph bucket
+            float a = total(j, m), b = total(j + 8, m);
+            int da, db;                                                      // dims within the head
+            if (!rotated) { da = part * 16 + j; db = da + 8; }
+            else if (p.interleaved) { da = part * 16 + 2 * j; db = da + 1; }
+            else { da = part * 8 + j; db = da + half; }
+            const int pos = p.positions[m];
+            if (rotated && p.cos_t != nullptr) {
+                const int jj = p.interleaved ? (da >> 1) : da;               // index of the pair
+                const float c = p.cos_t[(size_t)pos * half + jj], s = p.sin_t[(size_t)pos * half + jj];
+                const float ar = a * c - b * s, br = a * s + b * c;
+                a = ar; b = br;
+            }
+            const bf16 ha = __float2bfloat16_rn(a), hb = __float2bfloat16_rn(b);
+            if (head < p.nq + p.nkv) {                                       // q and k also go to the qkv buffer
+                bf16* o = reinterpret_cast<bf16*>(p.out) + (size_t)m * p.N + (size_t)head * p.hd;
+                o[da] = ha; o[db] = hb;
+            }
+            if (head >= p.nq && p.store) {
+                const int page = p.table[(size_t)slot * p.max_blocks + pos / p.bs];
+                if (page < 0) continue;
+                const bool is_k = head < p.nq + p.nkv;
+                const int kvh = is_k ? head - p.nq : head - p.nq - p.nkv;
+                bf16* dst = (is_k ? p.k_pages : p.v_pages) + (((size_t)page * p.nkv + kvh) * p.bs + pos % p.bs) * p.hd;
+                dst[da] = ha; dst[db] = hb;
+            }
+        }
+    }
+}
+
+template <int NT, bool FUSE_NORM>
+static int launch_gd(const GemmDecodeParams& p, cudaStream_t s) {
+    constexpr int MP = NT * 8;
+    size_t smem = (size_t)GD_WARPS * MP * GD_XSTRIDE * sizeof(bf16);
+    const size_t red = (size_t)GD_WARPS * 16 * (MP + 1) * sizeof(float);
+    if (red > smem) smem = red;
+    auto kern = gemm_decode_kernel<NT, FUSE_NORM>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    const int tiles = (p.w_rows + 15) / 16;
+    return launch_pdl(kern, dim3(tiles), dim3(GD_WARPS * 32), smem, s, p);
+}
+
+// See GemmDecodeParams.  M <= 16; K % 8 == 0; 16-byte aligned operands.
+// mode 3 (rope): N = (nq + 2 nkv) * hd, hd % 16 == 0, rotation over the whole head.
+ZLLM_API int zllm_gemm_decode(const void* x, const void* norm_w, int norm_w_bf16, float eps, const void* w, void* out,
+                              int M, int N, int K, int mode, int out_bf16, const int* positions, const int* row_slot,
+                              const float* cos_t, const float* sin_t, int interleaved, int nq, int nkv, int hd,
+                              void* k_pages, void* v_pages, const int* table, int max_blocks, int bs, int store,
+                              void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 16 || K <= 0 || (K % 8) || mode < 0 || mode > 3) return ZLLM_ERR_UNSUPPORTED;
+    if (mode == MODE_ADD && out_bf16) return ZLLM_ERR_UNSUPPORTED;
+    if (mode == MODE_SWIGLU && (N % 8)) return ZLLM_ERR_UNSUPPORTED;
+    if (mode == MODE_ROPE && (hd % 16 || N != (nq + 2 * nkv) * hd || !out_bf16)) return ZLLM_ERR_UNSUPPORTED;
+    if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)norm_w) & 15) return ZLLM_ERR_UNSUPPORTED;
+    GemmDecodeParams p;
+    p.x = x; p.norm_w = norm_w; p.norm_w_bf16 = norm_w_bf16; p.eps = eps; p.w = (const bf16*)w; p.out = out;
+    p.M = M; p.N = N; p.K = K; p.mode = mode; p.out_bf16 = out_bf16;
+    p.w_rows = mode == MODE_SWIGLU ? 2 * N : N;
+    p.positions = positions; p.row_slot = row_slot; p.cos_t = cos_t; p.sin_t = sin_t; p.interleaved = interleaved;
+    p.nq = nq; p.nkv = nkv; p.hd = hd; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages; p.table = table;
+    p.max_blocks = max_blocks; p.bs = bs; p.store = store;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool fuse = norm_w != nullptr;
+    if (M <= 8) return fuse ? launch_gd<1, true>(p, s) : launch_gd<1, false>(p, s);
+    return fuse ? launch_gd<2, true>(p, s) : launch_gd<2, false>(p, s);
+}

@@ -33,6 +33,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
                                                                 int* __restrict__ out, int V) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const float* lg = logits + (size_t)row * V;
     const float temp = temps ? temps[row] : 0.f;
@@ -73,8 +75,7 @@ ZLLM_API int zllm_sample(const float* logits, const float* temps, const unsigned
                          void* stream) {
     if (R <= 0) return 0;
     if (V <= 0) return ZLLM_ERR_UNSUPPORTED;
-    sample_kernel<<<R, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, temps, seeds, out, V);
-    return launch_status();
+    return launch_pdl(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, temps, seeds, out, V);
 }
 
 // top-k candidates in descending order (value desc, index asc); fewer than k distinct
@@ -146,6 +147,8 @@ ZLLM_API int zllm_topk(const float* logits, float* vals, int* idxs, int R, int V
 __global__ void advance_decode_kernel(int* __restrict__ tok, int* __restrict__ pos, const int* __restrict__ row_slot,
                                       unsigned* __restrict__ seeds, const int* __restrict__ out,
                                       int* __restrict__ hist, int* __restrict__ counter, int hist_cap, int B) {
+    pdl_trigger();
+    pdl_wait();
     const int r = threadIdx.x;
     const int c = counter[0];
     if (r < B) {
@@ -165,7 +168,6 @@ ZLLM_API int zllm_advance_decode(int* tok, int* pos, const int* row_slot, unsign
                                  int* counter, int hist_cap, int B, void* stream) {
     if (B <= 0) return 0;
     if (B > 1024 || hist_cap <= 0) return ZLLM_ERR_UNSUPPORTED;
-    advance_decode_kernel<<<1, ((B + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(tok, pos, row_slot, seeds, out, hist,
-                                                                              counter, hist_cap, B);
-    return launch_status();
+    return launch_pdl(advance_decode_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, (cudaStream_t)stream, tok, pos,
+                      row_slot, seeds, out, hist, counter, hist_cap, B);
 }

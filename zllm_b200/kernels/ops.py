@@ -55,7 +55,7 @@ class CudaOps:
         self.dtype = dtype
         names = ["elementwise", "gemm_plain", "attention_plain", "sampling"]
         if dtype == torch.bfloat16:
-            names += ["gemm_bf16", "gemm_tc", "attention_bf16"]
+            names += ["gemm_decode", "gemm_bf16", "gemm_tc", "attention_bf16"]
         build.build(names)
         for n in names:
             self._libs[n] = build.load(n)
@@ -142,12 +142,86 @@ class CudaOps:
         self._check(code, "gemm_plain")
 
     SKINNY_MAX_ROWS = 64
+    DECODE_MAX_ROWS = 16
+
+    def _gemm_decode(self, x, norm_w, eps, w, out, mode, M, N, K, rope=None):
+        """The fused decode product (csrc/gemm_decode.cu).  rope: (ctx, rot, cache, nq, nkv, hd, store)."""
+        if rope is None:
+            pos = slot = cos = sin = kp = vp = tb = None
+            inter = nq = nkv = hd = mb = bs = store = 0
+            code_mode = MODES[mode]
+        else:
+            ctx, rot, cache, nq, nkv, hd, store = rope
+            pos, slot = ctx.positions, ctx.row_slot
+            cos, sin = (rot.cos, rot.sin) if rot is not None else (None, None)
+            inter = int(rot.interleaved) if rot is not None else 0
+            if store:
+                kp, vp, tb, mb, bs = cache.k_pages, cache.v_pages, cache.block_table, cache.block_table.shape[1], cache.block_size
+            else:
+                kp = vp = tb = None
+                mb = bs = 1
+            code_mode = 3
+        code = self.lib("gemm_decode").zllm_gemm_decode(
+            _ptr(x), _ptr(norm_w), c_int(norm_w is not None and norm_w.dtype == torch.bfloat16), c_float(eps), _ptr(w),
+            _ptr(out), c_int(M), c_int(N), c_int(K), c_int(code_mode), c_int(out.dtype == torch.bfloat16), _ptr(pos),
+            _ptr(slot), _ptr(cos), _ptr(sin), c_int(inter), c_int(nq), c_int(nkv), c_int(hd), _ptr(kp), _ptr(vp),
+            _ptr(tb), c_int(mb), c_int(bs), c_int(1 if store else 0), self._stream())
+        self._check(code, "gemm_decode")
+
+    def _can_fuse_decode(self, x, norm_w, w, M, K) -> bool:
+        return (self.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= self.DECODE_MAX_ROWS and K % 8 == 0
+                and (x.data_ptr() | w.data_ptr() | (norm_w.data_ptr() if norm_w is not None else 0)) & 15 == 0)
+
+    def linear_normed(self, x, norm_w, eps, w, out, mode, ws):
+        """out = epilogue(rmsnorm(x; norm_w, eps) w^T), x the float32 residual.  One kernel for decode
+        batches; otherwise the norm kernel into a scratch buffer, then the product."""
+        self._dev(x, norm_w, w, out)
+        M, K = x.shape
+        N = out.shape[1]
+        if x.dtype != torch.float32 or norm_w.numel() != K or w.shape[1] != K or out.shape[0] != M \
+                or w.shape[0] != (2 * N if mode == "swiglu" else N):
+            raise BackendError("linear_normed: bad operand types or shapes")
+        if self._can_fuse_decode(x, norm_w, w, M, K) and not (mode == "swiglu" and N % 8) \
+                and not (mode == "add" and out.dtype != torch.float32):
+            self._gemm_decode(x, norm_w, eps, w, out, mode, M, N, K)
+            return
+        h = ws.get("normed", (M, K), self.dtype)
+        self.rmsnorm(x, norm_w, eps, h)
+        self.linear(h, w, out, mode)
+
+    def qkv_rope_store(self, x, norm, w_qkv, qkv, ctx, rot, cache, nq, nkv, hd, write_cache, ws):
+        """qkv = [rmsnorm](x) w_qkv^T, q and k rotated, k and v written to their cache pages.
+        ``norm`` is (weight, eps) when x is the float32 residual, None when x is already normed."""
+        self._dev(x, w_qkv, qkv)
+        M, K = x.shape
+        N = (nq + 2 * nkv) * hd
+        if tuple(qkv.shape) != (M, N) or tuple(w_qkv.shape) != (N, K):
+            raise BackendError("qkv_rope_store: shapes do not match the head counts")
+        norm_w, eps = norm if norm is not None else (None, 0.0)
+        fused = (self._can_fuse_decode(x, norm_w, w_qkv, M, K) and qkv.dtype == torch.bfloat16 and hd % 16 == 0
+                 and (rot is None or rot.rot_dim == hd) and (norm is None or x.dtype == torch.float32)
+                 and (norm is not None or x.dtype == torch.bfloat16))
+        if fused:
+            if write_cache:
+                self._check_cache(cache, nkv, hd, qkv.dtype, "qkv_rope_store")
+            self._gemm_decode(x, norm_w, eps, w_qkv, qkv, "store", M, N, K,
+                              rope=(ctx, rot, cache, nq, nkv, hd, bool(write_cache)))
+            return
+        if norm is not None:
+            h = ws.get("normed", (M, K), self.dtype)
+            self.rmsnorm(x, norm_w, eps, h)
+            x = h
+        self.linear(x, w_qkv, qkv, "store")
+        self.rope_kv_store(qkv, ctx, rot, cache, nq, nkv, hd, write_cache)
 
     def _linear_bf16(self, x, w, out, mode, M, N, K) -> bool:
         """Tensor-core products for bfloat16 operands; False: these sizes go to the plain kernel.
         The choice depends on the sizes only."""
         if K % 8 or (mode == "swiglu" and N % 8) or (x.data_ptr() | w.data_ptr()) & 15:
             return False
+        if M <= self.DECODE_MAX_ROWS:
+            self._gemm_decode(x, None, 0.0, w, out, mode, M, N, K)
+            return True
         if M <= self.SKINNY_MAX_ROWS:
             code = self.lib("gemm_bf16").zllm_gemm_skinny_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
                                                                c_int(MODES[mode]), c_int(out.dtype == torch.bfloat16),

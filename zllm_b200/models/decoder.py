@@ -125,8 +125,12 @@ class DecoderModel:
             return None
         rows = ctx.ws.get("head_rows", (R, self.spec.hidden_size), torch.float32, cap=R)
         ops.gather_rows(x, ctx.want_rows, rows)
-        hn = ctx.ws.get("head_in", (R, self.spec.hidden_size), rt.dtype, cap=R)
-        self.final_norm.forward(rows, hn, ctx)
         logits = ctx.ws.get("logits", (R, self.spec.vocab_size), torch.float32, cap=R)
-        ops.linear(hn, self.head, logits, "store")
+        pro = self.final_norm.as_prologue()
+        if pro is not None:
+            ops.linear_normed(rows, pro[0], pro[1], self.head, logits, "store", ctx.ws)
+        else:
+            hn = ctx.ws.get("head_in", (R, self.spec.hidden_size), rt.dtype, cap=R)
+            self.final_norm.forward(rows, hn, ctx)
+            ops.linear(hn, self.head, logits, "store")
         return logits

@@ -67,14 +67,17 @@ class PagedAttention(Mixer):
         self.w_qkv = torch.cat([tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]], dim=0).contiguous()
         self.w_o = tensors["o_proj"].contiguous()
 
-    def forward(self, h, residual, ctx, cache, write_cache: bool = True):
+    accepts_input_norm = True
+
+    def forward(self, h, residual, ctx, cache, write_cache: bool = True, input_norm=None):
+        """``input_norm`` None: h is the normed input.  Otherwise h is the float32 residual and
+        ``input_norm`` = (weight, eps) of the RMS norm to apply to it inside the QKV product."""
         ops = self.rt.ops
         T = h.shape[0]
         nq, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         qkv = ctx.ws.get("qkv", (T, (nq + 2 * nkv) * hd), self.rt.dtype)
-        ops.linear(h, self.w_qkv, qkv, "store")
         rot = self.position_encoding.rotary() if self.position_encoding is not None else None
-        ops.rope_kv_store(qkv, ctx, rot, cache, nq, nkv, hd, write_cache)
+        ops.qkv_rope_store(h, input_norm, self.w_qkv, qkv, ctx, rot, cache, nq, nkv, hd, write_cache, ctx.ws)
         att = ctx.ws.get("attn_out", (T, nq * hd), self.rt.dtype)
         ops.paged_attention(qkv, att, ctx, cache, nq, nkv, hd, self.scale, self.window)
         ops.linear(att, self.w_o, residual, "add")

@@ -155,6 +155,10 @@ class Norm(Part):
     def forward(self, x, out, ctx):
         raise NotImplementedError
 
+    def as_prologue(self):
+        """(weight, eps) if a following product may apply this norm itself (an RMS norm), else None."""
+        return None
+
 
 class PositionEncoding(Part):
     def rotary(self):
@@ -167,6 +171,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True: ``forward`` takes ``input_norm=(weight, eps)`` and then receives the float32 residual
+    # itself as ``h`` (it applies the norm inside its first product)
+    accepts_input_norm = False
+
     def cache_spec(self):
         return None
 
@@ -175,6 +183,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_input_norm = False          # as for Mixer
+
     def forward(self, h, residual, ctx):
         raise NotImplementedError
 

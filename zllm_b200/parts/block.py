@@ -28,8 +28,17 @@ class Layer:
 @register_arrangement("pre_norm")
 def pre_norm(layer: Layer, x, ctx, cache, write_cache):
     rt = layer.mixer.rt
-    h = ctx.ws.get("normed", tuple(x.shape), rt.dtype)
-    layer.norm1.forward(x, h, ctx)
-    layer.mixer.forward(h, x, ctx, cache, write_cache)
-    layer.norm2.forward(x, h, ctx)
-    layer.ffn.forward(h, x, ctx)
+    pro1 = layer.norm1.as_prologue() if layer.mixer.accepts_input_norm else None
+    if pro1 is not None:
+        layer.mixer.forward(x, x, ctx, cache, write_cache, input_norm=pro1)   # the norm runs inside the mixer's product
+    else:
+        h = ctx.ws.get("normed", tuple(x.shape), rt.dtype)
+        layer.norm1.forward(x, h, ctx)
+        layer.mixer.forward(h, x, ctx, cache, write_cache)
+    pro2 = layer.norm2.as_prologue() if layer.ffn.accepts_input_norm else None
+    if pro2 is not None:
+        layer.ffn.forward(x, x, ctx, input_norm=pro2)
+    else:
+        h = ctx.ws.get("normed", tuple(x.shape), rt.dtype)
+        layer.norm2.forward(x, h, ctx)
+        layer.ffn.forward(h, x, ctx)

@@ -57,13 +57,22 @@ class SwiGLU(FeedForward):
             self.w_up = tensors["up_proj"].contiguous()
         self.w_down = tensors["down_proj"].contiguous()
 
-    def forward(self, h, residual, ctx):
+    accepts_input_norm = True
+
+    def forward(self, h, residual, ctx, input_norm=None):
+        """``input_norm`` as for the attention mixer: (weight, eps) when h is the float32 residual."""
         ops = self.rt.ops
         T = h.shape[0]
         act = ctx.ws.get("ffn_act", (T, self.intermediate_size), self.rt.dtype)
-        if self.fused:
+        if self.fused and input_norm is not None:
+            ops.linear_normed(h, input_norm[0], input_norm[1], self.w_gate_up, act, "swiglu", ctx.ws)
+        elif self.fused:
             ops.linear(h, self.w_gate_up, act, "swiglu")
         else:
+            if input_norm is not None:
+                hn = ctx.ws.get("normed", tuple(h.shape), self.rt.dtype)
+                ops.rmsnorm(h, input_norm[0], input_norm[1], hn)
+                h = hn
             up = ctx.ws.get("ffn_up", (T, self.intermediate_size), self.rt.dtype)
             ops.linear(h, self.w_gate, act, "store")
             ops.linear(h, self.w_up, up, "store")

@@ -24,3 +24,7 @@ class RMSNorm(Norm):
     def forward(self, x, out, ctx):
         self.rt.ops.rmsnorm(x, self.weight, self.eps, out)
         return out
+
+    def as_prologue(self):
+        """(weight, eps): what a product needs to apply this norm to its own input rows."""
+        return (self.weight, self.eps)
