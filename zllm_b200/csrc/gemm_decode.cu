@@ -98,32 +98,36 @@ __device__ __forceinline__ void gd_rows(const GemmDecodeParams& p, int tile, int
     }
 }
 
-template <int NT, bool FUSE_NORM>
+// NT: 8-row tiles of x (M <= 8 NT);  RT: 16-row weight tiles per CTA -- x is staged once per CTA
+// and pass, so more tiles per CTA mean less traffic for x (which every CTA reads in full).
+template <int NT, int RT, bool FUSE_NORM>
 __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const GemmDecodeParams p) {
     constexpr int MP = NT * 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* xs_all = reinterpret_cast<bf16*>(smem_raw);                        // [warps][MP][GD_XSTRIDE]
-    float* red = reinterpret_cast<float*>(smem_raw);                         // [warps][16][MP + 1], after the loop
+    float* red = reinterpret_cast<float*>(smem_raw);                         // [warps][RT * 16][MP + 1], after the loop
     __shared__ float ss_part[GD_WARPS][MP];
     __shared__ float inv_rms[MP];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int tile = blockIdx.x;
+    const int tile0 = blockIdx.x * RT;
     const int M = p.M, K = p.K;
-    int ra, rb;
-    gd_rows(p, tile, g, ra, rb);
-    const bool va = ra < p.w_rows, vb = rb < p.w_rows;
-    const bf16* wa = p.w + (size_t)(va ? ra : 0) * K;
-    const bf16* wb = p.w + (size_t)(vb ? rb : 0) * K;
     bf16* xs = xs_all + (size_t)warp * MP * GD_XSTRIDE;
-    float acc[NT][4];
+    float acc[RT][NT][4];
 #pragma unroll
-    for (int i = 0; i < NT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int i = 0; i < NT; ++i) acc[r][i][0] = acc[r][i][1] = acc[r][i][2] = acc[r][i][3] = 0.f;
     float ss[MP];                                                            // FUSE_NORM: this lane's share of sum x^2
 #pragma unroll
     for (int m = 0; m < MP; ++m) ss[m] = 0.f;
 
     uint4 fa[4][2], fb[4][2];
-    auto load_w = [&](int kb) {
+    auto load_w = [&](int r, int kb) {
+        int ra, rb;
+        gd_rows(p, tile0 + r, g, ra, rb);
+        const bool va = ra < p.w_rows, vb = rb < p.w_rows;
+        const bf16* wa = p.w + (size_t)(va ? ra : 0) * K;
+        const bf16* wb = p.w + (size_t)(vb ? rb : 0) * K;
 #pragma unroll
         for (int s = 0; s < 4; ++s)
 #pragma unroll
@@ -134,21 +138,25 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
             }
     };
     const int n_pass = (K + GD_PASS - 1) / GD_PASS;
-    // weights do not depend on the kernel before: fetch the first pass, ask L2 for the rest, then wait
+    // weights do not depend on the kernel before: fetch the first tile of the first pass, ask L2
+    // for the rest of this CTA's weights, then wait
     pdl_trigger();
-    load_w(warp * GD_KW);
-    for (int ps = 1; ps < n_pass; ++ps) {
-        const int k = ps * GD_PASS + warp * GD_KW + t * 64;
-        if (k < K) {
-            if (va) asm volatile("prefetch.global.L2 [%0];" ::"l"(wa + k));
-            if (vb) asm volatile("prefetch.global.L2 [%0];" ::"l"(wb + k));
+    load_w(0, warp * GD_KW);
+    for (int r = 0; r < RT; ++r) {
+        int ra, rb;
+        gd_rows(p, tile0 + r, g, ra, rb);
+        for (int ps = (r == 0 ? 1 : 0); ps < n_pass; ++ps) {
+            const int k = ps * GD_PASS + warp * GD_KW + t * 64;
+            if (k < K) {
+                if (ra < p.w_rows) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.w + (size_t)ra * K + k));
+                if (rb < p.w_rows) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.w + (size_t)rb * K + k));
+            }
         }
     }
     pdl_wait();
 
     for (int ps = 0; ps < n_pass; ++ps) {
         const int kb = ps * GD_PASS + warp * GD_KW;                          // this warp's 256 k of the pass
-        if (ps > 0) load_w(kb);
         // stage x[0..M)[kb .. kb+256) as bf16; lane takes 8 consecutive k of every row
         const int kx = kb + lane * 8;
         if (FUSE_NORM) {
@@ -194,18 +202,22 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
         }
         __syncwarp();
 #pragma unroll
-        for (int s = 0; s < 4; ++s)
+        for (int r = 0; r < RT; ++r) {
+            if (r > 0 || ps > 0) load_w(r, kb);
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                const uint4 A = fa[s][hf], B = fb[s][hf];
+            for (int s = 0; s < 4; ++s)
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const uint4 X = *reinterpret_cast<const uint4*>(xs + (size_t)(nt * 8 + g) * GD_XSTRIDE + s * 64 +
-                                                                    t * 16 + hf * 8);
-                    gd_mma(acc[nt], A.x, B.x, A.y, B.y, X.x, X.y);
-                    gd_mma(acc[nt], A.z, B.z, A.w, B.w, X.z, X.w);
+                for (int hf = 0; hf < 2; ++hf) {
+                    const uint4 A = fa[s][hf], B = fb[s][hf];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const uint4 X = *reinterpret_cast<const uint4*>(xs + (size_t)(nt * 8 + g) * GD_XSTRIDE +
+                                                                        s * 64 + t * 16 + hf * 8);
+                        gd_mma(acc[r][nt], A.x, B.x, A.y, B.y, X.x, X.y);
+                        gd_mma(acc[r][nt], A.z, B.z, A.w, B.w, X.z, X.w);
+                    }
                 }
-            }
+        }
         __syncwarp();                                                        // the slice is overwritten by the next pass
     }
     // ---- sum the 8 warps' partial tiles (and sums of squares) in warp order ----
@@ -218,13 +230,15 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
     }
     __syncthreads();                                                         // every warp is done with its x slice
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        const int m = nt * 8 + 2 * t;
-        float* r0 = red + ((size_t)warp * 16 + g) * (MP + 1) + m;
-        float* r1 = red + ((size_t)warp * 16 + g + 8) * (MP + 1) + m;
-        r0[0] = acc[nt][0]; r0[1] = acc[nt][1];
-        r1[0] = acc[nt][2]; r1[1] = acc[nt][3];
-    }
+    for (int r = 0; r < RT; ++r)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const int m = nt * 8 + 2 * t;
+            float* r0 = red + ((size_t)warp * RT * 16 + r * 16 + g) * (MP + 1) + m;
+            float* r1 = r0 + 8 * (MP + 1);
+            r0[0] = acc[r][nt][0]; r0[1] = acc[r][nt][1];
+            r1[0] = acc[r][nt][2]; r1[1] = acc[r][nt][3];
+        }
     if (FUSE_NORM && threadIdx.x < MP) {
         float tot = 0.f;
 #pragma unroll
@@ -232,13 +246,17 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
         inv_rms[threadIdx.x] = rsqrtf(tot / (float)K + p.eps);
     }
     __syncthreads();
+    int rt_cur = 0;                                                          // the tile the epilogue is writing
     auto total = [&](int r16, int m) {
         float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < GD_WARPS; ++w) v += red[((size_t)w * 16 + r16) * (MP + 1) + m];
+        for (int w = 0; w < GD_WARPS; ++w) v += red[((size_t)w * RT * 16 + rt_cur * 16 + r16) * (MP + 1) + m];
         return FUSE_NORM ? v * inv_rms[m] : v;
     };
     const int mode = p.mode;
+    for (rt_cur = 0; rt_cur < RT; ++rt_cur) {
+    const int tile = tile0 + rt_cur;
+    if (tile * 16 >= p.w_rows) break;
     if (mode == MODE_STORE || mode == MODE_ADD) {
         for (int i = threadIdx.x; i < 16 * M; i += blockDim.x) {
             const int m = i >> 4, r = i & 15;
@@ -296,19 +314,29 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
             }
         }
     }
+    }   // tiles of the CTA
 }
 
-template <int NT, bool FUSE_NORM>
+template <int NT, int RT, bool FUSE_NORM>
 static int launch_gd(const GemmDecodeParams& p, cudaStream_t s) {
     constexpr int MP = NT * 8;
     size_t smem = (size_t)GD_WARPS * MP * GD_XSTRIDE * sizeof(bf16);
-    const size_t red = (size_t)GD_WARPS * 16 * (MP + 1) * sizeof(float);
+    const size_t red = (size_t)GD_WARPS * RT * 16 * (MP + 1) * sizeof(float);
     if (red > smem) smem = red;
-    auto kern = gemm_decode_kernel<NT, FUSE_NORM>;
+    auto kern = gemm_decode_kernel<NT, RT, FUSE_NORM>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const int tiles = (p.w_rows + 15) / 16;
-    return launch_pdl(kern, dim3(tiles), dim3(GD_WARPS * 32), smem, s, p);
+    return launch_pdl(kern, dim3((tiles + RT - 1) / RT), dim3(GD_WARPS * 32), smem, s, p);
+}
+
+template <int NT, bool FUSE_NORM>
+static int launch_gd_rt(const GemmDecodeParams& p, cudaStream_t s) {
+    // more weight rows per CTA while about two CTAs per SM remain: depends on the sizes only
+    const int tiles = (p.w_rows + 15) / 16;
+    if (tiles >= 4 * 256) return launch_gd<NT, 4, FUSE_NORM>(p, s);
+    if (tiles >= 2 * 256) return launch_gd<NT, 2, FUSE_NORM>(p, s);
+    return launch_gd<NT, 1, FUSE_NORM>(p, s);
 }
 
 // See GemmDecodeParams.  M <= 16; K % 8 == 0; 16-byte aligned operands.
@@ -333,6 +361,6 @@ ZLLM_API int zllm_gemm_decode(const void* x, const void* norm_w, int norm_w_bf16
     p.max_blocks = max_blocks; p.bs = bs; p.store = store;
     cudaStream_t s = (cudaStream_t)stream;
     const bool fuse = norm_w != nullptr;
-    if (M <= 8) return fuse ? launch_gd<1, true>(p, s) : launch_gd<1, false>(p, s);
-    return fuse ? launch_gd<2, true>(p, s) : launch_gd<2, false>(p, s);
+    if (M <= 8) return fuse ? launch_gd_rt<1, true>(p, s) : launch_gd_rt<1, false>(p, s);
+    return fuse ? launch_gd_rt<2, true>(p, s) : launch_gd_rt<2, false>(p, s);
 }
