@@ -114,6 +114,25 @@ def test_long_decoding_one_by_one(tmp_path, name, dtype):
     r.cache.check_integrity()
 
 
+@pytest.mark.parametrize("graphs", [True, False])
+def test_decode_step_beyond_one_split_with_and_without_graphs(tmp_path, graphs):
+    """Contexts of several hundred keys (more than one split of the decode kernel), decoded by
+    ``decode_step`` with captured graphs and with plain launches."""
+    d = make_model_dir(tmp_path, "C", "bfloat16")
+    cfg, w = P.read_model_dir(d)
+    toks = random_prompt(1536, 700, 17)
+    ref = P.forward_all_positions(cfg, w, toks)
+    bound = BF16_MAX_OF_SCALE * float(ref.abs().max())
+    r = gpu_runner(d, "C", "bfloat16", num_blocks=50, max_rows=1024, graphs=graphs)
+    s = r.admit()
+    r.step([StepEntry(s, toks[:600], ())])
+    for i in range(600, 700, 7):
+        for j in range(i, min(i + 7, 700)):
+            r.decode_step([s], [toks[j]], [0.0], [0])
+            err = float((r.last_logits[0].float().cpu() - ref[j]).abs().max())
+            assert err <= bound, f"position {j}: {err:.3e} > {bound:.3e}"
+
+
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_of_a_sequence(tmp_path, name, dtype):

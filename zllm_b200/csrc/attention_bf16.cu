@@ -102,34 +102,18 @@ __device__ __forceinline__ void gather_tile(bf16* __restrict__ tile, const bf16*
     }
 }
 
-// One block of NB keys (NB multiple of 16) against the warp's 16 rows.
-//   qf      : A fragments of the 16 x HD query tile
-//   ks, vs  : shared tiles [NB][HD + 8] of the block's keys / values
+// After the scores: masking, running softmax in float32, and O += P V with V from a shared tile.
+//   s       : raw scores q.k of the warp's 16 rows against the block's NB keys (C fragments)
+//   vs      : shared tile [NB][HD + 8] of the block's values
 //   key0    : absolute index of the block's first key
 //   lo_r/hi_r : per row (index 0: row g, 1: row g + 8) the visible key range [lo, hi]
-template <int HD, int NB, bool MASKED>
-__device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], const bf16* __restrict__ ks,
-                                             const bf16* __restrict__ vs, int key0, const int (&lo_r)[2],
-                                             const int (&hi_r)[2], float scale, TileState<HD>& st, int lane) {
+template <int HD, int NB, bool MASKED, bool WAIT_V = false>
+__device__ __forceinline__ void softmax_pv(float (&s)[NB / 8][4], const bf16* __restrict__ vs, int key0,
+                                           const int (&lo_r)[2], const int (&hi_r)[2], float scale,
+                                           TileState<HD>& st, int lane) {
     constexpr int STR = HD + 8;
     const int t = lane & 3;
-    float s[NB / 8][4];
-#pragma unroll
-    for (int j = 0; j < NB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    // S = Q K^T: B fragments of K by ldmatrix (rows = keys, 8 x 8 tiles along dims)
     const int lrow = lane & 7, lmat = lane >> 3;
-#pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
-#pragma unroll
-        for (int j = 0; j < NB / 8; j += 2) {
-            // matrices: (keys 8j.., dims 16kk..), (keys 8j.., dims 16kk+8..), (keys 8j+8.., dims 16kk..), (.., +8)
-            unsigned b[4];
-            const bf16* p = ks + (size_t)(8 * j + (lmat >> 1) * 8 + lrow) * STR + 16 * kk + (lmat & 1) * 8;
-            ldmatrix_x4(b, p);
-            mma16816(s[j], qf[kk], b[0], b[1]);
-            mma16816(s[j + 1], qf[kk], b[2], b[3]);
-        }
-    }
     // running max in the scaled log2 domain (scale > 0 holds log2(e): max commutes with it);
     // only blocks that touch a row's edge of visibility pay for the masking
     float mx[2] = {-INFINITY, -INFINITY};
@@ -183,6 +167,10 @@ __device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], c
         st.o[i][0] *= corr[0]; st.o[i][1] *= corr[0];
         st.o[i][2] *= corr[1]; st.o[i][3] *= corr[1];
     }
+    if (WAIT_V) {                        // the warp's own async copies of V must have landed
+        __pipeline_wait_prior(0);
+        __syncwarp();
+    }
     // O += P V: A fragments from the probabilities, B fragments of V by transposed ldmatrix
 #pragma unroll
     for (int kk = 0; kk < NB / 16; ++kk) {
@@ -201,6 +189,37 @@ __device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], c
             mma16816(st.o[i + 1], pa, b[2], b[3]);
         }
     }
+}
+
+// One block of NB keys (NB multiple of 16) against the warp's 16 rows.
+//   qf      : A fragments of the 16 x HD query tile
+//   ks, vs  : shared tiles [NB][HD + 8] of the block's keys / values
+//   key0    : absolute index of the block's first key
+//   lo_r/hi_r : per row (index 0: row g, 1: row g + 8) the visible key range [lo, hi]
+template <int HD, int NB, bool MASKED>
+__device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], const bf16* __restrict__ ks,
+                                             const bf16* __restrict__ vs, int key0, const int (&lo_r)[2],
+                                             const int (&hi_r)[2], float scale, TileState<HD>& st, int lane) {
+    constexpr int STR = HD + 8;
+    const int t = lane & 3;
+    float s[NB / 8][4];
+#pragma unroll
+    for (int j = 0; j < NB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    // S = Q K^T: B fragments of K by ldmatrix (rows = keys, 8 x 8 tiles along dims)
+    const int lrow = lane & 7, lmat = lane >> 3;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int j = 0; j < NB / 8; j += 2) {
+            // matrices: (keys 8j.., dims 16kk..), (keys 8j.., dims 16kk+8..), (keys 8j+8.., dims 16kk..), (.., +8)
+            unsigned b[4];
+            const bf16* p = ks + (size_t)(8 * j + (lmat >> 1) * 8 + lrow) * STR + 16 * kk + (lmat & 1) * 8;
+            ldmatrix_x4(b, p);
+            mma16816(s[j], qf[kk], b[0], b[1]);
+            mma16816(s[j + 1], qf[kk], b[2], b[3]);
+        }
+    }
+    softmax_pv<HD, NB, MASKED>(s, vs, key0, lo_r, hi_r, scale, st, lane);
 }
 
 // ------------------------------------------------------------------------------------ decode
@@ -225,19 +244,24 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int G = nq / nkv;
     const int* trow = table + (size_t)slot * max_blocks;
-    bf16* ks = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * 2 * DEC_BLOCK * STR;
-    bf16* vs = ks + DEC_BLOCK * STR;
-    // query fragments: row g of the tile is query head kvh * G + g (rows beyond the group are zero)
-    unsigned qf[HD / 16][4];
+    constexpr int NB = HD <= 64 ? 64 : 32;                  // keys per warp iteration
+    constexpr int NMMA = HD / 16;                            // tensor-core steps along the head
+    bf16* vs = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * NB * STR;
+    // Keys go straight from global memory into B fragments: the order of dims inside a
+    // tensor-core step is free as long as q uses the same one, so lane (g, t) takes the 8
+    // consecutive dims 32 p + 8 t of key g (two steps' worth) with one 16-byte load.  A last
+    // odd step (head sizes 16, 48, ...) takes dims base + 4 t with an 8-byte load.
+    // Query fragments in that same order: row g of the tile is query head kvh * G + g.
+    unsigned qf[NMMA][4];
     {
         const bf16* qrow = qkv + (size_t)row * (nq + 2 * nkv) * HD + (size_t)kvh * G * HD;
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-            const int d = 16 * kk + 2 * t;
-            qf[kk][0] = g < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)g * HD + d) : 0u;
-            qf[kk][1] = g + 8 < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)(g + 8) * HD + d) : 0u;
-            qf[kk][2] = g < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)g * HD + d + 8) : 0u;
-            qf[kk][3] = g + 8 < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)(g + 8) * HD + d + 8) : 0u;
+        for (int mm = 0; mm < NMMA; ++mm) {
+            const int d = (mm < 2 * (HD / 32)) ? 32 * (mm >> 1) + 8 * t + 4 * (mm & 1) : 32 * (HD / 32) + 4 * t;
+            qf[mm][0] = g < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)g * HD + d) : 0u;
+            qf[mm][1] = g + 8 < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)(g + 8) * HD + d) : 0u;
+            qf[mm][2] = g < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)g * HD + d + 2) : 0u;
+            qf[mm][3] = g + 8 < G ? *reinterpret_cast<const unsigned*>(qrow + (size_t)(g + 8) * HD + d + 2) : 0u;
         }
     }
     TileState<HD> st;
@@ -245,19 +269,47 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
     const int lo_r[2] = {lo, lo}, hi_r[2] = {pos, pos};
     const int w_first = k_first + warp * (SPLIT_KEYS / DEC_WARPS);
 #pragma unroll 1
-    for (int it = 0; it < SPLIT_KEYS / DEC_WARPS / DEC_BLOCK; ++it) {
-        const int key0 = w_first + it * DEC_BLOCK;
+    for (int it = 0; it < SPLIT_KEYS / DEC_WARPS / NB; ++it) {
+        const int key0 = w_first + it * NB;
         if (key0 > pos) break;                               // warp-uniform
-        gather_tile<HD, DEC_BLOCK, 32>(ks, k_pages, trow, key0, pos + 1, bs, bs_shift, nkv, kvh, lane);
-        gather_tile<HD, DEC_BLOCK, 32>(vs, v_pages, trow, key0, pos + 1, bs, bs_shift, nkv, kvh, lane);
+        unsigned kf[NB / 8][NMMA][2];
+#pragma unroll
+        for (int j = 0; j < NB / 8; ++j) {
+            const int key = key0 + 8 * j + g;
+            const bf16* krow = nullptr;
+            if (key <= pos) {
+                const int blk = bs_shift >= 0 ? (key >> bs_shift) : key / bs;
+                const int off = bs_shift >= 0 ? (key & (bs - 1)) : key - blk * bs;
+                const int page = trow[blk];
+                if (page >= 0) krow = k_pages + (((size_t)page * nkv + kvh) * bs + off) * HD;
+            }
+#pragma unroll
+            for (int pq = 0; pq < HD / 32; ++pq) {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (krow != nullptr) v = *reinterpret_cast<const uint4*>(krow + 32 * pq + 8 * t);
+                kf[j][2 * pq][0] = v.x; kf[j][2 * pq][1] = v.y;
+                kf[j][2 * pq + 1][0] = v.z; kf[j][2 * pq + 1][1] = v.w;
+            }
+            if (HD % 32) {
+                uint2 v = make_uint2(0, 0);
+                if (krow != nullptr) v = *reinterpret_cast<const uint2*>(krow + 32 * (HD / 32) + 4 * t);
+                kf[j][NMMA - 1][0] = v.x; kf[j][NMMA - 1][1] = v.y;
+            }
+        }
+        gather_tile<HD, NB, 32>(vs, v_pages, trow, key0, pos + 1, bs, bs_shift, nkv, kvh, lane);
         __pipeline_commit();
-        __pipeline_wait_prior(0);
-        __syncwarp();
-        if (key0 >= lo && key0 + DEC_BLOCK - 1 <= pos)
-            attend_block<HD, DEC_BLOCK, false>(qf, ks, vs, key0, lo_r, hi_r, scale, st, lane);
+        float sc[NB / 8][4];
+#pragma unroll
+        for (int j = 0; j < NB / 8; ++j) {
+            sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
+#pragma unroll
+            for (int mm = 0; mm < NMMA; ++mm) mma16816(sc[j], qf[mm], kf[j][mm][0], kf[j][mm][1]);
+        }
+        if (key0 >= lo && key0 + NB - 1 <= pos)
+            softmax_pv<HD, NB, false, true>(sc, vs, key0, lo_r, hi_r, scale, st, lane);
         else
-            attend_block<HD, DEC_BLOCK, true>(qf, ks, vs, key0, lo_r, hi_r, scale, st, lane);
-        __syncwarp();                                        // tile is reused by the next iteration
+            softmax_pv<HD, NB, true, true>(sc, vs, key0, lo_r, hi_r, scale, st, lane);
+        __syncwarp();                                        // the V tile is reused by the next iteration
     }
     // merge the warps' partials in warp order
     __syncthreads();                                         // all warps are done with their K/V tiles
@@ -338,7 +390,7 @@ static int launch_decode(const void* qkv, void* out, const int* rows, int n_rows
                          int max_blocks, int bs, int nq, int nkv, float scale, int window, float* part_o,
                          float* part_ml, int n_splits, int max_splits, cudaStream_t s) {
     constexpr int STR = HD + 8;
-    size_t smem = (size_t)DEC_WARPS * 2 * DEC_BLOCK * STR * sizeof(bf16);
+    size_t smem = (size_t)DEC_WARPS * (HD <= 64 ? 64 : 32) * STR * sizeof(bf16);
     const size_t merge = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
     if (merge > smem) smem = merge;
     auto kern = decode_split_kernel<HD>;

@@ -200,6 +200,8 @@ class ModelRunner:
         if use_graph:
             g["graph"].replay()
         else:
+            g["ctx"].max_context = max_ctx          # no captured shape to honour: size the step as it is
+            g["ctx"].fixed_splits = 0
             self._decode_body(g)
         for e, s in zip(entries, starts):
             self.cache.advance(e.slot, s + 1)
