@@ -201,7 +201,6 @@ __device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], c
                                              const bf16* __restrict__ vs, int key0, const int (&lo_r)[2],
                                              const int (&hi_r)[2], float scale, TileState<HD>& st, int lane) {
     constexpr int STR = HD + 8;
-    const int t = lane & 3;
     float s[NB / 8][4];
 #pragma unroll
     for (int j = 0; j < NB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -556,4 +555,78 @@ ZLLM_API int zllm_attention_prefill_bf16(const void* qkv, void* out, const int* 
     cudaStream_t s = (cudaStream_t)stream;
     DISPATCH_HD(hd, (launch_prefill<H_>(qkv, out, tiles, n_tiles, k_pages, v_pages, table, max_blocks, bs, nq, nkv,
                                         scale, window, s)))
+}
+
+// ------------------------------------------------------------------------------------ no-alloc variant
+// The decode kernels above with their scratch in a fixed array inside the library, for callers
+// that cannot allocate (see attention_noalloc.h, which has the full contract).
+#include "attention_noalloc.h"
+#include <stdio.h>
+
+// Per-split partials of the last call: [rows][nq][n_splits][hd] accumulators followed by
+// [rows][nq][n_splits][2] (max, sum).  In host code this name is only a handle: the device
+// address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) float g_noalloc_scratch[ZLLM_NOALLOC_SCRATCH_FLOATS];
+
+#define NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_ptr[NOALLOC_MAX_DEVICES];     // device address of the array, per device
+
+static void noalloc_msg(char* err, int err_len, const char* text) {
+    if (err != nullptr && err_len > 0) snprintf(err, (size_t)err_len, "%s", text);
+}
+
+ZLLM_API int zllm_attention_decode_bf16_noalloc(const void* qkv, void* out, const int* rows, int n_rows,
+                                                const int* positions, const int* row_slot, const void* k_pages,
+                                                const void* v_pages, const int* table, int max_blocks, int bs, int nq,
+                                                int nkv, int hd, float scale, int window, int n_splits, void* stream,
+                                                char* err, int err_len) {
+    if (n_rows <= 0) return 0;
+    if (nkv <= 0 || nq <= 0 || nq % nkv || nq / nkv > 16 || n_splits <= 0 || n_splits > 65535 || nkv > 65535 ||
+        hd % 16 || hd < 16 || hd > 128 || !(scale > 0.f)) {
+        noalloc_msg(err, err_len, "attention_decode_noalloc: head size must be 16..128 in steps of 16, nq a multiple "
+                                  "of nkv with at most 16 query heads per kv head, scale > 0, n_splits in 1..65535");
+        return ZLLM_ERR_UNSUPPORTED;
+    }
+    const unsigned long long need = (unsigned long long)n_rows * nq * n_splits * (hd + 2);
+    if (need > (unsigned long long)ZLLM_NOALLOC_SCRATCH_FLOATS) {
+        if (err != nullptr && err_len > 0)
+            snprintf(err, (size_t)err_len,
+                     "attention_decode_noalloc: rows * nq * n_splits * (hd + 2) = %llu floats exceeds the built-in "
+                     "scratch of %d floats; use fewer rows per call or the entry point that takes scratch buffers",
+                     need, ZLLM_NOALLOC_SCRATCH_FLOATS);
+        return ZLLM_NOALLOC_TOO_LARGE;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { noalloc_msg(err, err_len, cudaGetErrorString(e)); return (int)e; }
+    if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) {
+        noalloc_msg(err, err_len, "attention_decode_noalloc: device index beyond 63");
+        return ZLLM_ERR_UNSUPPORTED;
+    }
+    float* scratch = g_noalloc_ptr[dev];
+    if (scratch == nullptr) {
+        // once per device, with that device current: the array's address on THIS device
+        e = cudaGetSymbolAddress((void**)&scratch, g_noalloc_scratch);
+        if (e != cudaSuccess || scratch == nullptr) {
+            noalloc_msg(err, err_len, e != cudaSuccess ? cudaGetErrorString(e) : "no address for the scratch array");
+            return e != cudaSuccess ? (int)e : ZLLM_ERR_UNSUPPORTED;
+        }
+        g_noalloc_ptr[dev] = scratch;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)n_rows * nq * n_splits * hd;
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc;
+    switch (hd) {
+        case 16: rc = launch_decode<16>(qkv, out, rows, n_rows, positions, row_slot, k_pages, v_pages, table, max_blocks, bs, nq, nkv, scale, window, part_o, part_ml, n_splits, n_splits, s); break;
+        case 32: rc = launch_decode<32>(qkv, out, rows, n_rows, positions, row_slot, k_pages, v_pages, table, max_blocks, bs, nq, nkv, scale, window, part_o, part_ml, n_splits, n_splits, s); break;
+        case 48: rc = launch_decode<48>(qkv, out, rows, n_rows, positions, row_slot, k_pages, v_pages, table, max_blocks, bs, nq, nkv, scale, window, part_o, part_ml, n_splits, n_splits, s); break;
+        case 64: rc = launch_decode<64>(qkv, out, rows, n_rows, positions, row_slot, k_pages, v_pages, table, max_blocks, bs, nq, nkv, scale, window, part_o, part_ml, n_splits, n_splits, s); break;
+        case 80: rc = launch_decode<80>(qkv, out, rows, n_rows, positions, row_slot, k_pages, v_pages, table, max_blocks, bs, nq, nkv, scale, window, part_o, part_ml, n_splits, n_splits, s); break;
+        case 96: rc = launch_decode<96>(qkv, out, rows, n_rows, positions, row_slot, k_pages, v_pages, table, max_blocks, bs, nq, nkv, scale, window, part_o, part_ml, n_splits, n_splits, s); break;
+        case 112: rc = launch_decode<112>(qkv, out, rows, n_rows, positions, row_slot, k_pages, v_pages, table, max_blocks, bs, nq, nkv, scale, window, part_o, part_ml, n_splits, n_splits, s); break;
+        default: rc = launch_decode<128>(qkv, out, rows, n_rows, positions, row_slot, k_pages, v_pages, table, max_blocks, bs, nq, nkv, scale, window, part_o, part_ml, n_splits, n_splits, s); break;
+    }
+    if (rc != 0) noalloc_msg(err, err_len, rc == ZLLM_ERR_UNSUPPORTED ? "sizes not taken by the kernel" : cudaGetErrorString((cudaError_t)rc));
+    return rc;
 }
