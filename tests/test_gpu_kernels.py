@@ -266,6 +266,16 @@ def test_sampling_kernels(ops):
     for r in range(6):
         v, i = P.topk_desc(lg[r], 64)
         assert idx[r].cpu().tolist() == i and vals[r].cpu().tolist() == v
+    # a large vocabulary: many blocks per row, the last one to arrive picks the winner
+    big = torch.randn(3, 40003, generator=g)
+    big[0, 39999] = big[0, 123] = 11.0
+    tb, sb = torch.tensor([0.0, 0.9, 0.0]), torch.tensor([0, 77, 5], dtype=torch.int32)
+    ob = torch.zeros(3, dtype=torch.int32, device=DEV)
+    for _ in range(2):                          # twice: the arrival counters must be back at zero
+        ops.sample(big.to(DEV), tb.to(DEV), sb.to(DEV), ob)
+        gb = ob.cpu().tolist()
+        assert gb[0] == 123 and gb[2] == int(big[2].argmax())
+        assert gb[1] == P.gumbel_sample(big[1], 0.9, 77)
     small = torch.tensor([[1.0, 5.0, 5.0]])
     v3 = torch.zeros(1, 5, device=DEV); i3 = torch.zeros(1, 5, dtype=torch.int32, device=DEV)
     ops.topk(small.to(DEV), 5, v3, i3)

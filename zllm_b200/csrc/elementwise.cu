@@ -50,15 +50,64 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict
     for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_f32<OT>(xr[i] * inv * to_f32(w[i]));
 }
 
+// The same with 16-byte loads and the row kept in registers (H % 4 == 0, H <= 256 * 4 * RV).
+template <typename WT, typename OT, int RV>
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const WT* __restrict__ w,
+                                                          OT* __restrict__ y, int H, float eps) {
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * H);
+    const int n4 = H >> 2;
+    float4 v[RV];
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < RV; ++r) {
+        const int i = threadIdx.x + r * 256;
+        v[r] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += v[r].x * v[r].x + v[r].y * v[r].y + v[r].z * v[r].z + v[r].w * v[r].w;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    OT* yr = y + (size_t)blockIdx.x * H;
+#pragma unroll
+    for (int r = 0; r < RV; ++r) {
+        const int i = threadIdx.x + r * 256;
+        if (i >= n4) continue;
+        const WT* wp = w + 4 * i;
+        const float o0 = v[r].x * inv * to_f32(wp[0]), o1 = v[r].y * inv * to_f32(wp[1]);
+        const float o2 = v[r].z * inv * to_f32(wp[2]), o3 = v[r].w * inv * to_f32(wp[3]);
+        if (sizeof(OT) == 2) {
+            __nv_bfloat162 a = __floats2bfloat162_rn(o0, o1), b = __floats2bfloat162_rn(o2, o3);
+            uint2 pk;
+            pk.x = *reinterpret_cast<unsigned*>(&a);
+            pk.y = *reinterpret_cast<unsigned*>(&b);
+            *reinterpret_cast<uint2*>(yr + 4 * i) = pk;
+        } else {
+            *reinterpret_cast<float4*>(yr + 4 * i) = make_float4(o0, o1, o2, o3);
+        }
+    }
+}
+
+template <typename WT, typename OT>
+static int launch_rmsnorm(const float* x, const void* w, void* y, int T, int H, float eps, cudaStream_t s) {
+    const bool vec = (H % 4 == 0) && (((uintptr_t)x | (uintptr_t)y) % 16 == 0);
+    if (vec && H <= 256 * 4 * 2)
+        return launch_pdl(rmsnorm_vec_kernel<WT, OT, 2>, dim3(T), dim3(256), 0, s, x, (const WT*)w, (OT*)y, H, eps);
+    if (vec && H <= 256 * 4 * 8)
+        return launch_pdl(rmsnorm_vec_kernel<WT, OT, 8>, dim3(T), dim3(256), 0, s, x, (const WT*)w, (OT*)y, H, eps);
+    const int th = H >= 1024 ? 256 : 128;
+    return launch_pdl(rmsnorm_kernel<WT, OT>, dim3(T), dim3(th), 0, s, x, (const WT*)w, (OT*)y, H, eps);
+}
+
 ZLLM_API int zllm_rmsnorm(const float* x, const void* w, void* y, int T, int H, float eps, int w_bf16, int out_bf16,
                           void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int th = H >= 1024 ? 256 : 128;
-    if (w_bf16 && out_bf16) return launch_pdl(rmsnorm_kernel<bf16, bf16>, dim3(T), dim3(th), 0, s, x, (const bf16*)w, (bf16*)y, H, eps);
-    if (w_bf16) return launch_pdl(rmsnorm_kernel<bf16, float>, dim3(T), dim3(th), 0, s, x, (const bf16*)w, (float*)y, H, eps);
-    if (out_bf16) return launch_pdl(rmsnorm_kernel<float, bf16>, dim3(T), dim3(th), 0, s, x, (const float*)w, (bf16*)y, H, eps);
-    return launch_pdl(rmsnorm_kernel<float, float>, dim3(T), dim3(th), 0, s, x, (const float*)w, (float*)y, H, eps);
+    if (w_bf16 && out_bf16) return launch_rmsnorm<bf16, bf16>(x, w, y, T, H, eps, s);
+    if (w_bf16) return launch_rmsnorm<bf16, float>(x, w, y, T, H, eps, s);
+    if (out_bf16) return launch_rmsnorm<float, bf16>(x, w, y, T, H, eps, s);
+    return launch_rmsnorm<float, float>(x, w, y, T, H, eps, s);
 }
 
 // ---------------------------------------------------------------- silu * up
@@ -147,6 +196,73 @@ __global__ void rope_kv_store_kernel(AT* __restrict__ qkv, const int* __restrict
     }
 }
 
+// bfloat16, half-split pairing over the whole head, head_dim % 16 == 0: 16-byte accesses.
+// One thread rotates 8 pairs (j..j+7, j+half..j+half+7) of one head, or copies 8 values of v.
+__global__ void __launch_bounds__(256) rope_kv_store_vec_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions,
+                                                                const int* __restrict__ row_slot,
+                                                                const float* __restrict__ cos_t,
+                                                                const float* __restrict__ sin_t,
+                                                                bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
+                                                                const int* __restrict__ table, int max_blocks, int bs,
+                                                                int nq, int nkv, int hd, int store) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int slot = row_slot[t];
+    if (slot < 0) return;
+    const int pos = positions[t];
+    bf16* row = qkv + (size_t)t * (nq + 2 * nkv) * hd;
+    const int half = hd >> 1;
+    const int per_head = half >> 3;                                  // 8-pair groups per rotated head
+    size_t kv_base = 0;
+    bool have_page = false;
+    if (store) {
+        const int page = table[(size_t)slot * max_blocks + pos / bs];
+        have_page = page >= 0;
+        kv_base = ((size_t)(have_page ? page : 0) * nkv * bs + (size_t)(pos % bs)) * hd;   // + kvh * bs * hd
+    }
+    const int n_rot = (nq + nkv) * per_head;
+    const int n_v = store ? nkv * (hd >> 3) : 0;
+    for (int i = threadIdx.x; i < n_rot + n_v; i += blockDim.x) {
+        if (i < n_rot) {
+            const int head = i / per_head, j = (i - head * per_head) * 8;
+            bf16* h = row + (size_t)head * hd;
+            uint4 ra = *reinterpret_cast<uint4*>(h + j), rb = *reinterpret_cast<uint4*>(h + j + half);
+            float c[8], sn[8];
+            if (cos_t != nullptr) {
+                const float4* cp = reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j);
+                const float4* sp = reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j);
+                const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+                c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+                sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { c[e] = 1.f; sn[e] = 0.f; }
+            }
+            __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&ra);
+            __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&rb);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 a = __bfloat1622float2(pa[e]), b = __bfloat1622float2(pb[e]);
+                pa[e] = __floats2bfloat162_rn(a.x * c[2 * e] - b.x * sn[2 * e], a.y * c[2 * e + 1] - b.y * sn[2 * e + 1]);
+                pb[e] = __floats2bfloat162_rn(a.x * sn[2 * e] + b.x * c[2 * e], a.y * sn[2 * e + 1] + b.y * c[2 * e + 1]);
+            }
+            *reinterpret_cast<uint4*>(h + j) = ra;
+            *reinterpret_cast<uint4*>(h + j + half) = rb;
+            if (head >= nq && have_page) {
+                bf16* dst = k_pages + kv_base + (size_t)(head - nq) * bs * hd;
+                *reinterpret_cast<uint4*>(dst + j) = ra;
+                *reinterpret_cast<uint4*>(dst + j + half) = rb;
+            }
+        } else if (have_page) {
+            const int vi = i - n_rot;
+            const int kvh = vi / (hd >> 3), d = (vi - kvh * (hd >> 3)) * 8;
+            const uint4 v = *reinterpret_cast<const uint4*>(row + (size_t)(nq + nkv + kvh) * hd + d);
+            *reinterpret_cast<uint4*>(v_pages + kv_base + (size_t)kvh * bs * hd + d) = v;
+        }
+    }
+}
+
 ZLLM_API int zllm_rope_kv_store(void* qkv, const int* positions, const int* row_slot, const float* cos_t,
                                 const float* sin_t, int rot_dim, int interleaved, void* k_pages, void* v_pages,
                                 const int* table, int max_blocks, int bs, int T, int nq, int nkv, int hd, int store,
@@ -154,6 +270,10 @@ ZLLM_API int zllm_rope_kv_store(void* qkv, const int* positions, const int* row_
     if (T <= 0) return 0;
     if (rot_dim > hd || (rot_dim & 1)) return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
+    if (is_bf16 && !interleaved && hd % 16 == 0 && (cos_t == nullptr || rot_dim == hd) && ((uintptr_t)qkv % 16 == 0) &&
+        (!store || (((uintptr_t)k_pages | (uintptr_t)v_pages) % 16 == 0)))
+        return launch_pdl(rope_kv_store_vec_kernel, dim3(T), dim3(256), 0, s, (bf16*)qkv, positions, row_slot, cos_t,
+                          sin_t, (bf16*)k_pages, (bf16*)v_pages, table, max_blocks, bs, nq, nkv, hd, store);
     if (is_bf16)
         return launch_pdl(rope_kv_store_kernel<bf16>, dim3(T), dim3(256), 0, s, (bf16*)qkv, positions, row_slot, cos_t,
                           sin_t, rot_dim, interleaved, (bf16*)k_pages, (bf16*)v_pages, table, max_blocks, bs, nq, nkv,

@@ -71,10 +71,86 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
     }
 }
 
+// The same over a large vocabulary with many blocks per row: each block scans one chunk and
+// writes its best (value, index); the block that arrives last for a row (a counter in global
+// memory) picks the best of the chunks and resets the counter.  "Best" is the largest value,
+// the lowest index among equals, which does not depend on the order of arrival.
+#define SAMPLE_CHUNKS 64
+__global__ void __launch_bounds__(256) sample_chunks_kernel(const float* __restrict__ logits,
+                                                            const float* __restrict__ temps,
+                                                            const unsigned* __restrict__ seeds, int* __restrict__ out,
+                                                            int V, float* __restrict__ part_v, int* __restrict__ part_i,
+                                                            unsigned* __restrict__ counters) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ bool last;
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x, chunk = blockIdx.y;
+    const int per = (V + SAMPLE_CHUNKS - 1) / SAMPLE_CHUNKS;
+    const int lo = chunk * per, hi = min(V, lo + per);
+    const float* lg = logits + (size_t)row * V;
+    const float temp = temps ? temps[row] : 0.f;
+    const bool greedy = !(temp > 0.f);
+    const float inv_t = greedy ? 1.f : 1.f / temp;
+    const unsigned seed = seeds ? seeds[row] : 0u;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int k = lo + threadIdx.x; k < hi; k += blockDim.x) {
+        float v = lg[k];
+        if (!greedy) v = v * inv_t + (-logf(-logf(rand01(seed, (unsigned)k))));
+        if (better(v, k, bv, bi)) { bv = v; bi = k; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) { sv[w] = bv; si[w] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int q = 1; q < 8; ++q)
+            if (better(sv[q], si[q], bv, bi)) { bv = sv[q]; bi = si[q]; }
+        part_v[(size_t)row * SAMPLE_CHUNKS + chunk] = bv;
+        part_i[(size_t)row * SAMPLE_CHUNKS + chunk] = bi;
+        __threadfence();
+        last = atomicAdd(&counters[row], 1u) == SAMPLE_CHUNKS - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (threadIdx.x < 32) {
+        float v = -INFINITY;
+        int i = 0x7fffffff;
+        for (int c = threadIdx.x; c < SAMPLE_CHUNKS; c += 32) {
+            const float cv = part_v[(size_t)row * SAMPLE_CHUNKS + c];
+            const int ci = part_i[(size_t)row * SAMPLE_CHUNKS + c];
+            if (better(cv, ci, v, i)) { v = cv; i = ci; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+            if (better(ov, oi, v, i)) { v = ov; i = oi; }
+        }
+        if (threadIdx.x == 0) {
+            out[row] = (i == 0x7fffffff) ? 0 : i;
+            counters[row] = 0u;                      // ready for the next call
+        }
+    }
+}
+
+// scratch (may be null: one block per row then): part_v [R][64] float, part_i [R][64] int,
+// counters [R] unsigned, all zero before the first call.
 ZLLM_API int zllm_sample(const float* logits, const float* temps, const unsigned* seeds, int* out, int R, int V,
-                         void* stream) {
+                         float* part_v, int* part_i, unsigned* counters, void* stream) {
     if (R <= 0) return 0;
     if (V <= 0) return ZLLM_ERR_UNSUPPORTED;
+    if (part_v != nullptr && V >= 16384)
+        return launch_pdl(sample_chunks_kernel, dim3(R, SAMPLE_CHUNKS), dim3(256), 0, (cudaStream_t)stream, logits, temps,
+                          seeds, out, V, part_v, part_i, counters);
     return launch_pdl(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, temps, seeds, out, V);
 }
 

@@ -46,6 +46,7 @@ class CudaOps:
             raise BackendError(f"the kernels are built for sm_100a (B200); this device is sm_{major}{minor}")
         self.dtype = torch.bfloat16
         self._libs = {}
+        self._sample_scratch = None
         self.launches = 0
 
     # ------------------------------------------------------------------
@@ -142,6 +143,7 @@ class CudaOps:
         self._check(code, "gemm_plain")
 
     SKINNY_MAX_ROWS = 64
+    SAMPLE_SCRATCH_ROWS = 1024
     DECODE_MAX_ROWS = 16
 
     def _gemm_decode(self, x, norm_w, eps, w, out, mode, M, N, K, rope=None):
@@ -357,8 +359,16 @@ class CudaOps:
             raise BackendError("sample: temps must be float32 [rows]")
         if seeds is not None and (seeds.dtype not in (torch.int32, torch.uint32) or seeds.numel() < R):
             raise BackendError("sample: seeds must be 32-bit [rows]")
+        # scratch of the many-blocks-per-row kernel: made once (captured graphs keep its address);
+        # more rows than it holds use the one-block-per-row kernel
+        if self._sample_scratch is None:
+            n = self.SAMPLE_SCRATCH_ROWS
+            self._sample_scratch = (torch.zeros((n, 64), dtype=torch.float32, device=self.device),
+                                    torch.zeros((n, 64), dtype=torch.int32, device=self.device),
+                                    torch.zeros(n, dtype=torch.int32, device=self.device))
+        sc = self._sample_scratch if R <= self.SAMPLE_SCRATCH_ROWS else (None, None, None)
         code = self.lib("sampling").zllm_sample(_ptr(logits), _ptr(temps), _ptr(seeds), _ptr(out), c_int(R), c_int(V),
-                                                self._stream())
+                                                _ptr(sc[0]), _ptr(sc[1]), _ptr(sc[2]), self._stream())
         self._check(code, "sample")
 
     def advance_decode(self, tok, pos, row_slot, seeds, out, hist, counter):
