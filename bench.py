@@ -249,11 +249,14 @@ def main():
     achieved = step_bytes / (ms_step / 1e3) / 1e9
 
     # ---- end to end through the Python entry point ------------------------------------------
+    # Prompts are prefilled in portions, so the requests start (and would end) decoding a few steps
+    # apart: max_tokens leaves room for that, and the warm-up runs until every request decodes.
+    slack = 4 * B + 8
     for i in range(B):
-        eng.add_request(prompt(CONTEXT - K - W - 2), SamplingParams.greedy(max_tokens=K + W + 1))
+        eng.add_request(prompt(CONTEXT - K - W - slack - 2), SamplingParams.greedy(max_tokens=K + W + slack))
     while eng.scheduler.prefilling or eng.scheduler.waiting:
         eng.step()
-    for _ in range(W - 1):
+    for _ in range(W):
         eng.step()
     torch.cuda.synchronize()
     t1 = time.perf_counter()

@@ -43,6 +43,8 @@ class Engine:
         self.sampler = Sampler(self.runner.ops, self.runner.device, max(ecfg.max_num_seqs, 1))
         self.steps = 0
         self.generated = 0
+        self.overlap = True            # launch the next decode step before reading this one's tokens
+        self._ahead = None             # (requests, handle) of a decode step launched ahead
 
     # ---- requests ------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -60,8 +62,47 @@ class Engine:
         return self.scheduler.has_unfinished()
 
     # ---- one step ----------------------------------------------------------
+    def _can_run_ahead(self, reqs, uncommitted: int) -> bool:
+        """May the step after the one in flight be launched before its tokens are known?  Only in
+        the steady state of decoding: nothing to admit or prefill, the same requests, sampling on
+        the device, and none of them ends by length at the step in flight."""
+        sch = self.scheduler
+        if not self.overlap or sch.waiting or sch.prefilling or sch.preempted or len(reqs) != len(sch.running) \
+                or any(a is not b for a, b in zip(reqs, sch.running)):
+            return False
+        for r in reqs:
+            p = r.params
+            if p.needs_topk or p.needs_full or r.gen_index + uncommitted >= p.max_tokens \
+                    or len(r.tokens) + uncommitted + 1 >= self.runner.max_len:
+                return False
+        return True
+
+    def _commit_ahead(self, reqs, toks):
+        """Commit a step that was launched ahead: rows of requests that ended meanwhile (a stop
+        token in the step before, a cancel) are dropped."""
+        from .scheduler import RUNNING
+        live = [(r, t) for r, t in zip(reqs, toks) if r.state == RUNNING]
+        plan = Plan(decodes=[r for r, _ in live])
+        out = self.scheduler.commit(plan, [t for _, t in live], [])
+        self.steps += 1
+        self.generated += len(out)
+        return out
+
     def step(self):
-        """One scheduler step: [(request id, token, done)] for every token produced."""
+        """One scheduler step: [(request id, token, done)] for every token produced.
+
+        While only decoding, the step after the one whose tokens are being returned is already
+        running on the device when this call returns (its inputs were advanced on the device), so
+        the host's share of a step overlaps the device's.  A request that ends on a stop token
+        has then computed one token too many, which is dropped."""
+        if self._ahead is not None:
+            reqs, handle = self._ahead
+            self._ahead = None
+            nxt = self.runner.decode_continue(handle) if self._can_run_ahead(reqs, 1) else None
+            out = self._commit_ahead(reqs, self.runner.decode_collect(handle))
+            if nxt is not None:
+                self._ahead = (reqs, nxt)
+            return out
         plan = self.scheduler.schedule()
         if plan.empty:
             return []
@@ -71,8 +112,11 @@ class Engine:
         first: List[Optional[int]] = [None] * len(plan.portions)
         if not plan.portions:
             temps = [0.0 if (p.is_greedy or p.needs_topk or p.needs_full) else p.temperature for p in dparams]
-            toks = self.runner.decode_step([r.slot for r in dec], [r.tokens[-1] for r in dec], temps, dseeds)
-            toks = toks.cpu().tolist()
+            handle = self.runner.decode_launch([r.slot for r in dec], [r.tokens[-1] for r in dec], temps, dseeds)
+            nxt = self.runner.decode_continue(handle) if self._can_run_ahead(dec, 1) else None
+            toks = self.runner.decode_collect(handle)
+            if nxt is not None:
+                self._ahead = (list(dec), nxt)
             if any(p.needs_topk or p.needs_full for p in dparams):
                 toks = self.sampler.host_finish(self.runner.last_logits, toks, dparams, dseeds)
             dtoks = toks

@@ -90,6 +90,8 @@ class ModelRunner:
         self.ws = Workspace(self.max_rows, self.device)
         self.buffers = StepBuffers(self.max_rows, self.max_rows, self.device)
         self._graphs: Dict[tuple, dict] = {}
+        self._token_ring = None
+        self._last_key = None
         self.steps = 0
         self.tokens_run = 0
 
@@ -208,7 +210,69 @@ class ModelRunner:
         self.steps += 1
         self.tokens_run += n
         self.last_logits = g["logits"]
+        self._last_key = key
         return g["out"][:n]
+
+    # ---- decode steps whose tokens are read later (host work overlaps the device) ----------
+    def decode_launch(self, slots: Sequence[int], tokens: Sequence[int], temps: Sequence[float],
+                      seeds: Sequence[int]):
+        """``decode_step`` that does not wait: the sampled tokens are copied to pinned host memory
+        behind the step and a handle is returned; ``decode_collect(handle)`` waits and reads them."""
+        out = self.decode_step(slots, tokens, temps, seeds)
+        return self._token_handle(out, len(slots), self._last_key, list(slots))
+
+    def decode_continue(self, handle):
+        """Launch the step AFTER the one in ``handle`` for the same slots without knowing its
+        tokens yet: the step's inputs were advanced on the device (token <- sampled token,
+        position + 1, seed + 0x9E3779B1).  Returns a new handle, or None when that is not
+        possible (another graph bucket would be needed, a page is missing, length limit)."""
+        if not (self.ecfg.cuda_graphs and self.device.type == "cuda"):
+            return None
+        slots = handle["slots"]
+        key = handle["key"]
+        g = self._graphs.get(key)
+        if g is None or g["graph"] is None:
+            return None
+        new_ctx = max(self.cache.length[s] for s in slots) + 1
+        if _bucket(self.ops.decode_splits(new_ctx)) != key[1]:
+            return None
+        if any(self.cache.length[s] + 1 > self.max_len for s in slots):
+            return None
+        if not self.cache.can_fit([(s, self.cache.length[s] + 1) for s in slots]):
+            return None
+        for s in slots:
+            ok = self.cache.ensure(s, self.cache.length[s] + 1)
+            assert ok
+        self.cache.sync_tables()
+        g["graph"].replay()
+        for s in slots:
+            self.cache.advance(s, self.cache.length[s] + 1)
+        self.steps += 1
+        self.tokens_run += len(slots)
+        self.last_logits = g["logits"]
+        return self._token_handle(g["out"][:len(slots)], len(slots), key, slots)
+
+    def _token_handle(self, out, n, key, slots):
+        ring = self._token_ring
+        if ring is None:
+            ring = self._token_ring = [torch.zeros(max(self.ecfg.max_num_seqs, 1), dtype=torch.int32).pin_memory()
+                                       if self.device.type == "cuda" else torch.zeros(self.ecfg.max_num_seqs, dtype=torch.int32)
+                                       for _ in range(4)]
+            self._token_ring_next = 0
+        host = ring[self._token_ring_next % len(ring)]
+        self._token_ring_next += 1
+        host[:n].copy_(out, non_blocking=True)
+        ev = None
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+        return {"host": host, "event": ev, "n": n, "key": key, "slots": slots}
+
+    @staticmethod
+    def decode_collect(handle) -> List[int]:
+        if handle["event"] is not None:
+            handle["event"].synchronize()
+        return handle["host"][:handle["n"]].tolist()
 
     def _decode_body(self, g):
         ctx = g["ctx"]
