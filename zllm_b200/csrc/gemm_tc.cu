@@ -98,31 +98,109 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The epilogue of 32 accumulator columns (n0 + c .. n0 + c + 31) of output row m, from registers.
+__device__ __forceinline__ void tc_epilogue32(const unsigned (&r)[32], void* __restrict__ out, int m, int n0, int c, int N,
+                                              int mode, int out_bf16) {
+    if (mode == MODE_SWIGLU) {
+        // columns c .. c+31 = two groups of (8 gate, 8 up) -> 16 outputs
+        const int o0 = (n0 + c) / 2;
+        float v[16];
+#pragma unroll
+        for (int gi = 0; gi < 2; ++gi)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float g = __uint_as_float(r[gi * 16 + j]);
+                const float u = __uint_as_float(r[gi * 16 + 8 + j]);
+                v[gi * 8 + j] = g / (1.f + expf(-g)) * u;
+            }
+        if (out_bf16) {
+            bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * N + o0;
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+                if (o0 + j >= N) break;
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+                pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+                *reinterpret_cast<uint4*>(o + j) = pk;
+            }
+        } else {
+            float* o = reinterpret_cast<float*>(out) + (size_t)m * N + o0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (o0 + j < N) o[j] = v[j];
+        }
+    } else if (mode == MODE_ADD) {
+        float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n0 + c;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            if (n0 + c + j >= N) break;
+            float4 cur = *reinterpret_cast<float4*>(o + j);
+            cur.x += __uint_as_float(r[j]); cur.y += __uint_as_float(r[j + 1]);
+            cur.z += __uint_as_float(r[j + 2]); cur.w += __uint_as_float(r[j + 3]);
+            *reinterpret_cast<float4*>(o + j) = cur;
+        }
+    } else if (out_bf16) {
+        bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * N + n0 + c;
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            if (n0 + c + j >= N) break;
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+            pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
+            pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
+            *reinterpret_cast<uint4*>(o + j) = pk;
+        }
+    } else {
+        float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n0 + c;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            if (n0 + c + j >= N) break;
+            *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                            __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        }
+    }
+}
+
+// Persistent: a CTA walks the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles
+// fastest, so the CTAs running at the same time share weight panels in L2).  Two accumulators
+// of 256 columns live in TMEM: while the epilogue warps drain one, the MMA warp fills the other.
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                          const __grid_constant__ CUtensorMap map_w,
                                                          void* __restrict__ out, int M, int N, int K, int mode,
-                                                         int out_bf16) {
+                                                         int out_bf16, int tiles_m, int tiles_n) {
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;         // swizzled tiles need 1024-byte alignment
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    const unsigned bars = base + TC_STAGES * TC_STAGE_BYTES;             // full[4], empty[4], accum, tmem slot
+    // barriers: full[4], empty[4], acc_full[2], acc_empty[2]; then the TMEM slot
+    const unsigned bars = base + TC_STAGES * TC_STAGE_BYTES;
+    const unsigned bar_acc_full = bars + 8 * (2 * TC_STAGES);
+    const unsigned bar_acc_empty = bar_acc_full + 16;
     volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(base_ptr + TC_STAGES * TC_STAGE_BYTES + 128);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * TC_BN;                                   // first weight row of the tile
-    const int m0 = blockIdx.y * TC_BM;
     const int k_iters = (K + TC_BK - 1) / TC_BK;
+    const int total_tiles = tiles_m * tiles_n;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
             mbar_init(bars + 8 * s, 1);                                  // full: one arrive (expect_tx) + bytes
             mbar_init(bars + 8 * (TC_STAGES + s), 1);                    // empty: one tcgen05.commit
         }
-        mbar_init(bars + 8 * (2 * TC_STAGES), 1);                        // accumulator ready
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + 8 * b, 1);                          // accumulator complete: one tcgen05.commit
+            mbar_init(bar_acc_empty + 8 * b, 4);                         // accumulator drained: one arrive per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {                                                     // this warp owns the tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(TC_BN) : "memory");
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(2 * TC_BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -134,23 +212,23 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             bool ok = true;
-            int issued = 0;
-            for (int it = 0; it < k_iters && ok; ++it) {
-                const int s = it % TC_STAGES;
-                const unsigned ph = (it / TC_STAGES) & 1;
-                ok = mbar_wait(bars + 8 * (TC_STAGES + s), ph ^ 1, 0);  // stage is free
-                if (!ok) break;
-                const unsigned full = bars + 8 * s;
-                mbar_expect_tx(full, TC_STAGE_BYTES);
-                const unsigned a_dst = base + s * TC_STAGE_BYTES;
-                tma_load_2d(a_dst, &map_x, it * TC_BK, m0, full);
-                tma_load_2d(a_dst + TC_A_BYTES, &map_w, it * TC_BK, n0, full);
-                issued = it + 1;
+            int g = 0;                                                   // k steps issued over all tiles
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TC_BN;
+                for (int it = 0; it < k_iters; ++it, ++g) {
+                    const int s = g % TC_STAGES;
+                    ok = mbar_wait(bars + 8 * (TC_STAGES + s), ((g / TC_STAGES) & 1) ^ 1, 0);   // stage is free
+                    if (!ok) break;
+                    const unsigned full = bars + 8 * s;
+                    mbar_expect_tx(full, TC_STAGE_BYTES);
+                    const unsigned a_dst = base + s * TC_STAGE_BYTES;
+                    tma_load_2d(a_dst, &map_x, it * TC_BK, m0, full);
+                    tma_load_2d(a_dst + TC_A_BYTES, &map_w, it * TC_BK, n0, full);
+                }
             }
             if (!ok) {
                 // drain: the copies already issued must land before the CTA may exit
-                for (int it = max(0, issued - TC_STAGES); it < issued; ++it)
-                    mbar_wait(bars + 8 * (it % TC_STAGES), (it / TC_STAGES) & 1, 1);
+                for (int q = max(0, g - TC_STAGES); q < g; ++q) mbar_wait(bars + 8 * (q % TC_STAGES), (q / TC_STAGES) & 1, 1);
             }
         }
     } else if (warp == 1) {
@@ -161,110 +239,61 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
             const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TC_BN >> 3) << 17) |
                                    ((unsigned)(TC_BM >> 4) << 24);
             bool ok = true;
-            for (int it = 0; it < k_iters && ok; ++it) {
-                const int s = it % TC_STAGES;
-                const unsigned ph = (it / TC_STAGES) & 1;
-                ok = mbar_wait(bars + 8 * s, ph, 2);                     // operands have landed
+            int g = 0, j = 0;                                            // k steps consumed; tiles done by this CTA
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+                const int buf = j & 1;
+                ok = mbar_wait(bar_acc_empty + 8 * buf, ((j >> 1) & 1) ^ 1, 4);   // the epilogue has drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
-                const unsigned a_addr = base + s * TC_STAGE_BYTES;
-                const unsigned long long adesc = umma_desc(a_addr);
-                const unsigned long long bdesc = umma_desc(a_addr + TC_A_BYTES);
+                const unsigned acc = tmem_acc + buf * TC_BN;
+                for (int it = 0; it < k_iters; ++it, ++g) {
+                    const int s = g % TC_STAGES;
+                    ok = mbar_wait(bars + 8 * s, (g / TC_STAGES) & 1, 2);         // operands have landed
+                    if (!ok) break;
+                    tc_fence_after();
+                    const unsigned a_addr = base + s * TC_STAGE_BYTES;
+                    const unsigned long long adesc = umma_desc(a_addr);
+                    const unsigned long long bdesc = umma_desc(a_addr + TC_A_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)                     // 32 bytes along K per step: +2 in the address field
-                    tc_mma(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
-                tc_commit(bars + 8 * (TC_STAGES + s));                   // stage free when these MMAs have read it
+                    for (int k = 0; k < TC_BK / 16; ++k)                 // 32 bytes along K per step: +2 in the address field
+                        tc_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(bars + 8 * (TC_STAGES + s));               // stage free when these MMAs have read it
+                }
+                tc_commit(bar_acc_full + 8 * buf);                       // accumulator complete (or abandoned)
             }
-            tc_commit(bars + 8 * (2 * TC_STAGES));                       // accumulator complete
         }
     } else {
         // ---------------- epilogue: warps 2..5, lane quadrant = warp % 4 ----------------
         const int q = warp & 3;
         const int row = q * 32 + lane;
-        const int m = m0 + row;
-        const bool ok = mbar_wait(bars + 8 * (2 * TC_STAGES), 0, 3);
-        tc_fence_after();
-        if (ok) {
-            const unsigned t_row = tmem_acc + ((unsigned)(q * 32) << 16);
+        bool ok = true;
+        int j = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TC_BN;
+            const int buf = j & 1;
+            const int m = m0 + row;
+            ok = mbar_wait(bar_acc_full + 8 * buf, (j >> 1) & 1, 3);
+            tc_fence_after();
+            if (!ok) break;
+            const unsigned t_row = tmem_acc + buf * TC_BN + ((unsigned)(q * 32) << 16);
+            const int n_limit = mode == MODE_SWIGLU ? 2 * N : N;
 #pragma unroll 1
             for (int c = 0; c < TC_BN; c += 32) {
-                if (n0 + c >= (mode == MODE_SWIGLU ? 2 * N : N)) break;  // warp-uniform
+                if (n0 + c >= n_limit) break;                            // warp-uniform
                 unsigned r[32];
                 tmem_ld32(t_row + c, r);
-                if (m >= M) continue;
-                if (mode == MODE_SWIGLU) {
-                    // columns c .. c+31 = two groups of (8 gate, 8 up) -> 16 outputs
-                    const int o0 = (n0 + c) / 2;
-                    float v[16];
-#pragma unroll
-                    for (int gi = 0; gi < 2; ++gi)
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float g = __uint_as_float(r[gi * 16 + j]);
-                            const float u = __uint_as_float(r[gi * 16 + 8 + j]);
-                            v[gi * 8 + j] = g / (1.f + expf(-g)) * u;
-                        }
-                    if (out_bf16) {
-                        bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * N + o0;
-#pragma unroll
-                        for (int j = 0; j < 16; j += 8) {
-                            if (o0 + j >= N) break;
-                            uint4 pk;
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                            pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
-                            pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
-                            *reinterpret_cast<uint4*>(o + j) = pk;
-                        }
-                    } else {
-                        float* o = reinterpret_cast<float*>(out) + (size_t)m * N + o0;
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (o0 + j < N) o[j] = v[j];
-                    }
-                } else if (mode == MODE_ADD) {
-                    float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n0 + c;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        if (n0 + c + j >= N) break;
-                        float4 cur = *reinterpret_cast<float4*>(o + j);
-                        cur.x += __uint_as_float(r[j]); cur.y += __uint_as_float(r[j + 1]);
-                        cur.z += __uint_as_float(r[j + 2]); cur.w += __uint_as_float(r[j + 3]);
-                        *reinterpret_cast<float4*>(o + j) = cur;
-                    }
-                } else if (out_bf16) {
-                    bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * N + n0 + c;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        if (n0 + c + j >= N) break;
-                        uint4 pk;
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                        __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                        __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                        pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
-                        pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
-                        *reinterpret_cast<uint4*>(o + j) = pk;
-                    }
-                } else {
-                    float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n0 + c;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        if (n0 + c + j >= N) break;
-                        *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                        __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                    }
-                }
+                if (m < M) tc_epilogue32(r, out, m, n0, c, N, mode, out_bf16);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(2 * TC_BN) : "memory");
     }
 }
 
@@ -318,8 +347,17 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
         if (ce != cudaSuccess) return (int)ce;
         attr_set = true;
     }
-    dim3 grid((w_rows + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
-    gemm_tc_kernel<<<grid, 192, TC_SMEM, (cudaStream_t)stream>>>(map_x, map_w, out, M, N, K, mode, out_bf16);
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    const int tiles_n = (w_rows + TC_BN - 1) / TC_BN, tiles_m = (M + TC_BM - 1) / TC_BM;
+    const int total = tiles_n * tiles_m;
+    const int grid = total < n_sm ? total : n_sm;                  // one CTA per SM walks the tiles
+    gemm_tc_kernel<<<grid, 192, TC_SMEM, (cudaStream_t)stream>>>(map_x, map_w, out, M, N, K, mode, out_bf16, tiles_m,
+                                                                  tiles_n);
     return launch_status();
 }
 

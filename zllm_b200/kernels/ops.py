@@ -143,6 +143,7 @@ class CudaOps:
         self._check(code, "gemm_plain")
 
     SKINNY_MAX_ROWS = 64
+    TC_MIN_WEIGHT_ROWS = 3072
     SAMPLE_SCRATCH_ROWS = 1024
     DECODE_MAX_ROWS = 16
 
@@ -224,13 +225,17 @@ class CudaOps:
         if M <= self.DECODE_MAX_ROWS:
             self._gemm_decode(x, None, 0.0, w, out, mode, M, N, K)
             return True
-        if M <= self.SKINNY_MAX_ROWS:
+        w_rows = 2 * N if mode == "swiglu" else N
+        tc_ok = N % 8 == 0 and out.data_ptr() % 16 == 0
+        # 17..64 rows: the cluster split-K kernel fills the GPU when the matrix has few rows; with
+        # many rows the TMA-fed tcgen05 kernel streams the weights faster (measured at 32 and 64 rows)
+        if M <= self.SKINNY_MAX_ROWS and not (tc_ok and w_rows >= self.TC_MIN_WEIGHT_ROWS):
             code = self.lib("gemm_bf16").zllm_gemm_skinny_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
                                                                c_int(MODES[mode]), c_int(out.dtype == torch.bfloat16),
                                                                self._stream())
             self._check(code, "gemm_skinny_bf16")
             return True
-        if N % 8 == 0 and out.data_ptr() % 16 == 0 and "gemm_tc" in self._libs:
+        if tc_ok and "gemm_tc" in self._libs:
             code = self.lib("gemm_tc").zllm_gemm_tc_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
                                                          c_int(MODES[mode]), c_int(out.dtype == torch.bfloat16),
                                                          self._stream())
