@@ -178,3 +178,46 @@ def test_a_reused_page_does_not_leak_old_keys(tmp_path, dtype):
     got = torch.cat(outs)
     tol = 0.0 if dtype == "float32" else BF16_MAX_OF_SCALE * float(want.abs().max())
     assert float((got - want).abs().max()) <= tol
+
+
+LLAMA_1B_LAYER_SIZES = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=2048,
+                            num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192,
+                            vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0,
+                            rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                              original_max_position_embeddings=8192),
+                            max_position_embeddings=131072, tie_word_embeddings=True)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_llama_1b_layer_sizes(tmp_path, dtype):
+    """The layer sizes of Llama-3.2-1B (width 2048, 32/8 heads of 64, feed-forward 8192, vocabulary
+    128256, llama3 rope scaling of factor 32) with two layers, so that the plain implementation on
+    the CPU stays affordable: whole, in portions and decoded one by one, against plain; in 32-bit
+    the ways of cutting agree to the last bit."""
+    from zllm_b200.config import LlamaConfig
+    from zllm_b200.weights import write_random_model
+    d = tmp_path / "m"
+    write_random_model(d, LlamaConfig.from_dict(LLAMA_1B_LAYER_SIZES), 2, dtype, std=0.02, norm_std=0.1)
+    cfg, w = P.read_model_dir(d)
+    toks = random_prompt(128256, 150, 31)
+    ref = P.forward_all_positions(cfg, w, toks)
+    scale = float(ref.abs().max())
+    atol, rel = tolerances(dtype)
+    bound = atol * max(1.0, scale) + rel * scale
+    r = ModelRunner(d, engine_config=EngineConfig(dtype=dtype, block_size=16, num_blocks=24, max_num_seqs=2,
+                                                  max_num_batched_tokens=256, max_model_len=384))
+    s = r.admit()
+    whole = r.step([StepEntry(s, toks, tuple(range(150)))]).float().cpu().clone()
+    assert float((whole - ref).abs().max()) <= bound
+    r.release(s)
+    s = r.admit()
+    parts = [r.step([StepEntry(s, toks[:70], tuple(range(70)))]).float().cpu().clone(),
+             r.step([StepEntry(s, toks[70:137], tuple(range(67)))]).float().cpu().clone()]
+    for i in range(137, 150):
+        r.decode_step([s], [toks[i]], [0.0], [0])
+        parts.append(r.last_logits[:1].float().cpu().clone())
+    cut = torch.cat(parts)
+    assert float((cut - ref).abs().max()) <= bound
+    if dtype == "float32":
+        assert torch.equal(cut, whole)
+    r.ops.check_async_errors()
