@@ -11,9 +11,9 @@
 //    sdpa_flash_partial2.comp:1-56, sdpa_flash_combine_h.comp:1-41) on the math of its paged
 //    kernel (src/backend/gpu/shaders.rs:670-725).  The split size is fixed, so how a row is
 //    split depends on its own position only, never on the batch.
-//  * prefill: one CTA per (tile of 64 query rows of a portion, query head); K/V tiles of 64
-//    keys are gathered through the block table into shared memory (double buffered) and
-//    shared by the 4 warps (16 query rows each); a portion that starts at position p
+//  * prefill: one CTA per (tile of 128 query rows of a portion, query head); K/V tiles of 64
+//    keys are gathered through the block table into a 3-stage ring in shared memory and
+//    shared by the CTA's warps (two 16-row tiles each for head sizes up to 64); a portion that starts at position p
 //    attends the whole prefix 0..p-1 from the cache plus its own rows causally (zllm's
 //    coopmat_flash_attn.comp with its query offset, src/backend/vulkan/mod.rs:1758-1777).
 //
@@ -26,7 +26,7 @@
 #define SPLIT_KEYS 256
 #define DEC_WARPS 4
 #define DEC_BLOCK 32            // keys per warp iteration in the decode kernel
-#define PF_QROWS 64             // query rows per prefill CTA
+#define PF_QROWS 128            // query rows per prefill CTA (= QUERY_TILE of the host's tile list)
 #define PF_KEYS 64              // keys per prefill tile
 #define PF_STAGES 3             // shared-memory tiles in flight
 
@@ -191,21 +191,26 @@ __device__ __forceinline__ void softmax_pv(float (&s)[NB / 8][4], const bf16* __
     }
 }
 
-// One block of NB keys (NB multiple of 16) against the warp's 16 rows.
-//   qf      : A fragments of the 16 x HD query tile
+// One block of NB keys (NB multiple of 16) against MT 16-row tiles of the warp (prefill).  The
+// fragments of K and V are read from shared memory ONCE and used for all MT tiles: with MT = 2
+// the shared-memory traffic per tensor-core step halves.
+//   qf      : A fragments of the MT 16 x HD query tiles
 //   ks, vs  : shared tiles [NB][HD + 8] of the block's keys / values
 //   key0    : absolute index of the block's first key
-//   lo_r/hi_r : per row (index 0: row g, 1: row g + 8) the visible key range [lo, hi]
-template <int HD, int NB, bool MASKED>
-__device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], const bf16* __restrict__ ks,
-                                             const bf16* __restrict__ vs, int key0, const int (&lo_r)[2],
-                                             const int (&hi_r)[2], float scale, TileState<HD>& st, int lane) {
+//   lo_r/hi_r : per tile and row (index 0: row g, 1: row g + 8) the visible key range [lo, hi]
+template <int HD, int NB, bool MASKED, int MT>
+__device__ __forceinline__ void attend_block(const unsigned (&qf)[MT][HD / 16][4], const bf16* __restrict__ ks,
+                                             const bf16* __restrict__ vs, int key0, const int (&lo_r)[MT][2],
+                                             const int (&hi_r)[MT][2], float scale, TileState<HD> (&st)[MT], int lane) {
     constexpr int STR = HD + 8;
-    float s[NB / 8][4];
-#pragma unroll
-    for (int j = 0; j < NB / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-    // S = Q K^T: B fragments of K by ldmatrix (rows = keys, 8 x 8 tiles along dims)
+    const int t = lane & 3;
     const int lrow = lane & 7, lmat = lane >> 3;
+    float s[MT][NB / 8][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int j = 0; j < NB / 8; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f;
+    // S = Q K^T: B fragments of K by ldmatrix (rows = keys, 8 x 8 tiles along dims)
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk) {
 #pragma unroll
@@ -214,11 +219,90 @@ __device__ __forceinline__ void attend_block(const unsigned (&qf)[HD / 16][4], c
             unsigned b[4];
             const bf16* p = ks + (size_t)(8 * j + (lmat >> 1) * 8 + lrow) * STR + 16 * kk + (lmat & 1) * 8;
             ldmatrix_x4(b, p);
-            mma16816(s[j], qf[kk], b[0], b[1]);
-            mma16816(s[j + 1], qf[kk], b[2], b[3]);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                mma16816(s[mt][j], qf[mt][kk], b[0], b[1]);
+                mma16816(s[mt][j + 1], qf[mt][kk], b[2], b[3]);
+            }
         }
     }
-    softmax_pv<HD, NB, MASKED>(s, vs, key0, lo_r, hi_r, scale, st, lane);
+    // masking and running softmax per tile, in the scaled log2 domain
+    unsigned pa[MT][NB / 16][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        float mx[2] = {-INFINITY, -INFINITY};
+        if (MASKED) {
+#pragma unroll
+            for (int j = 0; j < NB / 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int r = e >> 1;
+                    const int key = key0 + 8 * j + 2 * t + (e & 1);
+                    if (!(key >= lo_r[mt][r] && key <= hi_r[mt][r])) s[mt][j][e] = -INFINITY;
+                    mx[r] = fmaxf(mx[r], s[mt][j][e]);
+                }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NB / 8; ++j) {
+                mx[0] = fmaxf(mx[0], fmaxf(s[mt][j][0], s[mt][j][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[mt][j][2], s[mt][j][3]));
+            }
+        }
+        float corr[2], msafe[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(st[mt].m[r], mx[r] * scale);
+            corr[r] = (m_new == -INFINITY) ? 1.f : ex2_approx(st[mt].m[r] - m_new);
+            msafe[r] = (m_new == -INFINITY) ? 0.f : m_new;
+            st[mt].m[r] = m_new;
+        }
+        float rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < NB / 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const float pr = ex2_approx(fmaf(s[mt][j][e], scale, -msafe[r]));     // 2^(-inf) = 0 for hidden keys
+                s[mt][j][e] = pr;
+                rs[r] += pr;
+            }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+            rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+            st[mt].l[r] = st[mt].l[r] * corr[r] + rs[r];
+        }
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            st[mt].o[i][0] *= corr[0]; st[mt].o[i][1] *= corr[0];
+            st[mt].o[i][2] *= corr[1]; st[mt].o[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < NB / 16; ++kk) {
+            pa[mt][kk][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+            pa[mt][kk][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+            pa[mt][kk][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+            pa[mt][kk][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+        }
+    }
+    // O += P V: B fragments of V by transposed ldmatrix, shared by the MT tiles
+#pragma unroll
+    for (int kk = 0; kk < NB / 16; ++kk) {
+#pragma unroll
+        for (int i = 0; i < HD / 8; i += 2) {
+            // matrices: (keys 16kk.., dims 8i..), (keys 16kk+8.., dims 8i..), (keys 16kk.., dims 8i+8..), (.., +8)
+            unsigned b[4];
+            const bf16* p = vs + (size_t)(16 * kk + (lmat & 1) * 8 + lrow) * STR + 8 * i + (lmat >> 1) * 8;
+            ldmatrix_x4_trans(b, p);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                mma16816(st[mt].o[i], pa[mt][kk], b[0], b[1]);
+                mma16816(st[mt].o[i + 1], pa[mt][kk], b[2], b[3]);
+            }
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------ decode
@@ -437,14 +521,18 @@ ZLLM_API int zllm_attention_decode_bf16(const void* qkv, void* out, const int* r
 }
 
 // ------------------------------------------------------------------------------------ prefill
-// tiles [n_tiles][4] = (first row, rows (<= 64), slot, position of first row)
-template <int HD>
-__global__ void __launch_bounds__(128, HD <= 64 ? 4 : 2) prefill_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out,
-                                                      const int* __restrict__ tiles, const bf16* __restrict__ k_pages,
-                                                      const bf16* __restrict__ v_pages, const int* __restrict__ table,
-                                                      int max_blocks, int bs, int bs_shift, int nq, int nkv,
-                                                      float scale, int window) {
+// tiles [n_tiles][4] = (first row, rows (<= 128), slot, position of first row).
+// NWARPS warps of MT 16-row tiles each cover the 128 query rows of a tile: head sizes up to 64
+// run 4 warps x 2 tiles (K/V fragments shared by two tiles), larger ones 8 warps x 1 tile
+// (the accumulators of two tiles would not fit the registers).
+template <int HD, int MT, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32, MT == 2 ? 2 : 1) prefill_kernel(
+    const bf16* __restrict__ qkv, bf16* __restrict__ out, const int* __restrict__ tiles,
+    const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages, const int* __restrict__ table,
+    int max_blocks, int bs, int bs_shift, int nq, int nkv, float scale, int window) {
+    static_assert(MT * NWARPS * 16 == PF_QROWS, "the warps' tiles must cover the query tile");
     constexpr int STR = HD + 8;
+    constexpr int NT = NWARPS * 32;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);          // [PF_STAGES][PF_KEYS][STR]
     bf16* vbuf = kbuf + PF_STAGES * PF_KEYS * STR;           // [PF_STAGES][PF_KEYS][STR]
@@ -458,41 +546,43 @@ __global__ void __launch_bounds__(128, HD <= 64 ? 4 : 2) prefill_kernel(const bf
     const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
     const int kb_first = first_key / PF_KEYS;
     const int kb_last = last_pos / PF_KEYS;
-    // query fragments of the warp's 16 rows
-    const int r_a = warp * 16 + g, r_b = r_a + 8;            // rows within the tile
-    unsigned qf[HD / 16][4];
-    {
+    const int wrow0 = warp * MT * 16;                        // first row of the warp within the tile
+    unsigned qf[MT][HD / 16][4];
+    TileState<HD> st[MT];
+    int lo_r[MT][2], hi_r[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const int r_a = wrow0 + mt * 16 + g, r_b = r_a + 8;  // rows within the tile
         const size_t stride = (size_t)(nq + 2 * nkv) * HD;
         const bf16* qa = qkv + (size_t)(row0 + r_a) * stride + (size_t)h * HD;
         const bf16* qb = qkv + (size_t)(row0 + r_b) * stride + (size_t)h * HD;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
             const int d = 16 * kk + 2 * t;
-            qf[kk][0] = r_a < n_rows ? *reinterpret_cast<const unsigned*>(qa + d) : 0u;
-            qf[kk][1] = r_b < n_rows ? *reinterpret_cast<const unsigned*>(qb + d) : 0u;
-            qf[kk][2] = r_a < n_rows ? *reinterpret_cast<const unsigned*>(qa + d + 8) : 0u;
-            qf[kk][3] = r_b < n_rows ? *reinterpret_cast<const unsigned*>(qb + d + 8) : 0u;
+            qf[mt][kk][0] = r_a < n_rows ? *reinterpret_cast<const unsigned*>(qa + d) : 0u;
+            qf[mt][kk][1] = r_b < n_rows ? *reinterpret_cast<const unsigned*>(qb + d) : 0u;
+            qf[mt][kk][2] = r_a < n_rows ? *reinterpret_cast<const unsigned*>(qa + d + 8) : 0u;
+            qf[mt][kk][3] = r_b < n_rows ? *reinterpret_cast<const unsigned*>(qb + d + 8) : 0u;
         }
+        st[mt].init();
+        hi_r[mt][0] = r_a < n_rows ? pos0 + r_a : -1;        // rows beyond the tile see nothing
+        hi_r[mt][1] = r_b < n_rows ? pos0 + r_b : -1;
+        lo_r[mt][0] = window > 0 ? max(0, hi_r[mt][0] - window + 1) : 0;
+        lo_r[mt][1] = window > 0 ? max(0, hi_r[mt][1] - window + 1) : 0;
     }
-    TileState<HD> st;
-    st.init();
-    int lo_r[2], hi_r[2];
-    hi_r[0] = r_a < n_rows ? pos0 + r_a : -1;                // rows beyond the tile see nothing
-    hi_r[1] = r_b < n_rows ? pos0 + r_b : -1;
-    lo_r[0] = window > 0 ? max(0, hi_r[0] - window + 1) : 0;
-    lo_r[1] = window > 0 ? max(0, hi_r[1] - window + 1) : 0;
-    const int w_hi = pos0 + min(n_rows - 1, warp * 16 + 15);  // last key this warp's rows see
-    const int w_lo = window > 0 ? max(0, pos0 + warp * 16 - window + 1) : 0;
+    constexpr int WR = MT * 16;                              // rows of the warp
+    const int w_hi = pos0 + min(n_rows - 1, wrow0 + WR - 1);  // last key this warp's rows see
+    const int w_lo = window > 0 ? max(0, pos0 + wrow0 - window + 1) : 0;
     // the range every row of the warp sees in full (empty when the warp holds rows beyond the tile)
-    const int w_min_hi = (warp * 16 + 15 < n_rows) ? pos0 + warp * 16 : -1;
-    const int w_max_lo = window > 0 ? max(0, pos0 + warp * 16 + 15 - window + 1) : 0;
+    const int w_min_hi = (wrow0 + WR - 1 < n_rows) ? pos0 + wrow0 : -1;
+    const int w_max_lo = window > 0 ? max(0, pos0 + wrow0 + WR - 1 - window + 1) : 0;
 
     // three-stage ring: tiles kb + 1 and kb + 2 are in flight while tile kb is used
     auto load_tile = [&](int kb, int stage) {
-        gather_tile<HD, PF_KEYS, 128>(kbuf + (size_t)stage * PF_KEYS * STR, k_pages, trow, kb * PF_KEYS, last_pos + 1,
-                                      bs, bs_shift, nkv, kvh, threadIdx.x);
-        gather_tile<HD, PF_KEYS, 128>(vbuf + (size_t)stage * PF_KEYS * STR, v_pages, trow, kb * PF_KEYS, last_pos + 1,
-                                      bs, bs_shift, nkv, kvh, threadIdx.x);
+        gather_tile<HD, PF_KEYS, NT>(kbuf + (size_t)stage * PF_KEYS * STR, k_pages, trow, kb * PF_KEYS, last_pos + 1,
+                                     bs, bs_shift, nkv, kvh, threadIdx.x);
+        gather_tile<HD, PF_KEYS, NT>(vbuf + (size_t)stage * PF_KEYS * STR, v_pages, trow, kb * PF_KEYS, last_pos + 1,
+                                     bs, bs_shift, nkv, kvh, threadIdx.x);
     };
     load_tile(kb_first, 0);
     __pipeline_commit();
@@ -507,27 +597,31 @@ __global__ void __launch_bounds__(128, HD <= 64 ? 4 : 2) prefill_kernel(const bf
         const int key0 = kb * PF_KEYS;
         if (key0 <= w_hi && key0 + PF_KEYS - 1 >= w_lo) {    // warp-uniform: some key of the tile is visible
             if (key0 + PF_KEYS - 1 <= w_min_hi && key0 >= w_max_lo)   // every key visible to every row of the warp
-                attend_block<HD, PF_KEYS, false>(qf, kbuf + (size_t)cur * PF_KEYS * STR,
-                                                 vbuf + (size_t)cur * PF_KEYS * STR, key0, lo_r, hi_r, scale, st, lane);
+                attend_block<HD, PF_KEYS, false, MT>(qf, kbuf + (size_t)cur * PF_KEYS * STR,
+                                                     vbuf + (size_t)cur * PF_KEYS * STR, key0, lo_r, hi_r, scale, st, lane);
             else
-                attend_block<HD, PF_KEYS, true>(qf, kbuf + (size_t)cur * PF_KEYS * STR,
-                                                vbuf + (size_t)cur * PF_KEYS * STR, key0, lo_r, hi_r, scale, st, lane);
+                attend_block<HD, PF_KEYS, true, MT>(qf, kbuf + (size_t)cur * PF_KEYS * STR,
+                                                    vbuf + (size_t)cur * PF_KEYS * STR, key0, lo_r, hi_r, scale, st, lane);
         }
         __syncthreads();
     }
     __pipeline_wait_prior(0);
     // normalise and store
-    const float inv0 = st.l[0] > 0.f ? 1.f / st.l[0] : 0.f;
-    const float inv1 = st.l[1] > 0.f ? 1.f / st.l[1] : 0.f;
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-        const int d = 8 * i + 2 * t;
-        if (r_a < n_rows)
-            *reinterpret_cast<unsigned*>(out + ((size_t)(row0 + r_a) * nq + h) * HD + d) =
-                pack_bf16(st.o[i][0] * inv0, st.o[i][1] * inv0);
-        if (r_b < n_rows)
-            *reinterpret_cast<unsigned*>(out + ((size_t)(row0 + r_b) * nq + h) * HD + d) =
-                pack_bf16(st.o[i][2] * inv1, st.o[i][3] * inv1);
+    for (int mt = 0; mt < MT; ++mt) {
+        const int r_a = wrow0 + mt * 16 + g, r_b = r_a + 8;
+        const float inv0 = st[mt].l[0] > 0.f ? 1.f / st[mt].l[0] : 0.f;
+        const float inv1 = st[mt].l[1] > 0.f ? 1.f / st[mt].l[1] : 0.f;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            const int d = 8 * i + 2 * t;
+            if (r_a < n_rows)
+                *reinterpret_cast<unsigned*>(out + ((size_t)(row0 + r_a) * nq + h) * HD + d) =
+                    pack_bf16(st[mt].o[i][0] * inv0, st[mt].o[i][1] * inv0);
+            if (r_b < n_rows)
+                *reinterpret_cast<unsigned*>(out + ((size_t)(row0 + r_b) * nq + h) * HD + d) =
+                    pack_bf16(st[mt].o[i][2] * inv1, st[mt].o[i][3] * inv1);
+        }
     }
 }
 
@@ -536,17 +630,20 @@ static int launch_prefill(const void* qkv, void* out, const int* tiles, int n_ti
                           const void* v_pages, const int* table, int max_blocks, int bs, int nq, int nkv, float scale,
                           int window, cudaStream_t s) {
     constexpr int STR = HD + 8;
+    constexpr int MT = HD <= 64 ? 2 : 1;
+    constexpr int NWARPS = PF_QROWS / (16 * MT);
     const size_t smem = (size_t)2 * PF_STAGES * PF_KEYS * STR * sizeof(bf16);
-    auto kern = prefill_kernel<HD>;
+    auto kern = prefill_kernel<HD, MT, NWARPS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const int bs_shift = (bs & (bs - 1)) == 0 ? __builtin_ctz(bs) : -1;
-    kern<<<dim3(n_tiles, nq), 128, smem, s>>>((const bf16*)qkv, (bf16*)out, tiles, (const bf16*)k_pages,
-                                              (const bf16*)v_pages, table, max_blocks, bs, bs_shift, nq, nkv,
-                                              scale * 1.4426950408889634f, window);
+    kern<<<dim3(n_tiles, nq), NWARPS * 32, smem, s>>>((const bf16*)qkv, (bf16*)out, tiles, (const bf16*)k_pages,
+                                                      (const bf16*)v_pages, table, max_blocks, bs, bs_shift, nq, nkv,
+                                                      scale * 1.4426950408889634f, window);
     return launch_status();
 }
 
+// tiles: [n_tiles][4] int32 (first row, rows <= 128, slot, position of the first row)
 ZLLM_API int zllm_attention_prefill_bf16(const void* qkv, void* out, const int* tiles, int n_tiles,
                                          const void* k_pages, const void* v_pages, const int* table, int max_blocks,
                                          int bs, int nq, int nkv, int hd, float scale, int window, void* stream) {

@@ -19,7 +19,7 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
-QUERY_TILE = 64          # rows of one portion that one attention tile covers
+QUERY_TILE = 128         # rows of one portion that one attention tile covers (csrc/attention_bf16.cu PF_QROWS)
 
 
 @dataclass
