@@ -314,8 +314,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
     float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits) {
     constexpr int STR = HD + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    // What this block needs that the kernel before it (the QKV product of this step) does not
+    // write -- the row's slot and position, the page table, and every key and value older than
+    // the row's own position -- is requested BEFORE waiting for that kernel; only q and the key
+    // and value at the row's own position are read after the wait.
     pdl_trigger();
-    pdl_wait();
     const int row = rows[blockIdx.x];
     const int slot = row_slot[row];
     if (slot < 0) return;
@@ -329,12 +332,50 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
     const int* trow = table + (size_t)slot * max_blocks;
     constexpr int NB = HD <= 64 ? 64 : 32;                  // keys per warp iteration
     constexpr int NMMA = HD / 16;                            // tensor-core steps along the head
+    constexpr int CH = HD / 8;
     bf16* vs = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * NB * STR;
     // Keys go straight from global memory into B fragments: the order of dims inside a
     // tensor-core step is free as long as q uses the same one, so lane (g, t) takes the 8
     // consecutive dims 32 p + 8 t of key g (two steps' worth) with one 16-byte load.  A last
     // odd step (head sizes 16, 48, ...) takes dims base + 4 t with an 8-byte load.
-    // Query fragments in that same order: row g of the tile is query head kvh * G + g.
+    unsigned kf[NB / 8][NMMA][2];
+    auto key_row = [&](const bf16* pages, int key) -> const bf16* {
+        const int blk = bs_shift >= 0 ? (key >> bs_shift) : key / bs;
+        const int off = bs_shift >= 0 ? (key & (bs - 1)) : key - blk * bs;
+        const int page = trow[blk];
+        return page >= 0 ? pages + (((size_t)page * nkv + kvh) * bs + off) * HD : nullptr;
+    };
+    // (rows shorter than a 128-byte line bypass L1: a line fetched before the wait would hold the
+    // stale bytes of the row's own key)
+    auto load_k_row = [&](int j, const bf16* krow) {         // j must be a compile-time index after unrolling
+#pragma unroll
+        for (int pq = 0; pq < HD / 32; ++pq) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (krow != nullptr) v = (HD >= 64) ? *reinterpret_cast<const uint4*>(krow + 32 * pq + 8 * t)
+                                                : __ldcg(reinterpret_cast<const uint4*>(krow + 32 * pq + 8 * t));
+            kf[j][2 * pq][0] = v.x; kf[j][2 * pq][1] = v.y;
+            kf[j][2 * pq + 1][0] = v.z; kf[j][2 * pq + 1][1] = v.w;
+        }
+        if (HD % 32) {
+            uint2 v = make_uint2(0, 0);
+            if (krow != nullptr) v = __ldcg(reinterpret_cast<const uint2*>(krow + 32 * (HD / 32) + 4 * t));
+            kf[j][NMMA - 1][0] = v.x; kf[j][NMMA - 1][1] = v.y;
+        }
+    };
+    // keys key0 .. key0 + NB - 1 that are <= last_key: K into fragments, V into the shared tile
+    auto load_kv = [&](int key0, int last_key) {
+#pragma unroll
+        for (int j = 0; j < NB / 8; ++j) {
+            const int key = key0 + 8 * j + g;
+            load_k_row(j, key <= last_key ? key_row(k_pages, key) : nullptr);
+        }
+        gather_tile<HD, NB, 32>(vs, v_pages, trow, key0, last_key + 1, bs, bs_shift, nkv, kvh, lane);
+        __pipeline_commit();
+    };
+    const int w_first = k_first + warp * (SPLIT_KEYS / DEC_WARPS);
+    if (w_first <= pos) load_kv(w_first, pos - 1);           // everything older than this step
+    pdl_wait();
+    // Query fragments in the keys' order of dims: row g of the tile is query head kvh * G + g.
     unsigned qf[NMMA][4];
     {
         const bf16* qrow = qkv + (size_t)row * (nq + 2 * nkv) * HD + (size_t)kvh * G * HD;
@@ -350,37 +391,23 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
     TileState<HD> st;
     st.init();
     const int lo_r[2] = {lo, lo}, hi_r[2] = {pos, pos};
-    const int w_first = k_first + warp * (SPLIT_KEYS / DEC_WARPS);
 #pragma unroll 1
     for (int it = 0; it < SPLIT_KEYS / DEC_WARPS / NB; ++it) {
         const int key0 = w_first + it * NB;
         if (key0 > pos) break;                               // warp-uniform
-        unsigned kf[NB / 8][NMMA][2];
+        if (it > 0) {
+            load_kv(key0, pos);
+        } else if (pos < key0 + NB) {
+            // the row's own key and value, written by the kernel before this one
 #pragma unroll
-        for (int j = 0; j < NB / 8; ++j) {
-            const int key = key0 + 8 * j + g;
-            const bf16* krow = nullptr;
-            if (key <= pos) {
-                const int blk = bs_shift >= 0 ? (key >> bs_shift) : key / bs;
-                const int off = bs_shift >= 0 ? (key & (bs - 1)) : key - blk * bs;
-                const int page = trow[blk];
-                if (page >= 0) krow = k_pages + (((size_t)page * nkv + kvh) * bs + off) * HD;
-            }
-#pragma unroll
-            for (int pq = 0; pq < HD / 32; ++pq) {
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (krow != nullptr) v = *reinterpret_cast<const uint4*>(krow + 32 * pq + 8 * t);
-                kf[j][2 * pq][0] = v.x; kf[j][2 * pq][1] = v.y;
-                kf[j][2 * pq + 1][0] = v.z; kf[j][2 * pq + 1][1] = v.w;
-            }
-            if (HD % 32) {
-                uint2 v = make_uint2(0, 0);
-                if (krow != nullptr) v = *reinterpret_cast<const uint2*>(krow + 32 * (HD / 32) + 4 * t);
-                kf[j][NMMA - 1][0] = v.x; kf[j][NMMA - 1][1] = v.y;
-            }
+            for (int j = 0; j < NB / 8; ++j)
+                if (key0 + 8 * j + g == pos) load_k_row(j, key_row(k_pages, pos));
+            __syncwarp();                                    // the zero fill of that V row is done
+            const bf16* vrow = key_row(v_pages, pos);
+            if (lane < CH && vrow != nullptr)
+                __pipeline_memcpy_async(vs + (size_t)(pos - key0) * STR + lane * 8, vrow + lane * 8, 16);
+            __pipeline_commit();
         }
-        gather_tile<HD, NB, 32>(vs, v_pages, trow, key0, pos + 1, bs, bs_shift, nkv, kvh, lane);
-        __pipeline_commit();
         float sc[NB / 8][4];
 #pragma unroll
         for (int j = 0; j < NB / 8; ++j) {
