@@ -71,6 +71,16 @@ def test_temperature_and_topk_sampling(tmp_path, dtype):
     assert eng.generate(prompts[:1], greedy2) == g1          # temperature 0: the seed does not matter
 
 
+def test_warm_up_captures_every_bucket(tmp_path):
+    d = make_model_dir(tmp_path, "C", "bfloat16")
+    eng = Engine(str(d), dtype="bfloat16", max_num_seqs=5, max_model_len=600, num_blocks=64)
+    n = eng.warm_up()
+    assert n == 4 * 3 and eng.warm_up() == 0           # rows 1, 2, 4, 8 x splits 1, 2, 4
+    before = set(eng.runner._graphs)
+    out = eng.generate([random_prompt(1536, 300, 1), random_prompt(1536, 5, 2)], SamplingParams.greedy(max_tokens=30))
+    assert set(eng.runner._graphs) == before and len(out[0]) == 30
+
+
 def test_session_single_stream_calls(tmp_path):
     d = make_model_dir(tmp_path, "A", "float32")
     cfg, w = P.read_model_dir(d)

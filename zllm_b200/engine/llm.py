@@ -158,6 +158,11 @@ class Engine:
                     outs[rid].append(tok)
         return [outs[i] for i in ids]
 
+    def warm_up(self, max_batch: Optional[int] = None, max_context: Optional[int] = None) -> int:
+        """Capture every decode graph that requests up to these sizes can need (see
+        ``ModelRunner.capture_decode_graphs``); serving then never stalls on a capture."""
+        return self.runner.capture_decode_graphs(max_batch, max_context)
+
     def stats(self) -> dict:
         s = self.scheduler.stats()
         s.update({"steps": self.steps, "generated": self.generated, "tokens_run": self.runner.tokens_run})

@@ -368,6 +368,30 @@ class ModelRunner:
         g["graph"] = graph
         return g
 
+    def capture_decode_graphs(self, max_batch: Optional[int] = None, max_context: Optional[int] = None) -> int:
+        """Capture the decode graphs of every (rows, splits) bucket up to ``max_batch`` rows and
+        ``max_context`` positions now, so that no step pays for a capture later (a capture takes a
+        few milliseconds).  Returns the number of graphs captured."""
+        if not (self.ecfg.cuda_graphs and self.device.type == "cuda"):
+            return 0
+        max_batch = min(max_batch or self.ecfg.max_num_seqs, self.ecfg.max_num_seqs)
+        max_context = min(max_context or self.max_len, self.max_len)
+        n = 0
+        b = 1
+        while True:
+            sb = 1
+            while True:
+                if (b, sb) not in self._graphs:
+                    self._graphs[(b, sb)] = self._make_decode_graph(b, sb, True)
+                    n += 1
+                if sb >= self.ops.decode_splits(max_context):
+                    break
+                sb *= 2
+            if b >= max_batch:
+                break
+            b *= 2
+        return n
+
     # ---- numbers for measurement ------------------------------------------------
     def weight_bytes(self) -> int:
         seen = set()
