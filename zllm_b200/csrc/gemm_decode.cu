@@ -55,6 +55,7 @@ struct GemmDecodeParams {
     bf16* v_pages;
     const int* table;
     int max_blocks, bs, store;
+    int wide;               // weights may be read 32 bytes at a time
 };
 
 __device__ __forceinline__ void gd_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
@@ -68,6 +69,11 @@ __device__ __forceinline__ uint4 gd_ldg(const void* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
+}
+// 32 consecutive bytes in one request (a whole sector per lane; sm_100 has 256-bit loads)
+__device__ __forceinline__ void gd_ldg256(const void* p, uint4& lo, uint4& hi) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(p));
 }
 __device__ __forceinline__ unsigned gd_pack(float a, float b) {
     __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -128,6 +134,17 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
         const bool va = ra < p.w_rows, vb = rb < p.w_rows;
         const bf16* wa = p.w + (size_t)(va ? ra : 0) * K;
         const bf16* wb = p.w + (size_t)(vb ? rb : 0) * K;
+        if (p.wide) {                                                        // K % 16 == 0, rows 32-byte aligned
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const int k = kb + s * 64 + t * 16;
+                if (va && k < K) gd_ldg256(wa + k, fa[s][0], fa[s][1]);
+                else fa[s][0] = fa[s][1] = make_uint4(0, 0, 0, 0);
+                if (vb && k < K) gd_ldg256(wb + k, fb[s][0], fb[s][1]);
+                else fb[s][0] = fb[s][1] = make_uint4(0, 0, 0, 0);
+            }
+            return;
+        }
 #pragma unroll
         for (int s = 0; s < 4; ++s)
 #pragma unroll
@@ -359,6 +376,7 @@ ZLLM_API int zllm_gemm_decode(const void* x, const void* norm_w, int norm_w_bf16
     p.positions = positions; p.row_slot = row_slot; p.cos_t = cos_t; p.sin_t = sin_t; p.interleaved = interleaved;
     p.nq = nq; p.nkv = nkv; p.hd = hd; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages; p.table = table;
     p.max_blocks = max_blocks; p.bs = bs; p.store = store;
+    p.wide = (K % 16 == 0) && (((uintptr_t)w & 31) == 0);
     cudaStream_t s = (cudaStream_t)stream;
     const bool fuse = norm_w != nullptr;
     if (M <= 8) return fuse ? launch_gd_rt<1, true>(p, s) : launch_gd_rt<1, false>(p, s);
