@@ -91,6 +91,37 @@ def test_linear(ops, M, N, K, dtype, mode):
         assert err <= (2 ** -8) * max(scale, 1.0) * 1.5     # output rounding to bf16 plus accumulation order
 
 
+STREAM_SHAPES = [  # rows, N, K, epilogue: what the TMA-fed streaming product takes (9..64 rows), at sizes with one and
+    # several weight tiles, K split over clusters of 1 to 8 CTAs, ragged last tiles and k steps
+    (12, 4096, 3072, "store"), (9, 2048, 8192, "add"), (16, 8192, 1536, "swiglu"), (17, 48, 24, "store"),
+    (33, 3072, 2048, "store"), (40, 2048, 8192, "add"), (64, 1000, 1032, "store"), (64, 4104, 520, "swiglu"),
+    (23, 264, 4104, "add"), (32, 30000, 72, "store"),
+]
+
+
+@pytest.mark.parametrize("M,N,K,mode", STREAM_SHAPES)
+def test_streaming_product(ops, M, N, K, mode):
+    dtype = torch.bfloat16
+    x = rnd((M, K), dtype, 5)
+    if mode == "swiglu":
+        w = interleave_gate_up(rnd((N, K), dtype, 6, K ** -0.5), rnd((N, K), dtype, 7, K ** -0.5))
+    else:
+        w = rnd((N, K), dtype, 6, K ** -0.5)
+    assert ops._streams(M, w) or M > 16
+    for odt in ((torch.float32,) if mode == "add" else (torch.float32, torch.bfloat16)):
+        base = rnd((M, N), odt, 8)
+        out = base.clone().to(DEV)
+        before = ops.launches
+        ops.linear(x.to(DEV), w.to(DEV), out, mode)
+        assert ops.launches == before + 1
+        ops.check_async_errors()
+        want = base.clone().float()
+        REF.linear(x, w, want, mode)
+        err = float((out.cpu().float() - want).abs().max())
+        scale = max(float(want.abs().max()), 1.0)
+        assert err <= (2e-5 if odt == torch.float32 else 2 ** -8 * 1.5) * scale, (odt, err)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_linear_plain_matches_too(ops, dtype):
     x, w = rnd((33, 100), dtype, 1), rnd((77, 100), dtype, 2, 0.1)

@@ -15,7 +15,8 @@
 //
 // Layout of the work: one CTA = 16 weight rows; its 8 warps split K (256 k per warp per pass
 // of 2048); each warp streams its weights straight from global memory into mma.sync
-// fragments (16 consecutive k per lane and row, see gemm_bf16.cu) and stages its own slice
+// fragments (because the order of k inside a tensor-core step is free as long as both operands agree,
+// lane (g, t) takes the 16 consecutive k at k0 + 16 t of rows g and g + 8: no shuffles, no ldmatrix) and stages its own slice
 // of x in its own shared memory, so no CTA-wide barrier is needed until the 8 partial tiles
 // are summed, in warp order, through shared memory.  No cluster, no scratch, deterministic;
 // a row of x never mixes with another row.

@@ -56,7 +56,7 @@ class CudaOps:
         self.dtype = dtype
         names = ["elementwise", "gemm_plain", "attention_plain", "sampling"]
         if dtype == torch.bfloat16:
-            names += ["gemm_decode", "gemm_bf16", "gemm_tc", "attention_bf16"]
+            names += ["gemm_decode", "gemm_stream", "gemm_tc", "attention_bf16"]
         build.build(names)
         for n in names:
             self._libs[n] = build.load(n)
@@ -127,7 +127,7 @@ class CudaOps:
             raise BackendError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} mode {mode}")
         if mode == "add" and out.dtype != torch.float32:
             raise BackendError("linear: the 'add' epilogue accumulates into float32")
-        if x.dtype == torch.bfloat16 and "gemm_bf16" in self._libs and self._linear_bf16(x, w, out, mode, M, N, K):
+        if x.dtype == torch.bfloat16 and "gemm_decode" in self._libs and self._linear_bf16(x, w, out, mode, M, N, K):
             return
         code = self.lib("gemm_plain").zllm_gemm_plain(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
                                                       c_int(MODES[mode]), c_int(x.dtype == torch.bfloat16),
@@ -142,8 +142,15 @@ class CudaOps:
                                                       c_int(out.dtype == torch.bfloat16), self._stream())
         self._check(code, "gemm_plain")
 
-    SKINNY_MAX_ROWS = 64
-    TC_MIN_WEIGHT_ROWS = 3072
+    # Which kernel takes a bfloat16 product is decided by the sizes alone (never by trial):
+    #   rows <= 8: the fused decode product;  9..16: the same for small matrices (its fusions save
+    #   kernels), the TMA-fed streaming product for matrices of STREAM_MIN_WEIGHTS elements and more;
+    #   17..64: the streaming product, but matrices with STREAM_MAX_WEIGHT_ROWS rows and more (the
+    #   vocabulary head) go to the many-row kernel, which re-reads x once per 256 rows, not per 128;
+    #   more rows: the many-row kernel.
+    STREAM_MAX_ROWS = 64
+    STREAM_MIN_WEIGHTS = 12 * 1024 * 1024
+    STREAM_MAX_WEIGHT_ROWS = 32768
     SAMPLE_SCRATCH_ROWS = 1024
     DECODE_MAX_ROWS = 16
 
@@ -171,8 +178,17 @@ class CudaOps:
             _ptr(tb), c_int(mb), c_int(bs), c_int(1 if store else 0), self._stream())
         self._check(code, "gemm_decode")
 
+    def _streams(self, M, w) -> bool:
+        """True when a product of M rows with matrix w belongs to the streaming kernel."""
+        if M <= 8 or M > self.STREAM_MAX_ROWS:
+            return False
+        if M <= self.DECODE_MAX_ROWS:
+            return w.numel() >= self.STREAM_MIN_WEIGHTS
+        return w.shape[0] < self.STREAM_MAX_WEIGHT_ROWS
+
     def _can_fuse_decode(self, x, norm_w, w, M, K) -> bool:
         return (self.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= self.DECODE_MAX_ROWS and K % 8 == 0
+                and not self._streams(M, w)
                 and (x.data_ptr() | w.data_ptr() | (norm_w.data_ptr() if norm_w is not None else 0)) & 15 == 0)
 
     def linear_normed(self, x, norm_w, eps, w, out, mode, ws):
@@ -222,18 +238,15 @@ class CudaOps:
         The choice depends on the sizes only."""
         if K % 8 or (mode == "swiglu" and N % 8) or (x.data_ptr() | w.data_ptr()) & 15:
             return False
+        tc_ok = N % 8 == 0 and out.data_ptr() % 16 == 0
+        if self._streams(M, w) or (M <= self.STREAM_MAX_ROWS and M > self.DECODE_MAX_ROWS and not tc_ok):
+            code = self.lib("gemm_stream").zllm_gemm_stream_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                                                 c_int(MODES[mode]), c_int(out.dtype == torch.bfloat16),
+                                                                 self._stream())
+            self._check(code, "gemm_stream_bf16")
+            return True
         if M <= self.DECODE_MAX_ROWS:
             self._gemm_decode(x, None, 0.0, w, out, mode, M, N, K)
-            return True
-        w_rows = 2 * N if mode == "swiglu" else N
-        tc_ok = N % 8 == 0 and out.data_ptr() % 16 == 0
-        # 17..64 rows: the cluster split-K kernel fills the GPU when the matrix has few rows; with
-        # many rows the TMA-fed tcgen05 kernel streams the weights faster (measured at 32 and 64 rows)
-        if M <= self.SKINNY_MAX_ROWS and not (tc_ok and w_rows >= self.TC_MIN_WEIGHT_ROWS):
-            code = self.lib("gemm_bf16").zllm_gemm_skinny_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
-                                                               c_int(MODES[mode]), c_int(out.dtype == torch.bfloat16),
-                                                               self._stream())
-            self._check(code, "gemm_skinny_bf16")
             return True
         if tc_ok and "gemm_tc" in self._libs:
             code = self.lib("gemm_tc").zllm_gemm_tc_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
@@ -245,11 +258,12 @@ class CudaOps:
 
     def check_async_errors(self):
         """Raise if a kernel's bounded wait gave up since the last call (synchronises the device)."""
-        lib = self._libs.get("gemm_tc")
-        if lib is not None:
-            v = lib.zllm_gemm_tc_error()
-            if v != 0:
-                raise BackendError(f"gemm_tc: a bounded wait ran out (code {v}); results of that launch are invalid")
+        for name, fn in (("gemm_tc", "zllm_gemm_tc_error"), ("gemm_stream", "zllm_gemm_stream_error")):
+            lib = self._libs.get(name)
+            if lib is not None:
+                v = getattr(lib, fn)()
+                if v != 0:
+                    raise BackendError(f"{name}: a bounded wait ran out (code {v}); results of that launch are invalid")
 
     # ---- silu * up -----------------------------------------------------
     def silu_mul(self, a, b, out):
