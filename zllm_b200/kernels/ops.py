@@ -47,6 +47,7 @@ class CudaOps:
         self.dtype = torch.bfloat16
         self._libs = {}
         self._sample_scratch = None
+        self._kv_maps = {}
         self.launches = 0
 
     # ------------------------------------------------------------------
@@ -56,7 +57,7 @@ class CudaOps:
         self.dtype = dtype
         names = ["elementwise", "gemm_plain", "attention_plain", "sampling"]
         if dtype == torch.bfloat16:
-            names += ["gemm_decode", "gemm_stream", "gemm_tc", "attention_bf16"]
+            names += ["gemm_decode", "gemm_stream", "gemm_tc", "attention_bf16", "attention_decode_tma"]
         build.build(names)
         for n in names:
             self._libs[n] = build.load(n)
@@ -258,7 +259,8 @@ class CudaOps:
 
     def check_async_errors(self):
         """Raise if a kernel's bounded wait gave up since the last call (synchronises the device)."""
-        for name, fn in (("gemm_tc", "zllm_gemm_tc_error"), ("gemm_stream", "zllm_gemm_stream_error")):
+        for name, fn in (("gemm_tc", "zllm_gemm_tc_error"), ("gemm_stream", "zllm_gemm_stream_error"),
+                         ("attention_decode_tma", "zllm_attention_decode_tma_error")):
             lib = self._libs.get(name)
             if lib is not None:
                 v = getattr(lib, fn)()
@@ -338,6 +340,26 @@ class CudaOps:
             self._stream())
         self._check(code, "attention_plain")
 
+    def _kv_tensor_maps(self, cache, nkv, hd):
+        """The TMA descriptors (host buffers of 128 bytes) of a layer's key and value pools, made
+        once per pool; None when the TMA kernel does not take this head or page size."""
+        bs = cache.block_size
+        if hd not in (64, 128) or bs < 8 or bs > 256 or bs & (bs - 1):
+            return None
+        key = (cache.k_pages.data_ptr(), cache.v_pages.data_ptr(), tuple(cache.k_pages.shape))
+        maps = self._kv_maps.get(key)
+        if maps is None:
+            lib = self.lib("attention_decode_tma")
+            bufs = []
+            for pages in (cache.k_pages, cache.v_pages):
+                buf = ctypes.create_string_buffer(128)
+                code = lib.zllm_attention_kv_map(buf, _ptr(pages), c_longlong(pages.shape[0]), c_int(nkv), c_int(bs), c_int(hd))
+                if code != 0:
+                    raise BackendError(f"attention_kv_map: the driver refused the tensor map (code {code})")
+                bufs.append(buf)
+            maps = self._kv_maps[key] = tuple(bufs)
+        return maps
+
     def _attention_bf16(self, qkv, out, ctx, cache, nq, nkv, hd, scale, window) -> bool:
         """Tensor-core attention: decoded rows by the split kernel, portions by the tiled kernel.
         False: head size or group not taken, every row goes to the plain kernel."""
@@ -351,12 +373,23 @@ class CudaOps:
             nd = ctx.n_decode
             part_o = ctx.ws.get("attn_part_o", (nd, nq * max_splits * hd), torch.float32, cap=nd)
             part_ml = ctx.ws.get("attn_part_ml", (nd, nq * max_splits * 2), torch.float32, cap=nd)
-            code = lib.zllm_attention_decode_bf16(
-                _ptr(qkv), _ptr(out), _ptr(ctx.decode_rows), c_int(nd), _ptr(ctx.positions), _ptr(ctx.row_slot),
-                _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(tb), c_int(tb.shape[1]), c_int(cache.block_size),
-                c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window or 0), _ptr(part_o), _ptr(part_ml),
-                c_int(n_splits), c_int(max_splits), self._stream())
-            self._check(code, "attention_decode_bf16")
+            maps = self._kv_tensor_maps(cache, nkv, hd) if not window and nq // nkv <= 8 else None
+            if maps:
+                # pages by TMA: head sizes 64 and 128, page sizes 8..256 that are powers of two, no window
+                code = self.lib("attention_decode_tma").zllm_attention_decode_tma(
+                    _ptr(qkv), _ptr(out), _ptr(ctx.decode_rows), c_int(nd), _ptr(ctx.positions), _ptr(ctx.row_slot),
+                    maps[0], maps[1], _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(tb), c_int(tb.shape[1]),
+                    c_int(cache.block_size), c_int(nq), c_int(nkv),
+                    c_int(hd), c_float(scale), _ptr(part_o), _ptr(part_ml), c_int(n_splits), c_int(max_splits),
+                    self._stream())
+                self._check(code, "attention_decode_tma")
+            else:
+                code = lib.zllm_attention_decode_bf16(
+                    _ptr(qkv), _ptr(out), _ptr(ctx.decode_rows), c_int(nd), _ptr(ctx.positions), _ptr(ctx.row_slot),
+                    _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(tb), c_int(tb.shape[1]), c_int(cache.block_size),
+                    c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window or 0), _ptr(part_o), _ptr(part_ml),
+                    c_int(n_splits), c_int(max_splits), self._stream())
+                self._check(code, "attention_decode_bf16")
             self.launches += 1                  # split kernel + combine kernel
         if ctx.n_tiles > 0:
             code = lib.zllm_attention_prefill_bf16(
