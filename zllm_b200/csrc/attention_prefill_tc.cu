@@ -1,0 +1,442 @@
+// Prefill attention over the paged cache on the 5th-generation tensor cores.
+//
+// One CTA per (tile of up to 128 query rows of a portion, query head).  Per block of 128 keys:
+//   S = Q K^T      tcgen05.mma, M = 128 rows, N = 128 keys, K = head_dim, S float32 in tensor memory
+//   softmax        4 warps; tcgen05.ld gives each THREAD one whole row of S (lane = row), so the
+//                  row maximum and sum need no shuffles; masking only in blocks that touch the
+//                  diagonal; probabilities go to shared memory as bfloat16 in the K-major,
+//                  128-byte-swizzled layout of an MMA operand
+//   O += P V       tcgen05.mma, M = 128, N = head_dim, K = 128 keys, with V read in place as an
+//                  MN-major operand (the cache's [position][dim] rows ARE that layout), O float32
+//                  in tensor memory; O is rescaled in tensor memory only when a row's running
+//                  maximum moved
+// Q, and every page of K and V ([positions][64 dims] boxes of the pool's tensor map), come by
+// TMA from one producer warp; one thread issues the MMAs; mbarriers and tcgen05.commit connect
+// the three roles.  Two CTAs fit on an SM (head size 64), so one CTA's softmax runs beside the
+// other's products.  A portion that starts at position p attends the prefix 0..p-1 from the
+// cache and its own rows causally; its own keys and values are already in the cache.
+//
+// zllm's counterpart: coopmat_flash_attn.comp with its query offset
+// (src/backend/vulkan/mod.rs:1758-1777), whose math this follows.
+//
+// Takes head sizes 64 and 128, page sizes that are powers of two from 8 (16 for head size 128)
+// to 128, no window.  The pool must hold finite numbers everywhere (it is created zeroed).
+// Waits on mbarriers are bounded; a wait that runs out sets a flag the host reads.
+#include "common.cuh"
+#include <cuda.h>
+#include <math.h>
+#include <string.h>
+
+#define PT_ROWS 128
+#define PT_KEYS 128
+#define PT_THREADS 192
+#define PT_WAIT_LIMIT (1u << 24)
+
+__device__ int g_pt_error = 0;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int where) {
+    for (unsigned i = 0; i < PT_WAIT_LIMIT; ++i) {
+        unsigned done;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    atomicCAS(&g_pt_error, 0, 1 + where);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                       unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Operand tile in shared memory, 128-byte swizzle, rows of 128 bytes, 8-row groups 1024 bytes
+// apart.  K-major operands (Q, K, P): 64 elements of the contraction per row.  The MN-major
+// operand (V): 64 elements of N per row, the contraction runs over the rows; ``lbo`` is the
+// distance to the tile of the next 64 elements of N.
+__device__ __forceinline__ unsigned long long umma_desc(unsigned saddr, unsigned lbo_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((saddr >> 4) & 0x3FFF);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (unsigned long long)(1024 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ unsigned pack2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// tiles [n_tiles][4] = (first row, rows (<= 128), slot, position of first row)
+template <int HD>
+__global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ tiles,
+    const int* __restrict__ table, int max_blocks, int bs, int bs_shift, int box_rows, int nq, int nkv, float scale) {
+    constexpr int HALVES = HD / 64;                          // 64-element column boxes of a row
+    constexpr int HALF_BYTES = 128 * 128;                    // [128 rows][64 elements], swizzled
+    constexpr int TILE_BYTES = HALVES * HALF_BYTES;          // Q, K or V tile
+    constexpr int P_BYTES = 2 * HALF_BYTES;                  // [128 rows][128 keys] as two K-major halves
+    constexpr int TMEM_COLS = 256;                           // S: 128 columns, O: HD columns
+    extern __shared__ unsigned char smem_raw[];
+    const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const unsigned q_tile = base, k_tile = base + TILE_BYTES, v_tile = base + 2 * TILE_BYTES, p_tile = base + 3 * TILE_BYTES;
+    unsigned char* v_ptr = base_ptr + 2 * TILE_BYTES;
+    unsigned char* p_ptr = base_ptr + 3 * TILE_BYTES;
+    const unsigned bars = base + 3 * TILE_BYTES + P_BYTES;
+    const unsigned bar_q = bars, bar_k = bars + 8, bar_v = bars + 16, bar_s = bars + 24, bar_p = bars + 32, bar_o = bars + 40;
+    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(base_ptr + 3 * TILE_BYTES + P_BYTES + 48);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const int* tl = tiles + 4 * (gridDim.x - 1 - blockIdx.x);   // later tiles see more keys: start them first
+    const int row0 = tl[0], n_rows = tl[1], slot = tl[2], pos0 = tl[3];
+    const int h = blockIdx.y;
+    const int kvh = h / (nq / nkv);
+    const int* trow = table + (size_t)slot * max_blocks;
+    const int last_pos = pos0 + n_rows - 1;                  // last key any row of the tile sees
+    const int n_blocks = last_pos / PT_KEYS + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_q, 1);
+        mbar_init(bar_k, 1);                                 // keys landed: expect_tx arrive + bytes
+        mbar_init(bar_v, 1);                                 // values landed
+        mbar_init(bar_s, 1);                                 // S complete (and the K tile free): tcgen05.commit
+        mbar_init(bar_p, 4);                                 // P written, O rescaled: one arrive per softmax warp
+        mbar_init(bar_o, 1);                                 // O += P V complete (V and P free): tcgen05.commit
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + PT_KEYS;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (whole warp: lanes 0..15 key boxes, 16..31 value boxes) ----------------
+        if (lane == 0) {
+            mbar_expect_tx(bar_q, TILE_BYTES);
+            for (int hf = 0; hf < HALVES; ++hf)
+                tma_load_2d(q_tile + hf * HALF_BYTES, &map_q, h * HD + hf * 64, row0, bar_q);
+        }
+        const int n_box = (PT_KEYS / box_rows) * HALVES;
+        const int bidx = lane & 15, is_v = lane >> 4;
+        const int pb = bidx / HALVES, half = bidx - pb * HALVES;
+        const unsigned box_bytes = (unsigned)box_rows * 128u;
+        bool ok = true;
+        for (int kb = 0; kb < n_blocks && ok; ++kb) {
+            const int key_b0 = kb * PT_KEYS + pb * box_rows;
+            bool valid = bidx < n_box && key_b0 <= last_pos;
+            int y = 0;
+            if (valid) {
+                const int page = trow[key_b0 >> bs_shift];
+                valid = page >= 0;
+                y = (page * nkv + kvh) * bs + (key_b0 & (bs - 1));
+            }
+            const unsigned m = __ballot_sync(0xffffffffu, valid);
+            // keys: the tile is free when the S of the block before is complete
+            if (kb > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_s, (kb - 1) & 1, 0));
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(bar_k, (unsigned)__popc(m & 0xffffu) * box_bytes);
+            __syncwarp();
+            if (valid && !is_v) tma_load_2d(k_tile + half * HALF_BYTES + pb * box_rows * 128, &map_k, half * 64, y, bar_k);
+            // values: the tile is free when O += P V of the block before is complete
+            if (kb > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_o, (kb - 1) & 1, 1));
+            if (!ok) break;
+            // boxes that are not loaded must not hold garbage: probability 0 x NaN is NaN
+            bool zeroed = false;
+            for (int b = 0; b < n_box; ++b) {
+                if ((m >> (16 + b)) & 1u) continue;
+                const int pbb = b / HALVES, hb = b - pbb * HALVES;
+                uint4* z = reinterpret_cast<uint4*>(v_ptr + hb * HALF_BYTES + pbb * box_rows * 128);
+                for (int i = lane; i < box_rows * 8; i += 32) z[i] = make_uint4(0, 0, 0, 0);
+                zeroed = true;
+            }
+            if (zeroed) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_expect_tx(bar_v, (unsigned)__popc(m >> 16) * box_bytes);
+            __syncwarp();
+            if (valid && is_v) tma_load_2d(v_tile + half * HALF_BYTES + pb * box_rows * 128, &map_v, half * 64, y, bar_v);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // D float32, A and B bfloat16; N >> 3 at [17,23), M >> 4 at [24,29); bit 16: B is MN-major
+            const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(PT_KEYS >> 3) << 17) |
+                                     ((unsigned)(PT_ROWS >> 4) << 24);
+            const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) |
+                                     ((unsigned)(PT_ROWS >> 4) << 24);
+            bool ok = mbar_wait(bar_q, 0, 2);
+            for (int kb = 0; kb < n_blocks && ok; ++kb) {
+                const unsigned ph = kb & 1;
+                ok = mbar_wait(bar_k, ph, 3);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {       // 32 bytes along the head per step
+                    const unsigned off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+                    tc_mma(tmem_s, umma_desc(q_tile + off, 16), umma_desc(k_tile + off, 16), idesc_s, ks > 0 ? 1u : 0u);
+                }
+                tc_commit(bar_s);
+                ok = mbar_wait(bar_p, ph, 4) && mbar_wait(bar_v, ph, 5);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int j = 0; j < PT_KEYS / 16; ++j) {     // 16 keys per step: 32 bytes of a P row, 16 rows of V
+                    const unsigned p_off = (j >> 2) * HALF_BYTES + (j & 3) * 32;
+                    tc_mma(tmem_o, umma_desc(p_tile + p_off, 16), umma_desc(v_tile + j * 16 * 128, HALF_BYTES), idesc_o,
+                           (kb > 0 || j > 0) ? 1u : 0u);
+                }
+                tc_commit(bar_o);
+            }
+            if (!ok) { tc_commit(bar_s); tc_commit(bar_o); }
+        }
+    } else {
+        // ---------------- softmax: warps 2..5, thread = query row ----------------
+        const int q = warp & 3;
+        const int r = q * 32 + lane;                         // row of the tile = TMEM lane
+        const unsigned lane_base = (unsigned)(q * 32) << 16;
+        const int my_pos = pos0 + r;                         // the last key this row sees
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int kb = 0; kb < n_blocks; ++kb) {
+            const unsigned ph = kb & 1;
+            const int key0 = kb * PT_KEYS;
+            ok = ok && mbar_wait(bar_s, ph, 6);
+            tc_fence_after();
+            const bool masked = key0 + PT_KEYS - 1 > pos0;   // the block reaches past the first row's own key
+            // pass 1: the row's maximum over the block
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < PT_KEYS; c += 32) {
+                unsigned v[32];
+                tmem_ld32(tmem_s + lane_base + c, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float s = __uint_as_float(v[i]);
+                    if (masked && key0 + c + i > my_pos) s = -INFINITY;
+                    mx = fmaxf(mx, s);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx * scale);
+            const float corr = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_new);
+            const float msafe = (m_new == -INFINITY) ? 0.f : m_new;
+            m_run = m_new;
+            // O and the P tile are free once the products of the block before are complete
+            if (kb > 0) {
+                ok = ok && mbar_wait(bar_o, (kb - 1) & 1, 7);
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+                    for (int c = 0; c < HD; c += 32) {
+                        unsigned v[32];
+                        tmem_ld32(tmem_o + lane_base + c, v);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        tmem_st32(tmem_o + lane_base + c, v);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
+            }
+            // pass 2: probabilities, their sum, P as bfloat16 into the operand tile
+            float rs = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < PT_KEYS; c += 32) {
+                unsigned v[32];
+                tmem_ld32(tmem_s + lane_base + c, v);
+                float p[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float s = __uint_as_float(v[i]);
+                    if (masked && key0 + c + i > my_pos) s = -INFINITY;
+                    p[i] = ex2_approx(fmaf(s, scale, -msafe));           // 2^(-inf) = 0 for hidden keys
+                    rs += p[i];
+                }
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {                         // 16-byte chunks of 8 keys
+                    const int chunk = (c >> 3) + ch;                     // 0..15 along the 128 keys
+                    uint4 pk;
+                    pk.x = pack2(p[8 * ch], p[8 * ch + 1]);
+                    pk.y = pack2(p[8 * ch + 2], p[8 * ch + 3]);
+                    pk.z = pack2(p[8 * ch + 4], p[8 * ch + 5]);
+                    pk.w = pack2(p[8 * ch + 6], p[8 * ch + 7]);
+                    *reinterpret_cast<uint4*>(p_ptr + (chunk >> 3) * HALF_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = pk;
+                }
+            }
+            l_run = l_run * corr + rs;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the MMA reads P through the async proxy
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_p);
+        }
+        // the finished rows: O / l as bfloat16
+        ok = ok && mbar_wait(bar_o, (n_blocks - 1) & 1, 8);
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+            unsigned v[32];
+            tmem_ld32(tmem_o + lane_base + c, v);
+            if (r < n_rows && ok) {
+                bf16* o = out + ((size_t)(row0 + r) * nq + h) * HD + c;
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 pk;
+                    pk.x = pack2(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+                    pk.y = pack2(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                    pk.z = pack2(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+                    pk.w = pack2(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+                    *reinterpret_cast<uint4*>(o + i) = pk;
+                }
+            }
+        }
+        tc_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// rows x row_len bfloat16, row-major; boxes of box_rows x 64 elements, 128-byte swizzle, zero fill outside
+static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long row_len, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return ZLLM_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)row_len, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_len * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : ZLLM_ERR_UNSUPPORTED;
+}
+
+template <int HD>
+static int launch_prefill_tc(const void* qkv, int T, void* out, const int* tiles, int n_tiles, const void* k_pages,
+                             const void* v_pages, long long num_pages, const int* table, int max_blocks, int bs, int nq,
+                             int nkv, float scale, cudaStream_t s) {
+    const int box_rows = bs < PT_KEYS ? bs : PT_KEYS;
+    alignas(64) CUtensorMap mq, mk, mv;
+    int e = make_map(&mq, qkv, T, (long long)(nq + 2 * nkv) * HD, PT_ROWS);
+    if (e) return e;
+    e = make_map(&mk, k_pages, num_pages * nkv * bs, HD, box_rows);
+    if (e) return e;
+    e = make_map(&mv, v_pages, num_pages * nkv * bs, HD, box_rows);
+    if (e) return e;
+    const size_t smem = 1024 + 3 * (size_t)(HD / 64) * 128 * 128 + 2 * 128 * 128 + 64;
+    auto kern = prefill_tc_kernel<HD>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce != cudaSuccess) return (int)ce;
+        attr_set = true;
+    }
+    kern<<<dim3(n_tiles, nq), PT_THREADS, smem, s>>>(mq, mk, mv, (bf16*)out, tiles, table, max_blocks, bs,
+                                                       (int)__builtin_ctz(bs), box_rows, nq, nkv,
+                                                       scale * 1.4426950408889634f);
+    return launch_status();
+}
+
+// qkv [T][(nq + 2 nkv) hd] bfloat16 (only q is read), out [T][nq hd]; the pools [num_pages][nkv][bs][hd].
+// hd 64 or 128; bs a power of two, 8..128 (16..128 for hd 128); no window.
+ZLLM_API int zllm_attention_prefill_tc(const void* qkv, int T, void* out, const int* tiles, int n_tiles,
+                                       const void* k_pages, const void* v_pages, long long num_pages, const int* table,
+                                       int max_blocks, int bs, int nq, int nkv, int hd, float scale, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (nkv <= 0 || nq % nkv || nq > 65535 || bs < 8 || bs > 128 || (bs & (bs - 1)) || (hd == 128 && bs < 16) ||
+        (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15))
+        return ZLLM_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 64)
+        return launch_prefill_tc<64>(qkv, T, out, tiles, n_tiles, k_pages, v_pages, num_pages, table, max_blocks, bs, nq,
+                                     nkv, scale, s);
+    if (hd == 128)
+        return launch_prefill_tc<128>(qkv, T, out, tiles, n_tiles, k_pages, v_pages, num_pages, table, max_blocks, bs, nq,
+                                      nkv, scale, s);
+    return ZLLM_ERR_UNSUPPORTED;
+}
+
+// The device flag that a bounded wait sets when it gives up (0: none); reading clears it.
+ZLLM_API int zllm_attention_prefill_tc_error(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_pt_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_pt_error, &zero, sizeof(int));
+    return v;
+}

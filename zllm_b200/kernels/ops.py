@@ -57,7 +57,7 @@ class CudaOps:
         self.dtype = dtype
         names = ["elementwise", "gemm_plain", "attention_plain", "sampling"]
         if dtype == torch.bfloat16:
-            names += ["gemm_decode", "gemm_stream", "gemm_tc", "attention_bf16", "attention_decode_tma"]
+            names += ["gemm_decode", "gemm_stream", "gemm_tc", "attention_bf16", "attention_decode_tma", "attention_prefill_tc"]
         build.build(names)
         for n in names:
             self._libs[n] = build.load(n)
@@ -260,7 +260,8 @@ class CudaOps:
     def check_async_errors(self):
         """Raise if a kernel's bounded wait gave up since the last call (synchronises the device)."""
         for name, fn in (("gemm_tc", "zllm_gemm_tc_error"), ("gemm_stream", "zllm_gemm_stream_error"),
-                         ("attention_decode_tma", "zllm_attention_decode_tma_error")):
+                         ("attention_decode_tma", "zllm_attention_decode_tma_error"),
+                         ("attention_prefill_tc", "zllm_attention_prefill_tc_error")):
             lib = self._libs.get(name)
             if lib is not None:
                 v = getattr(lib, fn)()
@@ -391,7 +392,16 @@ class CudaOps:
                     c_int(n_splits), c_int(max_splits), self._stream())
                 self._check(code, "attention_decode_bf16")
             self.launches += 1                  # split kernel + combine kernel
-        if ctx.n_tiles > 0:
+        bs = cache.block_size
+        if ctx.n_tiles > 0 and not window and hd in (64, 128) and (16 if hd == 128 else 8) <= bs <= 128 \
+                and bs & (bs - 1) == 0:
+            # the tcgen05 kernel: Q and pages by TMA, S and O in tensor memory
+            code = self.lib("attention_prefill_tc").zllm_attention_prefill_tc(
+                _ptr(qkv), c_int(qkv.shape[0]), _ptr(out), _ptr(ctx.tiles), c_int(ctx.n_tiles), _ptr(cache.k_pages),
+                _ptr(cache.v_pages), c_longlong(cache.k_pages.shape[0]), _ptr(tb), c_int(tb.shape[1]), c_int(bs),
+                c_int(nq), c_int(nkv), c_int(hd), c_float(scale), self._stream())
+            self._check(code, "attention_prefill_tc")
+        elif ctx.n_tiles > 0:
             code = lib.zllm_attention_prefill_bf16(
                 _ptr(qkv), _ptr(out), _ptr(ctx.tiles), c_int(ctx.n_tiles), _ptr(cache.k_pages), _ptr(cache.v_pages),
                 _ptr(tb), c_int(tb.shape[1]), c_int(cache.block_size), c_int(nq), c_int(nkv), c_int(hd),
