@@ -1,19 +1,19 @@
 // Prefill attention over the paged cache on the 5th-generation tensor cores.
 //
-// One CTA per (tile of up to 128 query rows of a portion, query head).  Per block of 128 keys:
-//   S = Q K^T      tcgen05.mma, M = 128 rows, N = 128 keys, K = head_dim, S float32 in tensor memory
+// One CTA per (tile of up to 128 query rows of a portion, query head).  Per block of 64 keys:
+//   S = Q K^T      tcgen05.mma, M = 128 rows, N = 64 keys, K = head_dim, S float32 in tensor memory
 //   softmax        4 warps; tcgen05.ld gives each THREAD one whole row of S (lane = row), so the
 //                  row maximum and sum need no shuffles; masking only in blocks that touch the
 //                  diagonal; probabilities go to shared memory as bfloat16 in the K-major,
 //                  128-byte-swizzled layout of an MMA operand
-//   O += P V       tcgen05.mma, M = 128, N = head_dim, K = 128 keys, with V read in place as an
+//   O += P V       tcgen05.mma, M = 128, N = head_dim, K = 64 keys, with V read in place as an
 //                  MN-major operand (the cache's [position][dim] rows ARE that layout), O float32
 //                  in tensor memory; O is rescaled in tensor memory only when a row's running
 //                  maximum moved
 // Q, and every page of K and V ([positions][64 dims] boxes of the pool's tensor map), come by
 // TMA from one producer warp; one thread issues the MMAs; mbarriers and tcgen05.commit connect
-// the three roles.  Two CTAs fit on an SM (head size 64), so one CTA's softmax runs beside the
-// other's products.  A portion that starts at position p attends the prefix 0..p-1 from the
+// the three roles.  Blocks alternate between two sets of buffers, so S of the next block is
+// computed while the softmax warps work on this one; two CTAs fit on an SM (head size 64).  A portion that starts at position p attends the prefix 0..p-1 from the
 // cache and its own rows causally; its own keys and values are already in the cache.
 //
 // zllm's counterpart: coopmat_flash_attn.comp with its query offset
@@ -28,9 +28,10 @@
 #include <string.h>
 
 #define PT_ROWS 128
-#define PT_KEYS 128
+#define PT_KEYS 64                      // keys per block: S has PT_KEYS columns of tensor memory
 #define PT_THREADS 192
-#define PT_WAIT_LIMIT (1u << 24)
+#define PT_LAZY 8.0f                     // see m_ref in the kernel
+#define PT_WAIT_LIMIT (1u << 22)
 
 __device__ int g_pt_error = 0;
 
@@ -98,6 +99,16 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld32_nowait(unsigned taddr, unsigned (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -119,25 +130,40 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 }
 
 // tiles [n_tiles][4] = (first row, rows (<= 128), slot, position of first row)
+//
+// Blocks alternate between two sets of buffers (S in tensor memory; K, V and P in shared
+// memory), so the tensor core computes S of block kb + 1 while the softmax warps work on block
+// kb, and O += P V of block kb runs beside the softmax of block kb + 1.  Block kb uses set
+// kb & 1; the barriers of a set are in their phase kb >> 1.
 template <int HD>
 __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ tiles,
     const int* __restrict__ table, int max_blocks, int bs, int bs_shift, int box_rows, int nq, int nkv, float scale) {
     constexpr int HALVES = HD / 64;                          // 64-element column boxes of a row
-    constexpr int HALF_BYTES = 128 * 128;                    // [128 rows][64 elements], swizzled
-    constexpr int TILE_BYTES = HALVES * HALF_BYTES;          // Q, K or V tile
-    constexpr int P_BYTES = 2 * HALF_BYTES;                  // [128 rows][128 keys] as two K-major halves
-    constexpr int TMEM_COLS = 256;                           // S: 128 columns, O: HD columns
+    constexpr int QHALF = PT_ROWS * 128;                     // [128 rows][64 elements], swizzled (Q, P)
+    constexpr int KHALF = PT_KEYS * 128;                     // [PT_KEYS keys][64 elements], swizzled (K, V)
+    constexpr int Q_BYTES = HALVES * QHALF;
+    constexpr int KV_BYTES = HALVES * KHALF;
+    constexpr int P_BYTES = (PT_KEYS / 64) * QHALF;          // [128 rows][PT_KEYS keys] as K-major halves of 64 keys
+    constexpr int TMEM_COLS = 256;                           // S: 2 x PT_KEYS columns, O: HD columns
+    static_assert(2 * PT_KEYS + HD <= TMEM_COLS, "tensor memory");
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    const unsigned q_tile = base, k_tile = base + TILE_BYTES, v_tile = base + 2 * TILE_BYTES, p_tile = base + 3 * TILE_BYTES;
-    unsigned char* v_ptr = base_ptr + 2 * TILE_BYTES;
-    unsigned char* p_ptr = base_ptr + 3 * TILE_BYTES;
-    const unsigned bars = base + 3 * TILE_BYTES + P_BYTES;
-    const unsigned bar_q = bars, bar_k = bars + 8, bar_v = bars + 16, bar_s = bars + 24, bar_p = bars + 32, bar_o = bars + 40;
-    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(base_ptr + 3 * TILE_BYTES + P_BYTES + 48);
+    // Q | K0 K1 | V0 V1 | P0 P1 | barriers
+    const unsigned q_tile = base, k_tiles = base + Q_BYTES, v_tiles = k_tiles + 2 * KV_BYTES, p_tiles = v_tiles + 2 * KV_BYTES;
+    unsigned char* v_ptr = base_ptr + Q_BYTES + 2 * KV_BYTES;
+    unsigned char* p_ptr = base_ptr + Q_BYTES + 4 * KV_BYTES;
+    const unsigned bars = p_tiles + 2 * P_BYTES;
+    // per set b: keys landed, values landed, S complete (K free), P written (S free, O rescaled), O += P V complete
+    const unsigned bar_q = bars;
+    auto bar_k = [&](int b) { return bars + 8 + 8 * b; };
+    auto bar_v = [&](int b) { return bars + 24 + 8 * b; };
+    auto bar_s = [&](int b) { return bars + 40 + 8 * b; };
+    auto bar_p = [&](int b) { return bars + 56 + 8 * b; };
+    auto bar_o = [&](int b) { return bars + 72 + 8 * b; };
+    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(p_ptr + 2 * P_BYTES + 88);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     const int* tl = tiles + 4 * (gridDim.x - 1 - blockIdx.x);   // later tiles see more keys: start them first
@@ -150,11 +176,13 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1);
-        mbar_init(bar_k, 1);                                 // keys landed: expect_tx arrive + bytes
-        mbar_init(bar_v, 1);                                 // values landed
-        mbar_init(bar_s, 1);                                 // S complete (and the K tile free): tcgen05.commit
-        mbar_init(bar_p, 4);                                 // P written, O rescaled: one arrive per softmax warp
-        mbar_init(bar_o, 1);                                 // O += P V complete (V and P free): tcgen05.commit
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_k(b), 1);                          // expect_tx arrive + bytes
+            mbar_init(bar_v(b), 1);
+            mbar_init(bar_s(b), 1);                          // tcgen05.commit
+            mbar_init(bar_p(b), 4);                          // one arrive per softmax warp
+            mbar_init(bar_o(b), 1);                          // tcgen05.commit
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
@@ -168,14 +196,14 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + PT_KEYS;
+    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 2 * PT_KEYS;
 
     if (warp == 0) {
         // ---------------- TMA producer (whole warp: lanes 0..15 key boxes, 16..31 value boxes) ----------------
         if (lane == 0) {
-            mbar_expect_tx(bar_q, TILE_BYTES);
+            mbar_expect_tx(bar_q, Q_BYTES);
             for (int hf = 0; hf < HALVES; ++hf)
-                tma_load_2d(q_tile + hf * HALF_BYTES, &map_q, h * HD + hf * 64, row0, bar_q);
+                tma_load_2d(q_tile + hf * QHALF, &map_q, h * HD + hf * 64, row0, bar_q);
         }
         const int n_box = (PT_KEYS / box_rows) * HALVES;
         const int bidx = lane & 15, is_v = lane >> 4;
@@ -183,6 +211,8 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
         const unsigned box_bytes = (unsigned)box_rows * 128u;
         bool ok = true;
         for (int kb = 0; kb < n_blocks && ok; ++kb) {
+            const int b = kb & 1;
+            const unsigned prev = ((kb >> 1) & 1) ^ 1;       // parity of the phase in which block kb - 2 used the set
             const int key_b0 = kb * PT_KEYS + pb * box_rows;
             bool valid = bidx < n_box && key_b0 <= last_pos;
             int y = 0;
@@ -192,29 +222,31 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
                 y = (page * nkv + kvh) * bs + (key_b0 & (bs - 1));
             }
             const unsigned m = __ballot_sync(0xffffffffu, valid);
-            // keys: the tile is free when the S of the block before is complete
-            if (kb > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_s, (kb - 1) & 1, 0));
+            // keys: the tile is free when S of block kb - 2 is complete
+            if (kb >= 2) ok = __all_sync(0xffffffffu, mbar_wait(bar_s(b), prev, 0));
             if (!ok) break;
-            if (lane == 0) mbar_expect_tx(bar_k, (unsigned)__popc(m & 0xffffu) * box_bytes);
+            if (lane == 0) mbar_expect_tx(bar_k(b), (unsigned)__popc(m & 0xffffu) * box_bytes);
             __syncwarp();
-            if (valid && !is_v) tma_load_2d(k_tile + half * HALF_BYTES + pb * box_rows * 128, &map_k, half * 64, y, bar_k);
-            // values: the tile is free when O += P V of the block before is complete
-            if (kb > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_o, (kb - 1) & 1, 1));
+            if (valid && !is_v)
+                tma_load_2d(k_tiles + b * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_k, half * 64, y, bar_k(b));
+            // values: the tile is free when O += P V of block kb - 2 is complete
+            if (kb >= 2) ok = __all_sync(0xffffffffu, mbar_wait(bar_o(b), prev, 1));
             if (!ok) break;
             // boxes that are not loaded must not hold garbage: probability 0 x NaN is NaN
             bool zeroed = false;
-            for (int b = 0; b < n_box; ++b) {
-                if ((m >> (16 + b)) & 1u) continue;
-                const int pbb = b / HALVES, hb = b - pbb * HALVES;
-                uint4* z = reinterpret_cast<uint4*>(v_ptr + hb * HALF_BYTES + pbb * box_rows * 128);
+            for (int bx = 0; bx < n_box; ++bx) {
+                if ((m >> (16 + bx)) & 1u) continue;
+                const int pbb = bx / HALVES, hb = bx - pbb * HALVES;
+                uint4* z = reinterpret_cast<uint4*>(v_ptr + b * KV_BYTES + hb * KHALF + pbb * box_rows * 128);
                 for (int i = lane; i < box_rows * 8; i += 32) z[i] = make_uint4(0, 0, 0, 0);
                 zeroed = true;
             }
             if (zeroed) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_expect_tx(bar_v, (unsigned)__popc(m >> 16) * box_bytes);
+            if (lane == 0) mbar_expect_tx(bar_v(b), (unsigned)__popc(m >> 16) * box_bytes);
             __syncwarp();
-            if (valid && is_v) tma_load_2d(v_tile + half * HALF_BYTES + pb * box_rows * 128, &map_v, half * 64, y, bar_v);
+            if (valid && is_v)
+                tma_load_2d(v_tiles + b * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_v, half * 64, y, bar_v(b));
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -224,30 +256,37 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
                                      ((unsigned)(PT_ROWS >> 4) << 24);
             const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) |
                                      ((unsigned)(PT_ROWS >> 4) << 24);
+            // S[kb & 1] = Q K(kb)^T
+            auto issue_s = [&](int kb) -> bool {
+                const int b = kb & 1;
+                if (!mbar_wait(bar_k(b), (kb >> 1) & 1, 3)) return false;
+                tc_fence_after();
+                const unsigned kt = k_tiles + b * KV_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks)         // 32 bytes along the head per step
+                    tc_mma(tmem_s + b * PT_KEYS, umma_desc(q_tile + (ks >> 2) * QHALF + (ks & 3) * 32, 16),
+                           umma_desc(kt + (ks >> 2) * KHALF + (ks & 3) * 32, 16), idesc_s, ks > 0 ? 1u : 0u);
+                tc_commit(bar_s(b));
+                return true;
+            };
             bool ok = mbar_wait(bar_q, 0, 2);
+            ok = ok && issue_s(0);
+            if (n_blocks > 1) ok = ok && issue_s(1);
             for (int kb = 0; kb < n_blocks && ok; ++kb) {
-                const unsigned ph = kb & 1;
-                ok = mbar_wait(bar_k, ph, 3);
+                const int b = kb & 1;
+                const unsigned ph = (kb >> 1) & 1;
+                ok = mbar_wait(bar_p(b), ph, 4) && mbar_wait(bar_v(b), ph, 5);
                 if (!ok) break;
                 tc_fence_after();
+                const unsigned pt = p_tiles + b * P_BYTES, vt = v_tiles + b * KV_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {       // 32 bytes along the head per step
-                    const unsigned off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-                    tc_mma(tmem_s, umma_desc(q_tile + off, 16), umma_desc(k_tile + off, 16), idesc_s, ks > 0 ? 1u : 0u);
-                }
-                tc_commit(bar_s);
-                ok = mbar_wait(bar_p, ph, 4) && mbar_wait(bar_v, ph, 5);
-                if (!ok) break;
-                tc_fence_after();
-#pragma unroll
-                for (int j = 0; j < PT_KEYS / 16; ++j) {     // 16 keys per step: 32 bytes of a P row, 16 rows of V
-                    const unsigned p_off = (j >> 2) * HALF_BYTES + (j & 3) * 32;
-                    tc_mma(tmem_o, umma_desc(p_tile + p_off, 16), umma_desc(v_tile + j * 16 * 128, HALF_BYTES), idesc_o,
-                           (kb > 0 || j > 0) ? 1u : 0u);
-                }
-                tc_commit(bar_o);
+                for (int j = 0; j < PT_KEYS / 16; ++j)       // 16 keys per step: 32 bytes of a P row, 16 rows of V
+                    tc_mma(tmem_o, umma_desc(pt + (j >> 2) * QHALF + (j & 3) * 32, 16), umma_desc(vt + j * 16 * 128, KHALF),
+                           idesc_o, (kb > 0 || j > 0) ? 1u : 0u);
+                tc_commit(bar_o(b));
+                if (kb + 2 < n_blocks) ok = issue_s(kb + 2);  // S[b] is free: the softmax warps have read block kb
             }
-            if (!ok) { tc_commit(bar_s); tc_commit(bar_o); }
+            if (!ok) for (int b = 0; b < 2; ++b) { tc_commit(bar_s(b)); tc_commit(bar_o(b)); }
         }
     } else {
         // ---------------- softmax: warps 2..5, thread = query row ----------------
@@ -255,36 +294,47 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
         const int r = q * 32 + lane;                         // row of the tile = TMEM lane
         const unsigned lane_base = (unsigned)(q * 32) << 16;
         const int my_pos = pos0 + r;                         // the last key this row sees
-        float m_run = -INFINITY, l_run = 0.f;
+        // m_ref: the maximum the row's exponents refer to.  It follows the true running maximum
+        // only when that has moved by more than PT_LAZY (in log2 units): until then the
+        // probabilities of a block are at most 2^PT_LAZY, exact in float32 sums and well inside
+        // bfloat16's range, O needs no rescaling, and this block does not have to wait for the
+        // products of the block before.  The final O / l is the same whatever reference was used.
+        float m_ref = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int kb = 0; kb < n_blocks; ++kb) {
-            const unsigned ph = kb & 1;
+            const int b = kb & 1;
+            const unsigned ph = (kb >> 1) & 1;
             const int key0 = kb * PT_KEYS;
-            ok = ok && mbar_wait(bar_s, ph, 6);
+            const unsigned s_addr = tmem_s + b * PT_KEYS + lane_base;
+            ok = ok && mbar_wait(bar_s(b), ph, 6);
             tc_fence_after();
             const bool masked = key0 + PT_KEYS - 1 > pos0;   // the block reaches past the first row's own key
-            // pass 1: the row's maximum over the block
-            float mx = -INFINITY;
-#pragma unroll 1
+            // the row's scores of the block, once, into registers
+            float sv[PT_KEYS];
+#pragma unroll
             for (int c = 0; c < PT_KEYS; c += 32) {
                 unsigned v[32];
-                tmem_ld32(tmem_s + lane_base + c, v);
+                tmem_ld32_nowait(s_addr + c, v);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(v[i]);
-                    if (masked && key0 + c + i > my_pos) s = -INFINITY;
-                    mx = fmaxf(mx, s);
-                }
+                for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(v[i]);
             }
-            const float m_new = fmaxf(m_run, mx * scale);
-            const float corr = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_new);
-            const float msafe = (m_new == -INFINITY) ? 0.f : m_new;
-            m_run = m_new;
-            // O and the P tile are free once the products of the block before are complete
-            if (kb > 0) {
-                ok = ok && mbar_wait(bar_o, (kb - 1) & 1, 7);
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float mx = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < PT_KEYS; ++i) {
+                if (masked && key0 + i > my_pos) sv[i] = -INFINITY;
+                mx = fmaxf(mx, sv[i]);
+            }
+            const float m_blk = mx * scale;
+            if (__any_sync(0xffffffffu, m_blk > m_ref + PT_LAZY)) {
+                // (warp-uniform) move the reference to the true maximum and rescale O and l
+                const float m_new = fmaxf(m_ref, m_blk);
+                const float corr = (m_ref == -INFINITY) ? 0.f : ex2_approx(m_ref - m_new);
+                m_ref = m_new;
+                l_run *= corr;
+                if (kb > 0) {
+                    ok = ok && mbar_wait(bar_o((kb - 1) & 1), ((kb - 1) >> 1) & 1, 7);   // O is complete up to block kb - 1
+                    tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < HD; c += 32) {
                         unsigned v[32];
@@ -296,39 +346,34 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
             }
-            // pass 2: probabilities, their sum, P as bfloat16 into the operand tile
+            const float msafe = (m_ref == -INFINITY) ? 0.f : m_ref;
+            // P[b] was last read by the products of block kb - 2
+            if (kb >= 2) ok = ok && mbar_wait(bar_o(b), ph ^ 1, 9);
+            unsigned char* pt = p_ptr + b * P_BYTES;
             float rs = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < PT_KEYS; c += 32) {
-                unsigned v[32];
-                tmem_ld32(tmem_s + lane_base + c, v);
-                float p[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(v[i]);
-                    if (masked && key0 + c + i > my_pos) s = -INFINITY;
-                    p[i] = ex2_approx(fmaf(s, scale, -msafe));           // 2^(-inf) = 0 for hidden keys
+            for (int ch = 0; ch < PT_KEYS / 8; ++ch) {                       // 16-byte chunks of 8 keys
+                float p[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    p[i] = ex2_approx(fmaf(sv[8 * ch + i], scale, -msafe));  // 2^(-inf) = 0 for hidden keys
                     rs += p[i];
                 }
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {                         // 16-byte chunks of 8 keys
-                    const int chunk = (c >> 3) + ch;                     // 0..15 along the 128 keys
-                    uint4 pk;
-                    pk.x = pack2(p[8 * ch], p[8 * ch + 1]);
-                    pk.y = pack2(p[8 * ch + 2], p[8 * ch + 3]);
-                    pk.z = pack2(p[8 * ch + 4], p[8 * ch + 5]);
-                    pk.w = pack2(p[8 * ch + 6], p[8 * ch + 7]);
-                    *reinterpret_cast<uint4*>(p_ptr + (chunk >> 3) * HALF_BYTES + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = pk;
-                }
+                uint4 pk;
+                pk.x = pack2(p[0], p[1]);
+                pk.y = pack2(p[2], p[3]);
+                pk.z = pack2(p[4], p[5]);
+                pk.w = pack2(p[6], p[7]);
+                *reinterpret_cast<uint4*>(pt + (ch >> 3) * QHALF + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = pk;
             }
-            l_run = l_run * corr + rs;
+            l_run += rs;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the MMA reads P through the async proxy
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_p);
+            if (lane == 0) mbar_arrive(bar_p(b));
         }
         // the finished rows: O / l as bfloat16
-        ok = ok && mbar_wait(bar_o, (n_blocks - 1) & 1, 8);
+        ok = ok && mbar_wait(bar_o((n_blocks - 1) & 1), ((n_blocks - 1) >> 1) & 1, 8);
         tc_fence_after();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll 1
@@ -400,7 +445,7 @@ static int launch_prefill_tc(const void* qkv, int T, void* out, const int* tiles
     if (e) return e;
     e = make_map(&mv, v_pages, num_pages * nkv * bs, HD, box_rows);
     if (e) return e;
-    const size_t smem = 1024 + 3 * (size_t)(HD / 64) * 128 * 128 + 2 * 128 * 128 + 64;
+    const size_t smem = 1024 + (size_t)(HD / 64) * (PT_ROWS + 4 * PT_KEYS) * 128 + 2 * (size_t)(PT_KEYS / 64) * PT_ROWS * 128 + 128;
     auto kern = prefill_tc_kernel<HD>;
     static bool attr_set = false;
     if (!attr_set) {
