@@ -492,9 +492,11 @@ __global__ void __launch_bounds__(NWARPS * 32, MT == 2 ? 2 : 1) prefill_kernel(
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* kbuf = reinterpret_cast<bf16*>(smem_raw);          // [PF_STAGES][PF_KEYS][STR]
     bf16* vbuf = kbuf + PF_STAGES * PF_KEYS * STR;           // [PF_STAGES][PF_KEYS][STR]
-    const int* tl = tiles + 4 * (gridDim.x - 1 - blockIdx.x);   // later tiles see more keys: start them first
+    // heads run fastest over the grid and later tiles (which see more keys) come first: the CTAs
+    // with the most work start first for ALL heads and the short ones fill the tail
+    const int* tl = tiles + 4 * (gridDim.y - 1 - blockIdx.y);
     const int row0 = tl[0], n_rows = tl[1], slot = tl[2], pos0 = tl[3];
-    const int h = blockIdx.y;
+    const int h = blockIdx.x;
     const int kvh = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int* trow = table + (size_t)slot * max_blocks;
@@ -593,7 +595,7 @@ static int launch_prefill(const void* qkv, void* out, const int* tiles, int n_ti
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const int bs_shift = (bs & (bs - 1)) == 0 ? __builtin_ctz(bs) : -1;
-    kern<<<dim3(n_tiles, nq), NWARPS * 32, smem, s>>>((const bf16*)qkv, (bf16*)out, tiles, (const bf16*)k_pages,
+    kern<<<dim3(nq, n_tiles), NWARPS * 32, smem, s>>>((const bf16*)qkv, (bf16*)out, tiles, (const bf16*)k_pages,
                                                       (const bf16*)v_pages, table, max_blocks, bs, bs_shift, nq, nkv,
                                                       scale * 1.4426950408889634f, window);
     return launch_status();
@@ -604,7 +606,7 @@ ZLLM_API int zllm_attention_prefill_bf16(const void* qkv, void* out, const int* 
                                          const void* k_pages, const void* v_pages, const int* table, int max_blocks,
                                          int bs, int nq, int nkv, int hd, float scale, int window, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (nkv <= 0 || nq % nkv || nq > 65535) return ZLLM_ERR_UNSUPPORTED;
+    if (nkv <= 0 || nq % nkv || n_tiles > 65535) return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     DISPATCH_HD(hd, (launch_prefill<H_>(qkv, out, tiles, n_tiles, k_pages, v_pages, table, max_blocks, bs, nq, nkv,
                                         scale, window, s)))

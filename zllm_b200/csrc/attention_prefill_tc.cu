@@ -2,8 +2,9 @@
 //
 // One CTA per (tile of up to 128 query rows of a portion, query head).  Per block of 64 keys:
 //   S = Q K^T      tcgen05.mma, M = 128 rows, N = 64 keys, K = head_dim, S float32 in tensor memory
-//   softmax        4 warps; tcgen05.ld gives each THREAD one whole row of S (lane = row), so the
-//                  row maximum and sum need no shuffles; masking only in blocks that touch the
+//   softmax        8 warps; tcgen05.ld gives a THREAD half a row of S (lane = row), so the row
+//                  maximum and sum need no shuffles, one exchange between the two threads of a
+//                  row through shared memory; masking only in blocks that touch the
 //                  diagonal; probabilities go to shared memory as bfloat16 in the K-major,
 //                  128-byte-swizzled layout of an MMA operand
 //   O += P V       tcgen05.mma, M = 128, N = head_dim, K = 64 keys, with V read in place as an
@@ -29,7 +30,8 @@
 
 #define PT_ROWS 128
 #define PT_KEYS 64                      // keys per block: S has PT_KEYS columns of tensor memory
-#define PT_THREADS 192
+#define PT_THREADS 320                  // TMA warp, MMA warp, 8 softmax warps
+#define PT_STAGES 3                     // K/V tiles in flight
 #define PT_LAZY 8.0f                     // see m_ref in the kernel
 #define PT_WAIT_LIMIT (1u << 22)
 
@@ -151,24 +153,31 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    // Q | K0 K1 | V0 V1 | P0 P1 | barriers
-    const unsigned q_tile = base, k_tiles = base + Q_BYTES, v_tiles = k_tiles + 2 * KV_BYTES, p_tiles = v_tiles + 2 * KV_BYTES;
-    unsigned char* v_ptr = base_ptr + Q_BYTES + 2 * KV_BYTES;
-    unsigned char* p_ptr = base_ptr + Q_BYTES + 4 * KV_BYTES;
+    // Q | K ring | V ring | P0 P1 | barriers
+    constexpr int NS = PT_STAGES;
+    const unsigned q_tile = base, k_tiles = base + Q_BYTES, v_tiles = k_tiles + NS * KV_BYTES, p_tiles = v_tiles + NS * KV_BYTES;
+    unsigned char* v_ptr = base_ptr + Q_BYTES + NS * KV_BYTES;
+    unsigned char* p_ptr = base_ptr + Q_BYTES + 2 * NS * KV_BYTES;
     const unsigned bars = p_tiles + 2 * P_BYTES;
-    // per set b: keys landed, values landed, S complete (K free), P written (S free, O rescaled), O += P V complete
+    // ring stage st = kb % NS: keys landed, values landed, keys read (S complete), values read (O += P V complete);
+    // set b = kb & 1: S complete, P written (S read, O rescaled), O += P V complete
     const unsigned bar_q = bars;
-    auto bar_k = [&](int b) { return bars + 8 + 8 * b; };
-    auto bar_v = [&](int b) { return bars + 24 + 8 * b; };
-    auto bar_s = [&](int b) { return bars + 40 + 8 * b; };
-    auto bar_p = [&](int b) { return bars + 56 + 8 * b; };
-    auto bar_o = [&](int b) { return bars + 72 + 8 * b; };
-    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(p_ptr + 2 * P_BYTES + 88);
+    auto bar_k = [&](int st) { return bars + 8 * (1 + st); };
+    auto bar_v = [&](int st) { return bars + 8 * (1 + NS + st); };
+    auto bar_kfree = [&](int st) { return bars + 8 * (1 + 2 * NS + st); };
+    auto bar_vfree = [&](int st) { return bars + 8 * (1 + 3 * NS + st); };
+    auto bar_s = [&](int b) { return bars + 8 * (1 + 4 * NS + b); };
+    auto bar_p = [&](int b) { return bars + 8 * (3 + 4 * NS + b); };
+    auto bar_o = [&](int b) { return bars + 8 * (5 + 4 * NS + b); };
+    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(p_ptr + 2 * P_BYTES + 8 * (7 + 4 * NS));
+    float* xmax = reinterpret_cast<float*>(p_ptr + 2 * P_BYTES + 256);      // [2 sets][2 halves][128 rows] maxima, then [2 halves][128 rows] sums
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    const int* tl = tiles + 4 * (gridDim.x - 1 - blockIdx.x);   // later tiles see more keys: start them first
+    // Heads run fastest over the grid and later tiles (which see more keys) come first, so the
+    // CTAs with the most work start first for ALL heads and the short ones fill the tail.
+    const int* tl = tiles + 4 * (gridDim.y - 1 - blockIdx.y);
     const int row0 = tl[0], n_rows = tl[1], slot = tl[2], pos0 = tl[3];
-    const int h = blockIdx.y;
+    const int h = blockIdx.x;
     const int kvh = h / (nq / nkv);
     const int* trow = table + (size_t)slot * max_blocks;
     const int last_pos = pos0 + n_rows - 1;                  // last key any row of the tile sees
@@ -176,11 +185,15 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
 
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1);
+        for (int st = 0; st < NS; ++st) {
+            mbar_init(bar_k(st), 1);                         // expect_tx arrive + bytes
+            mbar_init(bar_v(st), 1);
+            mbar_init(bar_kfree(st), 1);                     // tcgen05.commit
+            mbar_init(bar_vfree(st), 1);
+        }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(bar_k(b), 1);                          // expect_tx arrive + bytes
-            mbar_init(bar_v(b), 1);
             mbar_init(bar_s(b), 1);                          // tcgen05.commit
-            mbar_init(bar_p(b), 4);                          // one arrive per softmax warp
+            mbar_init(bar_p(b), 8);                          // one arrive per softmax warp
             mbar_init(bar_o(b), 1);                          // tcgen05.commit
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -211,8 +224,8 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
         const unsigned box_bytes = (unsigned)box_rows * 128u;
         bool ok = true;
         for (int kb = 0; kb < n_blocks && ok; ++kb) {
-            const int b = kb & 1;
-            const unsigned prev = ((kb >> 1) & 1) ^ 1;       // parity of the phase in which block kb - 2 used the set
+            const int st = kb % NS;
+            const unsigned prev = ((kb / NS) & 1) ^ 1;       // parity of the phase in which block kb - NS used the stage
             const int key_b0 = kb * PT_KEYS + pb * box_rows;
             bool valid = bidx < n_box && key_b0 <= last_pos;
             int y = 0;
@@ -222,31 +235,31 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
                 y = (page * nkv + kvh) * bs + (key_b0 & (bs - 1));
             }
             const unsigned m = __ballot_sync(0xffffffffu, valid);
-            // keys: the tile is free when S of block kb - 2 is complete
-            if (kb >= 2) ok = __all_sync(0xffffffffu, mbar_wait(bar_s(b), prev, 0));
+            // keys: the stage is free when S of block kb - NS is complete
+            if (kb >= NS) ok = __all_sync(0xffffffffu, mbar_wait(bar_kfree(st), prev, 0));
             if (!ok) break;
-            if (lane == 0) mbar_expect_tx(bar_k(b), (unsigned)__popc(m & 0xffffu) * box_bytes);
+            if (lane == 0) mbar_expect_tx(bar_k(st), (unsigned)__popc(m & 0xffffu) * box_bytes);
             __syncwarp();
             if (valid && !is_v)
-                tma_load_2d(k_tiles + b * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_k, half * 64, y, bar_k(b));
-            // values: the tile is free when O += P V of block kb - 2 is complete
-            if (kb >= 2) ok = __all_sync(0xffffffffu, mbar_wait(bar_o(b), prev, 1));
+                tma_load_2d(k_tiles + st * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_k, half * 64, y, bar_k(st));
+            // values: the stage is free when O += P V of block kb - NS is complete
+            if (kb >= NS) ok = __all_sync(0xffffffffu, mbar_wait(bar_vfree(st), prev, 1));
             if (!ok) break;
             // boxes that are not loaded must not hold garbage: probability 0 x NaN is NaN
             bool zeroed = false;
             for (int bx = 0; bx < n_box; ++bx) {
                 if ((m >> (16 + bx)) & 1u) continue;
                 const int pbb = bx / HALVES, hb = bx - pbb * HALVES;
-                uint4* z = reinterpret_cast<uint4*>(v_ptr + b * KV_BYTES + hb * KHALF + pbb * box_rows * 128);
+                uint4* z = reinterpret_cast<uint4*>(v_ptr + st * KV_BYTES + hb * KHALF + pbb * box_rows * 128);
                 for (int i = lane; i < box_rows * 8; i += 32) z[i] = make_uint4(0, 0, 0, 0);
                 zeroed = true;
             }
             if (zeroed) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_expect_tx(bar_v(b), (unsigned)__popc(m >> 16) * box_bytes);
+            if (lane == 0) mbar_expect_tx(bar_v(st), (unsigned)__popc(m >> 16) * box_bytes);
             __syncwarp();
             if (valid && is_v)
-                tma_load_2d(v_tiles + b * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_v, half * 64, y, bar_v(b));
+                tma_load_2d(v_tiles + st * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_v, half * 64, y, bar_v(st));
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -258,39 +271,46 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
                                      ((unsigned)(PT_ROWS >> 4) << 24);
             // S[kb & 1] = Q K(kb)^T
             auto issue_s = [&](int kb) -> bool {
-                const int b = kb & 1;
-                if (!mbar_wait(bar_k(b), (kb >> 1) & 1, 3)) return false;
+                const int b = kb & 1, st = kb % NS;
+                if (!mbar_wait(bar_k(st), (kb / NS) & 1, 3)) return false;
                 tc_fence_after();
-                const unsigned kt = k_tiles + b * KV_BYTES;
+                const unsigned kt = k_tiles + st * KV_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)         // 32 bytes along the head per step
                     tc_mma(tmem_s + b * PT_KEYS, umma_desc(q_tile + (ks >> 2) * QHALF + (ks & 3) * 32, 16),
                            umma_desc(kt + (ks >> 2) * KHALF + (ks & 3) * 32, 16), idesc_s, ks > 0 ? 1u : 0u);
                 tc_commit(bar_s(b));
+                tc_commit(bar_kfree(st));
                 return true;
             };
             bool ok = mbar_wait(bar_q, 0, 2);
             ok = ok && issue_s(0);
             if (n_blocks > 1) ok = ok && issue_s(1);
             for (int kb = 0; kb < n_blocks && ok; ++kb) {
-                const int b = kb & 1;
-                const unsigned ph = (kb >> 1) & 1;
-                ok = mbar_wait(bar_p(b), ph, 4) && mbar_wait(bar_v(b), ph, 5);
+                const int b = kb & 1, st = kb % NS;
+                ok = mbar_wait(bar_p(b), (kb >> 1) & 1, 4) && mbar_wait(bar_v(st), (kb / NS) & 1, 5);
                 if (!ok) break;
                 tc_fence_after();
-                const unsigned pt = p_tiles + b * P_BYTES, vt = v_tiles + b * KV_BYTES;
+                const unsigned pt = p_tiles + b * P_BYTES, vt = v_tiles + st * KV_BYTES;
 #pragma unroll
                 for (int j = 0; j < PT_KEYS / 16; ++j)       // 16 keys per step: 32 bytes of a P row, 16 rows of V
                     tc_mma(tmem_o, umma_desc(pt + (j >> 2) * QHALF + (j & 3) * 32, 16), umma_desc(vt + j * 16 * 128, KHALF),
                            idesc_o, (kb > 0 || j > 0) ? 1u : 0u);
                 tc_commit(bar_o(b));
+                tc_commit(bar_vfree(st));
                 if (kb + 2 < n_blocks) ok = issue_s(kb + 2);  // S[b] is free: the softmax warps have read block kb
             }
             if (!ok) for (int b = 0; b < 2; ++b) { tc_commit(bar_s(b)); tc_commit(bar_o(b)); }
+            if (!ok) for (int st = 0; st < NS; ++st) { tc_commit(bar_kfree(st)); tc_commit(bar_vfree(st)); }
         }
     } else {
-        // ---------------- softmax: warps 2..5, thread = query row ----------------
-        const int q = warp & 3;
+        // ---------------- softmax: warps 2..9, two threads per query row ----------------
+        // Warps w and w + 4 share the 32 rows of TMEM lane quadrant w & 3; ``half`` says which half
+        // of a block's keys (and, for O, of the head's dims) a thread takes.  The two threads of a
+        // row exchange their half-maxima through shared memory (one named barrier per quadrant).
+        constexpr int HK = PT_KEYS / 2;                      // keys of a block per thread
+        constexpr int HO = HD / 2;                           // dims of O per thread
+        const int q = warp & 3, half = (warp - 2) >> 2;
         const int r = q * 32 + lane;                         // row of the tile = TMEM lane
         const unsigned lane_base = (unsigned)(q * 32) << 16;
         const int my_pos = pos0 + r;                         // the last key this row sees
@@ -299,35 +319,39 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
         // probabilities of a block are at most 2^PT_LAZY, exact in float32 sums and well inside
         // bfloat16's range, O needs no rescaling, and this block does not have to wait for the
         // products of the block before.  The final O / l is the same whatever reference was used.
-        float m_ref = -INFINITY, l_run = 0.f;
+        float m_ref = -INFINITY, l_run = 0.f;                // l_run: this thread's half of the row's sum
         bool ok = true;
         for (int kb = 0; kb < n_blocks; ++kb) {
             const int b = kb & 1;
             const unsigned ph = (kb >> 1) & 1;
-            const int key0 = kb * PT_KEYS;
-            const unsigned s_addr = tmem_s + b * PT_KEYS + lane_base;
+            const int key0 = kb * PT_KEYS + half * HK;       // first key of this thread's half
             ok = ok && mbar_wait(bar_s(b), ph, 6);
             tc_fence_after();
-            const bool masked = key0 + PT_KEYS - 1 > pos0;   // the block reaches past the first row's own key
-            // the row's scores of the block, once, into registers
-            float sv[PT_KEYS];
+            // the row's scores of this half, once, into registers
+            float sv[HK];
+            {
+                unsigned v[HK];
+                tmem_ld32(tmem_s + b * PT_KEYS + half * HK + lane_base, v);
 #pragma unroll
-            for (int c = 0; c < PT_KEYS; c += 32) {
-                unsigned v[32];
-                tmem_ld32_nowait(s_addr + c, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) sv[c + i] = __uint_as_float(v[i]);
+                for (int i = 0; i < HK; ++i) sv[i] = __uint_as_float(v[i]);
             }
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             float mx = -INFINITY;
+            if (kb * PT_KEYS + PT_KEYS - 1 > pos0) {         // the block reaches past the first row's own key
 #pragma unroll
-            for (int i = 0; i < PT_KEYS; ++i) {
-                if (masked && key0 + i > my_pos) sv[i] = -INFINITY;
-                mx = fmaxf(mx, sv[i]);
+                for (int i = 0; i < HK; ++i) {
+                    if (key0 + i > my_pos) sv[i] = -INFINITY;
+                    mx = fmaxf(mx, sv[i]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < HK; ++i) mx = fmaxf(mx, sv[i]);
             }
-            const float m_blk = mx * scale;
+            xmax[(b * 2 + half) * PT_ROWS + r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+            const float m_blk = fmaxf(mx, xmax[(b * 2 + (half ^ 1)) * PT_ROWS + r]) * scale;
             if (__any_sync(0xffffffffu, m_blk > m_ref + PT_LAZY)) {
-                // (warp-uniform) move the reference to the true maximum and rescale O and l
+                // (the same decision in both warps of the quadrant) move the reference to the true
+                // maximum and rescale l and this thread's half of O
                 const float m_new = fmaxf(m_ref, m_blk);
                 const float corr = (m_ref == -INFINITY) ? 0.f : ex2_approx(m_ref - m_new);
                 m_ref = m_new;
@@ -336,12 +360,12 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
                     ok = ok && mbar_wait(bar_o((kb - 1) & 1), ((kb - 1) >> 1) & 1, 7);   // O is complete up to block kb - 1
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c = 0; c < HD; c += 32) {
+                    for (int c = 0; c < HO; c += 32) {
                         unsigned v[32];
-                        tmem_ld32(tmem_o + lane_base + c, v);
+                        tmem_ld32(tmem_o + lane_base + half * HO + c, v);
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                        tmem_st32(tmem_o + lane_base + c, v);
+                        tmem_st32(tmem_o + lane_base + half * HO + c, v);
                     }
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
@@ -352,7 +376,7 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
             unsigned char* pt = p_ptr + b * P_BYTES;
             float rs = 0.f;
 #pragma unroll
-            for (int ch = 0; ch < PT_KEYS / 8; ++ch) {                       // 16-byte chunks of 8 keys
+            for (int ch = 0; ch < HK / 8; ++ch) {                            // 16-byte chunks of 8 keys
                 float p[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -364,7 +388,8 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
                 pk.y = pack2(p[2], p[3]);
                 pk.z = pack2(p[4], p[5]);
                 pk.w = pack2(p[6], p[7]);
-                *reinterpret_cast<uint4*>(pt + (ch >> 3) * QHALF + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = pk;
+                const int chunk = half * (HK / 8) + ch;                      // chunk of the block's PT_KEYS keys
+                *reinterpret_cast<uint4*>(pt + (chunk >> 3) * QHALF + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = pk;
             }
             l_run += rs;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the MMA reads P through the async proxy
@@ -372,16 +397,19 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_p(b));
         }
-        // the finished rows: O / l as bfloat16
+        // the finished rows: O / l as bfloat16, each thread its half of the dims
+        xmax[(4 + half) * PT_ROWS + r] = l_run;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+        const float l_row = l_run + xmax[(4 + (half ^ 1)) * PT_ROWS + r];
         ok = ok && mbar_wait(bar_o((n_blocks - 1) & 1), ((n_blocks - 1) >> 1) & 1, 8);
         tc_fence_after();
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
+        for (int c = 0; c < HO; c += 32) {
             unsigned v[32];
-            tmem_ld32(tmem_o + lane_base + c, v);
+            tmem_ld32(tmem_o + lane_base + half * HO + c, v);
             if (r < n_rows && ok) {
-                bf16* o = out + ((size_t)(row0 + r) * nq + h) * HD + c;
+                bf16* o = out + ((size_t)(row0 + r) * nq + h) * HD + half * HO + c;
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     uint4 pk;
@@ -445,7 +473,8 @@ static int launch_prefill_tc(const void* qkv, int T, void* out, const int* tiles
     if (e) return e;
     e = make_map(&mv, v_pages, num_pages * nkv * bs, HD, box_rows);
     if (e) return e;
-    const size_t smem = 1024 + (size_t)(HD / 64) * (PT_ROWS + 4 * PT_KEYS) * 128 + 2 * (size_t)(PT_KEYS / 64) * PT_ROWS * 128 + 128;
+    const size_t smem = 1024 + (size_t)(HD / 64) * (PT_ROWS + 2 * PT_STAGES * PT_KEYS) * 128 +
+                        2 * (size_t)(PT_KEYS / 64) * PT_ROWS * 128 + 256 + 6 * PT_ROWS * sizeof(float);
     auto kern = prefill_tc_kernel<HD>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -453,7 +482,7 @@ static int launch_prefill_tc(const void* qkv, int T, void* out, const int* tiles
         if (ce != cudaSuccess) return (int)ce;
         attr_set = true;
     }
-    kern<<<dim3(n_tiles, nq), PT_THREADS, smem, s>>>(mq, mk, mv, (bf16*)out, tiles, table, max_blocks, bs,
+    kern<<<dim3(nq, n_tiles), PT_THREADS, smem, s>>>(mq, mk, mv, (bf16*)out, tiles, table, max_blocks, bs,
                                                        (int)__builtin_ctz(bs), box_rows, nq, nkv,
                                                        scale * 1.4426950408889634f);
     return launch_status();
@@ -465,7 +494,7 @@ ZLLM_API int zllm_attention_prefill_tc(const void* qkv, int T, void* out, const 
                                        const void* k_pages, const void* v_pages, long long num_pages, const int* table,
                                        int max_blocks, int bs, int nq, int nkv, int hd, float scale, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (nkv <= 0 || nq % nkv || nq > 65535 || bs < 8 || bs > 128 || (bs & (bs - 1)) || (hd == 128 && bs < 16) ||
+    if (nkv <= 0 || nq % nkv || n_tiles > 65535 || bs < 8 || bs > 128 || (bs & (bs - 1)) || (hd == 128 && bs < 16) ||
         (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15))
         return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
