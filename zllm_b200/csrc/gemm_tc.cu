@@ -30,7 +30,7 @@
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_B_BYTES (TC_BN * TC_BK * 2)
 #define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
-#define TC_SMEM (TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */)
+#define TC_SMEM (TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */ + 4 * 2 * 4096 /* output staging */)
 #define TC_WAIT_LIMIT (1u << 24)
 
 __device__ int g_tc_error = 0;       // 0 ok; else 1 + index of the wait that gave up
@@ -86,6 +86,11 @@ __device__ __forceinline__ unsigned long long umma_desc(unsigned saddr) {
     return d;
 }
 
+__device__ __forceinline__ unsigned pack2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
 __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -98,12 +103,11 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// The epilogue of 32 accumulator columns (n0 + c .. n0 + c + 31) of output row m, from registers.
-__device__ __forceinline__ void tc_epilogue32(const unsigned (&r)[32], void* __restrict__ out, int m, int n0, int c, int N,
-                                              int mode, int out_bf16) {
+// The epilogue of 32 accumulator columns of one output row, written to the row's place in the
+// warp's staging tile [32 rows][box columns] in the output's type: store and add keep the 32
+// values; swiglu turns two groups of (8 gate, 8 up) into 16.
+__device__ __forceinline__ void tc_stage32(const unsigned (&r)[32], unsigned char* stage, int lane, int mode, int out_bf16) {
     if (mode == MODE_SWIGLU) {
-        // columns c .. c+31 = two groups of (8 gate, 8 up) -> 16 outputs
-        const int o0 = (n0 + c) / 2;
         float v[16];
 #pragma unroll
         for (int gi = 0; gi < 2; ++gi)
@@ -114,58 +118,44 @@ __device__ __forceinline__ void tc_epilogue32(const unsigned (&r)[32], void* __r
                 v[gi * 8 + j] = g / (1.f + expf(-g)) * u;
             }
         if (out_bf16) {
-            bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * N + o0;
+            uint4* d = reinterpret_cast<uint4*>(stage + lane * 32);
 #pragma unroll
             for (int j = 0; j < 16; j += 8) {
-                if (o0 + j >= N) break;
                 uint4 pk;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
-                pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
-                *reinterpret_cast<uint4*>(o + j) = pk;
+                pk.x = pack2(v[j], v[j + 1]); pk.y = pack2(v[j + 2], v[j + 3]);
+                pk.z = pack2(v[j + 4], v[j + 5]); pk.w = pack2(v[j + 6], v[j + 7]);
+                d[j >> 3] = pk;
             }
         } else {
-            float* o = reinterpret_cast<float*>(out) + (size_t)m * N + o0;
+            float4* d = reinterpret_cast<float4*>(stage + lane * 64);
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (o0 + j < N) o[j] = v[j];
-        }
-    } else if (mode == MODE_ADD) {
-        float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n0 + c;
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-            if (n0 + c + j >= N) break;
-            float4 cur = *reinterpret_cast<float4*>(o + j);
-            cur.x += __uint_as_float(r[j]); cur.y += __uint_as_float(r[j + 1]);
-            cur.z += __uint_as_float(r[j + 2]); cur.w += __uint_as_float(r[j + 3]);
-            *reinterpret_cast<float4*>(o + j) = cur;
+            for (int j = 0; j < 16; j += 4) d[j >> 2] = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
         }
     } else if (out_bf16) {
-        bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * N + n0 + c;
+        uint4* d = reinterpret_cast<uint4*>(stage + lane * 64);
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
-            if (n0 + c + j >= N) break;
             uint4 pk;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-            pk.x = *reinterpret_cast<unsigned*>(&h0); pk.y = *reinterpret_cast<unsigned*>(&h1);
-            pk.z = *reinterpret_cast<unsigned*>(&h2); pk.w = *reinterpret_cast<unsigned*>(&h3);
-            *reinterpret_cast<uint4*>(o + j) = pk;
+            pk.x = pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            pk.y = pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            pk.z = pack2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+            pk.w = pack2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+            d[j >> 3] = pk;
         }
     } else {
-        float* o = reinterpret_cast<float*>(out) + (size_t)m * N + n0 + c;
+        uint4* d = reinterpret_cast<uint4*>(stage + lane * 128);
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-            if (n0 + c + j >= N) break;
-            *reinterpret_cast<float4*>(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                            __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-        }
+        for (int j = 0; j < 32; j += 4) d[j >> 2] = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
     }
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, unsigned src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, unsigned src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
 }
 
 // Persistent: a CTA walks the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles
@@ -173,8 +163,8 @@ __device__ __forceinline__ void tc_epilogue32(const unsigned (&r)[32], void* __r
 // of 256 columns live in TMEM: while the epilogue warps drain one, the MMA warp fills the other.
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                          const __grid_constant__ CUtensorMap map_w,
-                                                         void* __restrict__ out, int M, int N, int K, int mode,
-                                                         int out_bf16, int tiles_m, int tiles_n) {
+                                                         const __grid_constant__ CUtensorMap map_o, int M, int N, int K,
+                                                         int mode, int out_bf16, int tiles_m, int tiles_n) {
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;         // swizzled tiles need 1024-byte alignment
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -183,6 +173,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     const unsigned bar_acc_full = bars + 8 * (2 * TC_STAGES);
     const unsigned bar_acc_empty = bar_acc_full + 16;
     volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(base_ptr + TC_STAGES * TC_STAGE_BYTES + 128);
+    unsigned char* out_stage = base_ptr + TC_STAGES * TC_STAGE_BYTES + 256;      // [4 warps][2][32 rows x 128 bytes]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_iters = (K + TC_BK - 1) / TC_BK;
     const int total_tiles = tiles_m * tiles_n;
@@ -264,14 +255,21 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         }
     } else {
         // ---------------- epilogue: warps 2..5, lane quadrant = warp % 4 ----------------
+        // A warp turns 32 accumulator columns of its 32 rows into a staging tile in shared memory
+        // (thread = row) and one lane hands the tile to the TMA engine: a store, or for the
+        // residual a reduce-add in L2 (every output element is added exactly once, so the sum does
+        // not depend on any order).  The memory system sees whole rows of the box instead of 32
+        // scattered 16-byte pieces per instruction, and nobody waits for the old residual.
         const int q = warp & 3;
-        const int row = q * 32 + lane;
+        unsigned char* stage0 = out_stage + (size_t)(warp - 2) * 2 * 4096;
+        const int box_cols = mode == MODE_SWIGLU ? 16 : 32;                  // output columns per 32 accumulator columns
         bool ok = true;
         int j = 0;
+        unsigned n_staged = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TC_BN;
             const int buf = j & 1;
-            const int m = m0 + row;
+            const int y = m0 + q * 32;                                       // first output row of this warp
             ok = mbar_wait(bar_acc_full + 8 * buf, (j >> 1) & 1, 3);
             tc_fence_after();
             if (!ok) break;
@@ -282,12 +280,28 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                 if (n0 + c >= n_limit) break;                            // warp-uniform
                 unsigned r[32];
                 tmem_ld32(t_row + c, r);
-                if (m < M) tc_epilogue32(r, out, m, n0, c, N, mode, out_bf16);
+                if (y >= M) continue;                                    // warp-uniform: no row of this warp exists
+                unsigned char* stage = stage0 + (n_staged & 1) * 4096;
+                // the copy that read this buffer two tiles ago must have read it
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                __syncwarp();
+                tc_stage32(r, stage, lane, mode, out_bf16);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    const int x = mode == MODE_SWIGLU ? (n0 + c) / 2 : n0 + c;
+                    if (mode == MODE_ADD) tma_reduce_add_2d(&map_o, x, y, smem_u32(stage));
+                    else tma_store_2d(&map_o, x, y, smem_u32(stage));
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                ++n_staged;
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // all tiles are in global memory
+        (void)box_cols;
     }
     tc_fence_before();
     __syncthreads();
@@ -328,6 +342,21 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
     return r == CUDA_SUCCESS ? 0 : ZLLM_ERR_UNSUPPORTED;
 }
 
+// out [M, N] float32 or bfloat16 row-major; boxes of 32 rows x box_cols elements, no swizzle
+static int make_out_map(CUtensorMap* map, void* ptr, int M, int N, int out_bf16, int box_cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return ZLLM_ERR_UNSUPPORTED;
+    const int es = out_bf16 ? 2 : 4;
+    cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    cuuint64_t strides[1] = {(cuuint64_t)N * es};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : ZLLM_ERR_UNSUPPORTED;
+}
+
 // x [M,K] bf16, w [N,K] bf16 ([2N,K] for swiglu), out [M,N].  K % 8 == 0, N % 8 == 0, operands 16-byte aligned.
 ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_bf16,
                                void* stream) {
@@ -336,10 +365,12 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
     if (mode == MODE_ADD && out_bf16) return ZLLM_ERR_UNSUPPORTED;
     if ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15)) return ZLLM_ERR_UNSUPPORTED;
     const int w_rows = mode == MODE_SWIGLU ? 2 * N : N;
-    CUtensorMap map_x, map_w;
+    CUtensorMap map_x, map_w, map_o;
     int e = make_map(&map_x, x, M, K, TC_BM);
     if (e) return e;
     e = make_map(&map_w, w, w_rows, K, TC_BN);
+    if (e) return e;
+    e = make_out_map(&map_o, out, M, N, out_bf16, mode == MODE_SWIGLU ? 16 : 32);
     if (e) return e;
     static bool attr_set = false;
     if (!attr_set) {
@@ -356,7 +387,7 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
     const int tiles_n = (w_rows + TC_BN - 1) / TC_BN, tiles_m = (M + TC_BM - 1) / TC_BM;
     const int total = tiles_n * tiles_m;
     const int grid = total < n_sm ? total : n_sm;                  // one CTA per SM walks the tiles
-    gemm_tc_kernel<<<grid, 192, TC_SMEM, (cudaStream_t)stream>>>(map_x, map_w, out, M, N, K, mode, out_bf16, tiles_m,
+    gemm_tc_kernel<<<grid, 192, TC_SMEM, (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode, out_bf16, tiles_m,
                                                                   tiles_n);
     return launch_status();
 }
