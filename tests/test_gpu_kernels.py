@@ -243,6 +243,42 @@ def test_attention_finds_a_far_key_among_hundreds(ops, dtype):
         view.k_pages[page, :, far % bs] = saved
 
 
+@pytest.mark.parametrize("slope", [0.0, 0.5, 3.0, -2.0])
+@pytest.mark.parametrize("hd,nq,nkv", [(64, 8, 2), (128, 4, 1)])
+def test_prefill_attention_when_the_maximum_keeps_moving(ops, slope, hd, nq, nkv):
+    """The scores of a row grow (or fall) with the key's position at a chosen rate, so the running
+    maximum of the softmax moves from block to block: slowly (the kernel may keep a stale reference),
+    fast (it has to rescale what it has summed at every block) or never (the first block holds it).
+    A portion of 300 rows behind a prefix of 500; random data would leave the maximum where it is."""
+    dtype = torch.bfloat16
+    bs = 16
+    cm = make_cache(nkv, hd, bs, 70, 2, 900, dtype)
+    s = cm.admit()
+    view = cm.view(0)
+    g = torch.Generator().manual_seed(15)
+    make_ctx(cm, [(s, 500)])
+    ctx = make_ctx(cm, [(s, 300)])
+    direction = torch.randn(hd, generator=g)
+    direction /= direction.norm()
+    k = torch.randn(view.k_pages.shape, generator=g) * 0.3
+    for pos in range(800):
+        page = int(view.block_table[s, pos // bs])
+        k[page, :, pos % bs] += direction * slope * pos / math.sqrt(hd) * 8.0 / 40.0
+    view.k_pages.copy_(k.to(dtype))
+    view.v_pages.copy_(torch.randn(view.v_pages.shape, generator=g).to(dtype))
+    qkv = torch.randn(300, (nq + 2 * nkv) * hd, generator=g) * 0.3
+    qkv[:, :nq * hd] += (direction * 40.0).repeat(nq)
+    qkv = qkv.to(dtype)
+    out = torch.zeros(300, nq * hd, dtype=dtype, device=DEV)
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(qkv.to(DEV), out, ctx, view, nq, nkv, hd, scale, None)
+    ops.check_async_errors()
+    want = torch.zeros(300, nq * hd)
+    REF.paged_attention(qkv.float(), want, cpu_ctx(ctx), CpuCacheView(view), nq, nkv, hd, scale, None)
+    err = float((out.cpu().float() - want).abs().max())
+    assert err <= 0.03, err
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_window_edge(ops, dtype):
     """The key just outside the window is made dominant: it must NOT be seen; the one just
