@@ -184,6 +184,10 @@ ATT_CASES = [  # nq, nkv, hd, page size, window
     (4, 2, 16, 16, None), (3, 1, 32, 8, None), (8, 2, 64, 16, None), (32, 8, 64, 16, None), (6, 6, 48, 5, None),
     (16, 2, 128, 16, None), (5, 1, 80, 7, None), (8, 2, 64, 16, 37), (4, 4, 96, 12, 20), (8, 1, 112, 16, None),
     (2, 1, 256, 16, None),
+    # page sizes and groups of the TMA / tcgen05 kernels (head sizes 64 and 128): one box per page, pages
+    # smaller and larger than a block of keys, a group of one head, the largest group
+    (8, 2, 64, 8, None), (8, 2, 64, 32, None), (6, 6, 64, 64, None), (4, 2, 64, 128, None), (8, 1, 64, 256, None),
+    (4, 2, 128, 32, None), (8, 1, 128, 128, None),
 ]
 
 
