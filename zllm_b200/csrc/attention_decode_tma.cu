@@ -64,14 +64,16 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
 
 // BIG changes no instruction: the two instantiations only carry different preferences for the
 // split of an SM's memory between L1 and shared memory (see launch_decode_tma).
-template <int HD, bool BIG>
+// DIRECT: the grid has ONE split per row (contexts up to 256), so the CTA's merged result is the
+// row's output: it is written as it is and no second kernel runs.
+template <int HD, bool BIG, bool DIRECT>
 __global__ void __launch_bounds__(DEC_WARPS * 32) decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     const bf16* __restrict__ qkv, const int* __restrict__ rows, const int* __restrict__ positions,
     const int* __restrict__ row_slot, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     const int* __restrict__ table, int max_blocks, int bs, int bs_shift,
     int box_rows, int nq, int nkv, float scale, float* __restrict__ part_o, float* __restrict__ part_ml,
-    int max_splits) {
+    int max_splits, bf16* __restrict__ out) {
     constexpr int NB = HD <= 64 ? 64 : 32;                   // keys per warp iteration
     constexpr int NIT = (SPLIT_KEYS / DEC_WARPS) / NB;       // iterations per warp
     constexpr int HALVES = HD / 64;                          // 128-byte column boxes per row
@@ -100,8 +102,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_tma_kernel(
     }
     const int row = rows[blockIdx.x];
     const int slot = row_slot[row];
-    if (slot < 0) return;
     const int kvh = blockIdx.y, split = blockIdx.z;
+    if (slot < 0) {                                          // padding row of a graph bucket
+        if (DIRECT) {
+            const int Gp = nq / nkv;
+            for (int i = threadIdx.x; i < Gp * HD; i += blockDim.x)
+                out[((size_t)row * nq + kvh * Gp) * HD + i] = __float2bfloat16_rn(0.f);
+        }
+        return;
+    }
     const int pos = positions[row];
     const int k_first = split * SPLIT_KEYS;
     if (k_first > pos) return;                               // this split holds no key of the row
@@ -312,9 +321,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_tma_kernel(
             L += wl[w * 8 + h] * f;
             O += wo[((size_t)w * 8 + h) * HD + d] * f;
         }
-        const size_t pi = ((size_t)blockIdx.x * nq + kvh * G + h) * max_splits + split;
-        part_o[pi * HD + d] = O;
-        if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+        if (DIRECT) {
+            out[((size_t)row * nq + kvh * G + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            const size_t pi = ((size_t)blockIdx.x * nq + kvh * G + h) * max_splits + split;
+            part_o[pi * HD + d] = O;
+            if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+        }
     }
 }
 
@@ -368,7 +381,7 @@ ZLLM_API int zllm_attention_kv_map(void* out_map, const void* pages, long long n
 // that (batch 64, context 4096: 2.71 ms against 3.02 ms).  So: the largest carveout when the grid
 // is large or the batch is one whose products already use the large-shared-memory streaming
 // kernel; 60 % otherwise.  The choice depends on the grid's size only and changes no result.
-template <int HD, bool BIG>
+template <int HD, bool BIG, bool DIRECT>
 static int launch_decode_tma_v(const CUtensorMap& mk, const CUtensorMap& mv, const void* k_pages, const void* v_pages,
                              const void* qkv, void* out, const int* rows,
                              int n_rows, const int* positions, const int* row_slot, const int* table, int max_blocks,
@@ -376,7 +389,7 @@ static int launch_decode_tma_v(const CUtensorMap& mk, const CUtensorMap& mv, con
                              int max_splits, cudaStream_t s) {
     constexpr int NB = HD <= 64 ? 64 : 32;
     const size_t smem = 1024 + (size_t)DEC_WARPS * 2 * (HD / 64) * NB * 128 + 16 * DEC_WARPS;
-    auto kern = decode_tma_kernel<HD, BIG>;
+    auto kern = decode_tma_kernel<HD, BIG, DIRECT>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -389,8 +402,8 @@ static int launch_decode_tma_v(const CUtensorMap& mk, const CUtensorMap& mv, con
     dim3 grid(n_rows, nkv, n_splits);
     int rc = launch_pdl(kern, grid, dim3(DEC_WARPS * 32), smem, s, mk, mv, (const bf16*)qkv, rows, positions, row_slot,
                         (const bf16*)k_pages, (const bf16*)v_pages, table, max_blocks, bs, (int)__builtin_ctz(bs), box_rows_for(bs, HD), nq, nkv,
-                        scale * 1.4426950408889634f, part_o, part_ml, max_splits);
-    if (rc) return rc;
+                        scale * 1.4426950408889634f, part_o, part_ml, max_splits, (bf16*)out);
+    if (rc || DIRECT) return rc;
     return launch_pdl(decode_combine_kernel<HD>, dim3(n_rows, nq), dim3(HD <= 64 ? 64 : 128), 0, s, rows, positions,
                       row_slot, (const float*)part_o, (const float*)part_ml, (bf16*)out, nq, 0, max_splits);
 }
@@ -401,11 +414,12 @@ static int launch_decode_tma(const CUtensorMap& mk, const CUtensorMap& mv, const
                              const int* row_slot, const int* table, int max_blocks, int bs, int nq, int nkv, float scale,
                              float* part_o, float* part_ml, int n_splits, int max_splits, cudaStream_t s) {
     const bool big = n_rows > 16 || (long long)n_rows * nkv * n_splits >= 2048;
-    if (big)
-        return launch_decode_tma_v<HD, true>(mk, mv, k_pages, v_pages, qkv, out, rows, n_rows, positions, row_slot, table,
-                                             max_blocks, bs, nq, nkv, scale, part_o, part_ml, n_splits, max_splits, s);
-    return launch_decode_tma_v<HD, false>(mk, mv, k_pages, v_pages, qkv, out, rows, n_rows, positions, row_slot, table,
-                                          max_blocks, bs, nq, nkv, scale, part_o, part_ml, n_splits, max_splits, s);
+#define DT_LAUNCH(B, D) launch_decode_tma_v<HD, B, D>(mk, mv, k_pages, v_pages, qkv, out, rows, n_rows, positions, row_slot, \
+                                                      table, max_blocks, bs, nq, nkv, scale, part_o, part_ml, n_splits,     \
+                                                      max_splits, s)
+    if (n_splits == 1) return big ? DT_LAUNCH(true, true) : DT_LAUNCH(false, true);
+    return big ? DT_LAUNCH(true, false) : DT_LAUNCH(false, false);
+#undef DT_LAUNCH
 }
 
 // As zllm_attention_decode_bf16 (attention_bf16.cu) with the pools given by their tensor maps

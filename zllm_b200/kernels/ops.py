@@ -384,6 +384,8 @@ class CudaOps:
                     c_int(hd), c_float(scale), _ptr(part_o), _ptr(part_ml), c_int(n_splits), c_int(max_splits),
                     self._stream())
                 self._check(code, "attention_decode_tma")
+                if n_splits == 1:
+                    self.launches -= 1          # one split per row: the kernel writes the output itself
             else:
                 code = lib.zllm_attention_decode_bf16(
                     _ptr(qkv), _ptr(out), _ptr(ctx.decode_rows), c_int(nd), _ptr(ctx.positions), _ptr(ctx.row_slot),
