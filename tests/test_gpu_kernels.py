@@ -122,6 +122,37 @@ def test_streaming_product(ops, M, N, K, mode):
         assert err <= (2e-5 if odt == torch.float32 else 2 ** -8 * 1.5) * scale, (odt, err)
 
 
+SPLIT_K_SHAPES = [  # rows, N, K, epilogue: few 128 x 256 tiles, so the many-row kernel splits K (2..16 slices, the last
+    # slice ragged or empty) and a second kernel sums the slices in order
+    (128, 2048, 8192, "add"), (200, 2048, 2048, "add"), (70, 3072, 2048, "store"), (512, 2048, 8192, "add"),
+    (300, 264, 4104, "store"), (96, 520, 1352, "swiglu"), (130, 1000, 2056, "store"),
+]
+
+
+@pytest.mark.parametrize("M,N,K,mode", SPLIT_K_SHAPES)
+def test_many_row_product_with_split_k(ops, M, N, K, mode):
+    dtype = torch.bfloat16
+    x = rnd((M, K), dtype, 5)
+    if mode == "swiglu":
+        w = interleave_gate_up(rnd((N, K), dtype, 6, K ** -0.5), rnd((N, K), dtype, 7, K ** -0.5))
+    else:
+        w = rnd((N, K), dtype, 6, K ** -0.5)
+    for odt in ((torch.float32,) if mode == "add" else (torch.float32, torch.bfloat16)):
+        base = rnd((M, N), odt, 8)
+        outs = []
+        for _ in range(2):                      # twice: the sum over the slices has a fixed order
+            out = base.clone().to(DEV)
+            ops.linear(x.to(DEV), w.to(DEV), out, mode)
+            ops.check_async_errors()
+            outs.append(out.cpu())
+        assert torch.equal(outs[0], outs[1])
+        want = base.clone().float()
+        REF.linear(x, w, want, mode)
+        err = float((outs[0].float() - want).abs().max())
+        scale = max(float(want.abs().max()), 1.0)
+        assert err <= (2e-5 if odt == torch.float32 else 2 ** -8 * 1.5) * scale, (odt, err)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_linear_plain_matches_too(ops, dtype):
     x, w = rnd((33, 100), dtype, 1), rnd((77, 100), dtype, 2, 0.1)

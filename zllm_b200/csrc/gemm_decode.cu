@@ -342,8 +342,12 @@ static int launch_gd(const GemmDecodeParams& p, cudaStream_t s) {
     const size_t red = (size_t)GD_WARPS * RT * 16 * (MP + 1) * sizeof(float);
     if (red > smem) smem = red;
     auto kern = gemm_decode_kernel<NT, RT, FUSE_NORM>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static bool attr_set = false;                                        // (smem depends on the template only)
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
     const int tiles = (p.w_rows + 15) / 16;
     return launch_pdl(kern, dim3((tiles + RT - 1) / RT), dim3(GD_WARPS * 32), smem, s, p);
 }

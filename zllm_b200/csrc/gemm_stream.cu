@@ -93,6 +93,11 @@ __device__ __forceinline__ unsigned long long umma_desc(unsigned saddr) {
     return d;
 }
 
+__device__ __forceinline__ unsigned pack2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
 __device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned* r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -238,7 +243,32 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_stream_kernel(const __grid_co
     };
     const int groups = 8 / csize;                                        // 16-row groups this rank finishes
     const int M = p.M;
-    if (p.mode == MODE_SWIGLU) {
+    auto total4 = [&](int m, int r) {                                    // r % 4 == 0: four weight rows at once
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+            if (s < csize) {
+                const float4 a = *reinterpret_cast<const float4*>(peer[s] + m * GS_PSTR + r);
+                v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+            }
+        return v;
+    };
+    const bool vec = (p.N % 4 == 0) && (((uintptr_t)p.out & 15) == 0);   // four outputs per thread and access
+    if (p.mode == MODE_SWIGLU && vec) {
+        for (int e = threadIdx.x; e < groups * 2 * M; e += GS_THREADS) {
+            const int h2 = e & 1, gi = (e >> 1) % groups, m = e / (2 * groups);
+            const int j = crank + gi * csize;
+            const int col = (n0 + 16 * j) / 2 + 4 * h2;
+            if (col >= p.N) continue;
+            const float4 gt = total4(m, 16 * j + 4 * h2), up = total4(m, 16 * j + 8 + 4 * h2);
+            float4 v;
+            v.x = gt.x / (1.f + expf(-gt.x)) * up.x; v.y = gt.y / (1.f + expf(-gt.y)) * up.y;
+            v.z = gt.z / (1.f + expf(-gt.z)) * up.z; v.w = gt.w / (1.f + expf(-gt.w)) * up.w;
+            const size_t o = (size_t)m * p.N + col;
+            if (p.out_bf16) *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + o) = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
+            else *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o) = v;
+        }
+    } else if (p.mode == MODE_SWIGLU) {
         for (int e = threadIdx.x; e < groups * 8 * M; e += GS_THREADS) {
             const int r8 = e & 7, gi = (e >> 3) % groups, m = e / (8 * groups);
             const int j = crank + gi * csize;
@@ -248,6 +278,25 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_stream_kernel(const __grid_co
             const float v = gt / (1.f + expf(-gt)) * up;
             if (p.out_bf16) reinterpret_cast<bf16*>(p.out)[(size_t)m * p.N + col] = __float2bfloat16_rn(v);
             else reinterpret_cast<float*>(p.out)[(size_t)m * p.N + col] = v;
+        }
+    } else if (vec) {
+        for (int e = threadIdx.x; e < groups * 4 * M; e += GS_THREADS) {
+            const int q4 = e & 3, gi = (e >> 2) % groups, m = e / (4 * groups);
+            const int r = 16 * (crank + gi * csize) + 4 * q4;
+            const int n = n0 + r;
+            if (n >= p.N) continue;
+            float4 v = total4(m, r);
+            const size_t o = (size_t)m * p.N + n;
+            if (p.mode == MODE_ADD) {
+                float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
+                const float4 cur = *d;
+                v.x += cur.x; v.y += cur.y; v.z += cur.z; v.w += cur.w;
+                *d = v;
+            } else if (p.out_bf16) {
+                *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + o) = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
+            } else {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o) = v;
+            }
         }
     } else {
         for (int e = threadIdx.x; e < groups * 16 * M; e += GS_THREADS) {
@@ -313,8 +362,12 @@ static int launch_stream(const CUtensorMap& map_w, const CUtensorMap& map_x, con
     p.iters_per_rank = (p.k_iters + csize - 1) / csize;
     const size_t smem = 1024 + (size_t)p.stages * STAGE_BYTES + (size_t)NP * GS_PSTR * sizeof(float) + 8 * (2 * GS_MAX_STAGES + 1) + 16;
     auto kern = gemm_stream_kernel<NP>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
+    static bool attr_set = false;                                        // (smem depends on the template only)
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(csize, tiles, 1);
     cfg.blockDim = dim3(GS_THREADS, 1, 1);

@@ -153,6 +153,10 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
                  ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int y, int z, unsigned src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(z), "r"(src) : "memory");
+}
 __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, unsigned src) {
     asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
                  ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
@@ -164,7 +168,7 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x,
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                          const __grid_constant__ CUtensorMap map_w,
                                                          const __grid_constant__ CUtensorMap map_o, int M, int N, int K,
-                                                         int mode, int out_bf16, int tiles_m, int tiles_n) {
+                                                         int mode, int out_bf16, int tiles_m, int tiles_n, int splits) {
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;         // swizzled tiles need 1024-byte alignment
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -175,8 +179,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(base_ptr + TC_STAGES * TC_STAGE_BYTES + 128);
     unsigned char* out_stage = base_ptr + TC_STAGES * TC_STAGE_BYTES + 256;      // [4 warps][2][32 rows x 128 bytes]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int k_iters = (K + TC_BK - 1) / TC_BK;
-    const int total_tiles = tiles_m * tiles_n;
+    // splits > 1: a unit of work is (tile, slice of K); the float32 partial tiles go to a scratch
+    // [splits][M][weight rows] (map_o is then its 3-D map) and a second kernel sums them in order
+    const int k_all = (K + TC_BK - 1) / TC_BK;
+    const int k_per = (k_all + splits - 1) / splits;
+    const int total_tiles = tiles_m * tiles_n * splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) {
@@ -205,7 +212,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
             bool ok = true;
             int g = 0;                                                   // k steps issued over all tiles
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TC_BN;
+                const int ks = tile % splits, t2 = tile / splits;
+                const int m0 = (t2 % tiles_m) * TC_BM, n0 = (t2 / tiles_m) * TC_BN;
+                const int k_lo = ks * k_per, k_iters = max(0, min(k_all, k_lo + k_per) - k_lo);
                 for (int it = 0; it < k_iters; ++it, ++g) {
                     const int s = g % TC_STAGES;
                     ok = mbar_wait(bars + 8 * (TC_STAGES + s), ((g / TC_STAGES) & 1) ^ 1, 0);   // stage is free
@@ -213,8 +222,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                     const unsigned full = bars + 8 * s;
                     mbar_expect_tx(full, TC_STAGE_BYTES);
                     const unsigned a_dst = base + s * TC_STAGE_BYTES;
-                    tma_load_2d(a_dst, &map_x, it * TC_BK, m0, full);
-                    tma_load_2d(a_dst + TC_A_BYTES, &map_w, it * TC_BK, n0, full);
+                    tma_load_2d(a_dst, &map_x, (k_lo + it) * TC_BK, m0, full);
+                    tma_load_2d(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full);
                 }
             }
             if (!ok) {
@@ -237,6 +246,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                 if (!ok) break;
                 tc_fence_after();
                 const unsigned acc = tmem_acc + buf * TC_BN;
+                const int k_lo = (tile % splits) * k_per, k_iters = max(0, min(k_all, k_lo + k_per) - k_lo);
                 for (int it = 0; it < k_iters; ++it, ++g) {
                     const int s = g % TC_STAGES;
                     ok = mbar_wait(bars + 8 * s, (g / TC_STAGES) & 1, 2);         // operands have landed
@@ -267,9 +277,11 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         int j = 0;
         unsigned n_staged = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
-            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TC_BN;
+            const int ks = tile % splits, t2 = tile / splits;
+            const int m0 = (t2 % tiles_m) * TC_BM, n0 = (t2 / tiles_m) * TC_BN;
             const int buf = j & 1;
             const int y = m0 + q * 32;                                       // first output row of this warp
+            const bool empty_slice = ks * k_per >= k_all;                    // no k step: the accumulator holds nothing
             ok = mbar_wait(bar_acc_full + 8 * buf, (j >> 1) & 1, 3);
             tc_fence_after();
             if (!ok) break;
@@ -280,17 +292,22 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                 if (n0 + c >= n_limit) break;                            // warp-uniform
                 unsigned r[32];
                 tmem_ld32(t_row + c, r);
+                if (empty_slice) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = 0u;
+                }
                 if (y >= M) continue;                                    // warp-uniform: no row of this warp exists
                 unsigned char* stage = stage0 + (n_staged & 1) * 4096;
                 // the copy that read this buffer two tiles ago must have read it
                 if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                 __syncwarp();
-                tc_stage32(r, stage, lane, mode, out_bf16);
+                tc_stage32(r, stage, lane, splits > 1 ? MODE_STORE : mode, splits > 1 ? 0 : out_bf16);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
                     const int x = mode == MODE_SWIGLU ? (n0 + c) / 2 : n0 + c;
-                    if (mode == MODE_ADD) tma_reduce_add_2d(&map_o, x, y, smem_u32(stage));
+                    if (splits > 1) tma_store_3d(&map_o, n0 + c, y, ks, smem_u32(stage));
+                    else if (mode == MODE_ADD) tma_reduce_add_2d(&map_o, x, y, smem_u32(stage));
                     else tma_store_2d(&map_o, x, y, smem_u32(stage));
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
@@ -311,6 +328,43 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     }
 }
 
+// Second pass of a product whose K was split: out = epilogue(sum over the slices, in slice order).
+// part [splits][M][w_rows] float32; a thread takes 4 consecutive outputs.
+__global__ void gemm_tc_reduce_kernel(const float* __restrict__ part, int splits, int M, int w_rows, void* __restrict__ out,
+                                      int N, int mode, int out_bf16) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int n4 = N / 4;
+    if (idx >= (long long)M * n4) return;
+    const int m = (int)(idx / n4), n = (int)(idx - (long long)m * n4) * 4;
+    auto sum4 = [&](int col) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < splits; ++s) {
+            const float4 a = *reinterpret_cast<const float4*>(part + ((size_t)s * M + m) * w_rows + col);
+            v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+        }
+        return v;
+    };
+    float4 v;
+    if (mode == MODE_SWIGLU) {                               // outputs n .. n+3 of group n / 8: gate rows, then up rows 8 further
+        const int col = (n / 8) * 16 + (n % 8);
+        const float4 g = sum4(col), u = sum4(col + 8);
+        v.x = g.x / (1.f + expf(-g.x)) * u.x; v.y = g.y / (1.f + expf(-g.y)) * u.y;
+        v.z = g.z / (1.f + expf(-g.z)) * u.z; v.w = g.w / (1.f + expf(-g.w)) * u.w;
+    } else {
+        v = sum4(n);
+    }
+    const size_t o = (size_t)m * N + n;
+    if (mode == MODE_ADD) {
+        float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + o);
+        const float4 cur = *d;
+        *d = make_float4(cur.x + v.x, cur.y + v.y, cur.z + v.z, cur.w + v.w);
+    } else if (out_bf16) {
+        *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + o) = make_uint2(pack2(v.x, v.y), pack2(v.z, v.w));
+    } else {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + o) = v;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -328,10 +382,36 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// Encoded maps are kept: a step encodes the same few (pointer, shape) pairs again and again
+// (weights never move, activations live in fixed workspaces), and encoding is host time on the
+// path of every launch.  A direct-mapped table; a collision only costs an encode.
+struct MapKey { const void* ptr; long long a, b, c; };
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+static MapSlot g_maps[512];
+static MapSlot& map_slot(const MapKey& k) {
+    const unsigned long long h = ((unsigned long long)(uintptr_t)k.ptr >> 4) * 0x9E3779B97F4A7C15ull ^
+                                 (unsigned long long)(k.a * 31 + k.b * 131 + k.c * 1031) * 0xD6E8FEB86659FD93ull;
+    return g_maps[(h >> 24) & 511];
+}
+static bool map_lookup(const MapKey& k, CUtensorMap* out) {
+    const MapSlot& s = map_slot(k);
+    if (!(s.used && s.key.ptr == k.ptr && s.key.a == k.a && s.key.b == k.b && s.key.c == k.c)) return false;
+    *out = s.map;
+    return true;
+}
+static void map_store(const MapKey& k, const CUtensorMap& m) {
+    MapSlot& s = map_slot(k);
+    s.key = k;
+    s.map = m;
+    s.used = true;
+}
+
 // [rows, K] bfloat16 row-major; box = box_rows x 64 elements, 128-byte swizzle, zero fill outside
 static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return ZLLM_ERR_UNSUPPORTED;
+    const MapKey key{ptr, rows, K, box_rows};
+    if (map_lookup(key, map)) return 0;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};
     cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
@@ -339,13 +419,17 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : ZLLM_ERR_UNSUPPORTED;
+    if (r != CUDA_SUCCESS) return ZLLM_ERR_UNSUPPORTED;
+    map_store(key, *map);
+    return 0;
 }
 
 // out [M, N] float32 or bfloat16 row-major; boxes of 32 rows x box_cols elements, no swizzle
 static int make_out_map(CUtensorMap* map, void* ptr, int M, int N, int out_bf16, int box_cols) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return ZLLM_ERR_UNSUPPORTED;
+    const MapKey key{ptr, M, N, 1000 + out_bf16 * 100 + box_cols};
+    if (map_lookup(key, map)) return 0;
     const int es = out_bf16 ? 2 : 4;
     cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
     cuuint64_t strides[1] = {(cuuint64_t)N * es};
@@ -354,12 +438,33 @@ static int make_out_map(CUtensorMap* map, void* ptr, int M, int N, int out_bf16,
     CUresult r = fn(map, out_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides,
                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : ZLLM_ERR_UNSUPPORTED;
+    if (r != CUDA_SUCCESS) return ZLLM_ERR_UNSUPPORTED;
+    map_store(key, *map);
+    return 0;
+}
+
+// scratch [splits][M][w_rows] float32; boxes of 1 x 32 rows x 32 columns
+static int make_part_map(CUtensorMap* map, void* ptr, int splits, int M, int w_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return ZLLM_ERR_UNSUPPORTED;
+    const MapKey key{ptr, M, w_rows, 5000 + splits};
+    if (map_lookup(key, map)) return 0;
+    cuuint64_t dims[3] = {(cuuint64_t)w_rows, (cuuint64_t)M, (cuuint64_t)splits};
+    cuuint64_t strides[2] = {(cuuint64_t)w_rows * 4, (cuuint64_t)w_rows * 4 * M};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ZLLM_ERR_UNSUPPORTED;
+    map_store(key, *map);
+    return 0;
 }
 
 // x [M,K] bf16, w [N,K] bf16 ([2N,K] for swiglu), out [M,N].  K % 8 == 0, N % 8 == 0, operands 16-byte aligned.
+// scratch (may be null): float32 workspace of scratch_bytes for products with few tiles, whose K is
+// then split over more CTAs and summed in a second pass, in a fixed order.
 ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_bf16,
-                               void* stream) {
+                               void* scratch, long long scratch_bytes, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) || (N % 8) || mode < 0 || mode > 2) return ZLLM_ERR_UNSUPPORTED;
     if (mode == MODE_ADD && out_bf16) return ZLLM_ERR_UNSUPPORTED;
@@ -385,10 +490,27 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
     }
     const int tiles_n = (w_rows + TC_BN - 1) / TC_BN, tiles_m = (M + TC_BM - 1) / TC_BM;
-    const int total = tiles_n * tiles_m;
-    const int grid = total < n_sm ? total : n_sm;                  // one CTA per SM walks the tiles
+    // few tiles: split K until about every SM has a unit of work, each with at least 4 k steps
+    // (the choice depends on the sizes only)
+    int splits = 1;
+    const int k_all = (K + TC_BK - 1) / TC_BK;
+    while (tiles_n * tiles_m * splits * 2 <= n_sm && k_all / (splits * 2) >= 4 && splits < 32) splits *= 2;
+    if (splits > 1 && (scratch == nullptr || (long long)splits * M * w_rows * 4 > scratch_bytes || (w_rows % 4) ||
+                       ((uintptr_t)scratch & 15)))
+        splits = 1;
+    if (splits > 1) {
+        e = make_part_map(&map_o, scratch, splits, M, w_rows);
+        if (e) return e;
+    }
+    const int total = tiles_n * tiles_m * splits;
+    const int grid = total < n_sm ? total : n_sm;                  // one CTA per SM walks the units
     gemm_tc_kernel<<<grid, 192, TC_SMEM, (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode, out_bf16, tiles_m,
-                                                                  tiles_n);
+                                                                  tiles_n, splits);
+    int rc = launch_status();
+    if (rc || splits == 1) return rc;
+    const long long n_thr = (long long)M * (N / 4);
+    gemm_tc_reduce_kernel<<<(unsigned)((n_thr + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (const float*)scratch, splits, M, w_rows, out, N, mode, out_bf16);
     return launch_status();
 }
 

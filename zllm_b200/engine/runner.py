@@ -161,12 +161,22 @@ class ModelRunner:
         buf.upload()
         self.cache.sync_tables()
         ctx = make_context(buf, T, R, nd, nt, max_ctx, self.ws, entries, starts)
-        logits = self.model.forward(ctx, self.cache.views)
+        logits = self._forward(ctx)
         for e, s in zip(entries, starts):
             self.cache.advance(e.slot, s + len(e.tokens))
         self.steps += 1
         self.tokens_run += T
         return logits
+
+    def _forward(self, ctx):
+        bind = getattr(self.ops, "bind_stream", None)
+        if bind is None:
+            return self.model.forward(ctx, self.cache.views)
+        bind()                                  # one stream lookup for the whole forward
+        try:
+            return self.model.forward(ctx, self.cache.views)
+        finally:
+            self.ops.unbind_stream()
 
     # ---- decode-only steps through a captured graph ----------------------------
     def decode_step(self, slots: Sequence[int], tokens: Sequence[int], temps: Sequence[float],
@@ -276,7 +286,7 @@ class ModelRunner:
 
     def _decode_body(self, g):
         ctx = g["ctx"]
-        logits = self.model.forward(ctx, self.cache.views)
+        logits = self._forward(ctx)
         g["logits"] = logits
         buf = g["buf"]
         B = ctx.T

@@ -47,6 +47,8 @@ class CudaOps:
         self.dtype = torch.bfloat16
         self._libs = {}
         self._sample_scratch = None
+        self._bound_stream = None
+        self._tc_scratch = None
         self._kv_maps = {}
         self.launches = 0
 
@@ -69,7 +71,17 @@ class CudaOps:
         return lib
 
     def _stream(self):
+        if self._bound_stream is not None:
+            return self._bound_stream
         return c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def bind_stream(self):
+        """Look the current stream up ONCE for the launches that follow (a step issues more than a
+        hundred); ``unbind_stream`` ends it.  Outside such a pair every launch asks torch."""
+        self._bound_stream = c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def unbind_stream(self):
+        self._bound_stream = None
 
     def _check(self, code, what):
         self.launches += 1
@@ -153,6 +165,7 @@ class CudaOps:
     STREAM_MIN_WEIGHTS = 12 * 1024 * 1024
     STREAM_MAX_WEIGHT_ROWS = 32768
     SAMPLE_SCRATCH_ROWS = 1024
+    TC_SCRATCH_BYTES = 64 * 1024 * 1024
     DECODE_MAX_ROWS = 16
 
     def _gemm_decode(self, x, norm_w, eps, w, out, mode, M, N, K, rope=None):
@@ -250,8 +263,11 @@ class CudaOps:
             self._gemm_decode(x, None, 0.0, w, out, mode, M, N, K)
             return True
         if tc_ok and "gemm_tc" in self._libs:
+            if self._tc_scratch is None:     # float32 partial tiles of products whose K is split (few tiles)
+                self._tc_scratch = torch.empty(self.TC_SCRATCH_BYTES // 4, dtype=torch.float32, device=self.device)
             code = self.lib("gemm_tc").zllm_gemm_tc_bf16(_ptr(x), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K),
                                                          c_int(MODES[mode]), c_int(out.dtype == torch.bfloat16),
+                                                         _ptr(self._tc_scratch), c_longlong(self.TC_SCRATCH_BYTES),
                                                          self._stream())
             self._check(code, "gemm_tc_bf16")
             return True
