@@ -99,3 +99,20 @@ def test_temperature_sampling_is_reproducible_and_survives_preemption(tmp_path):
         t = P.gumbel_sample(lg, 0.8, P.step_seed(100, n))
         assert t == a[0][n]
         toks.append(t)
+
+
+def test_workspace_keeps_a_buffer_that_had_to_grow():
+    """Captured graphs hold the addresses of the buffers they were captured with: a buffer that is
+    replaced by a larger one must stay allocated."""
+    import torch
+    from zllm_b200.engine.batch import Workspace
+    ws = Workspace(16, "cpu")
+    a = ws.get("partials", (2, 8), torch.float32, cap=2)
+    a.fill_(3.0)
+    old = a.data_ptr()
+    del a
+    b = ws.get("partials", (5, 8), torch.float32, cap=5)
+    assert b.shape == (5, 8) and b.data_ptr() != old
+    assert any(t.data_ptr() == old and float(t.sum()) == 48.0 for t in ws._retired)
+    assert ws.get("partials", (3, 8), torch.float32, cap=3).data_ptr() == b.data_ptr()
+    assert ws.bytes() == (2 + 5) * 8 * 4

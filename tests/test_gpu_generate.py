@@ -81,6 +81,33 @@ def test_warm_up_captures_every_bucket(tmp_path):
     assert set(eng.runner._graphs) == before and len(out[0]) == 30
 
 
+def test_small_graphs_stay_valid_when_the_batch_has_grown(tmp_path):
+    """Decode graphs of a small batch are captured first, then a larger batch makes the scratch
+    buffers grow, then the small batch runs again through its old graphs (which hold the addresses
+    of the old buffers) while the larger batch's buffers are in use: every stream must still be the
+    plain implementation's.  float32, so the streams are exact."""
+    d = make_model_dir(tmp_path, "A", "float32", std=0.3)
+    cfg, w = P.read_model_dir(d)
+    V = cfg["vocab_size"]
+    prompts = [random_prompt(V, 4 + 3 * i, 70 + i) for i in range(7)]
+    # the first two requests run long, the others end early: the batch is 2, then 7, then 2 again
+    lens = [40, 40, 6, 6, 6, 6, 6]
+    want = [P.greedy_generate(cfg, w, p, n) for p, n in zip(prompts, lens)]
+    eng = Engine(str(d), dtype="float32", block_size=TINY["A"][1], num_blocks=64 * 16 // TINY["A"][1], max_num_seqs=8,
+                 max_num_batched_tokens=64)
+    got = {}
+    ids = [eng.add_request(p, SamplingParams.greedy(max_tokens=n)) for p, n in zip(prompts[:2], lens[:2])]
+    for _ in range(6):                                        # batch of 2: graphs of the small bucket
+        for rid, tok, done in eng.step():
+            got.setdefault(rid, []).append(tok)
+    ids += [eng.add_request(p, SamplingParams.greedy(max_tokens=n)) for p, n in zip(prompts[2:], lens[2:])]
+    while eng.has_unfinished():
+        for rid, tok, done in eng.step():
+            got.setdefault(rid, []).append(tok)
+    assert [got[i] for i in ids] == want
+    assert len({k[0] for k in eng.runner._graphs}) >= 2      # at least two batch buckets were captured
+
+
 def test_session_single_stream_calls(tmp_path):
     d = make_model_dir(tmp_path, "A", "float32")
     cfg, w = P.read_model_dir(d)

@@ -166,12 +166,18 @@ def make_context(buf: StepBuffers, T, R, nd, nt, max_ctx, ws, entries=None, star
 
 
 class Workspace:
-    """Named scratch buffers, allocated once at their largest first dimension."""
+    """Named scratch buffers, allocated once at their largest first dimension.
+
+    A buffer that has to grow is REPLACED, and the old one is kept for the workspace's life:
+    captured CUDA graphs hold the addresses of the buffers they were captured with, and memory
+    given back to the allocator would be handed to someone else while those graphs still write it.
+    """
 
     def __init__(self, max_rows: int, device):
         self.max_rows = max_rows
         self.device = torch.device(device)
         self._bufs = {}
+        self._retired = []
 
     def get(self, name: str, shape, dtype, cap=None) -> torch.Tensor:
         """A [rows, ...] view of the buffer ``name``.  The buffer is made for ``cap`` rows
@@ -182,9 +188,11 @@ class Workspace:
         buf = self._bufs.get(key)
         if buf is None or buf.shape[0] < rows:
             cap = max(rows, self.max_rows if cap is None else cap)
+            if buf is not None:
+                self._retired.append(buf)
             buf = torch.empty((cap, *rest), dtype=dtype, device=self.device)
             self._bufs[key] = buf
         return buf[:rows]
 
     def bytes(self) -> int:
-        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+        return sum(b.numel() * b.element_size() for b in list(self._bufs.values()) + self._retired)
