@@ -108,6 +108,35 @@ def test_small_graphs_stay_valid_when_the_batch_has_grown(tmp_path):
     assert len({k[0] for k in eng.runner._graphs}) >= 2      # at least two batch buckets were captured
 
 
+def test_many_requests_through_few_slots_and_few_pages(tmp_path):
+    """Thirty requests of random lengths through five slots and so few pages that requests are
+    preempted: batches grow and shrink, slots and pages change hands, decode graphs of every size
+    run in turn between mixed steps.  float32: every stream must be the plain implementation's."""
+    import random
+    d = make_model_dir(tmp_path, "B", "float32", std=0.3)
+    cfg, w = P.read_model_dir(d)
+    V = cfg["vocab_size"]
+    rng = random.Random(5)
+    prompts = [random_prompt(V, rng.randint(1, 40), 300 + i) for i in range(30)]
+    lens = [rng.randint(1, 24) for _ in prompts]
+    want = [P.greedy_generate(cfg, w, p, n) for p, n in zip(prompts, lens)]
+    bs = TINY["B"][1]
+    eng = Engine(str(d), dtype="float32", block_size=bs, num_blocks=-(-150 // bs), max_num_seqs=5, max_num_batched_tokens=48)
+    got = {}
+    ids = []
+    pending = list(zip(prompts, lens))
+    while pending or eng.has_unfinished():
+        for _ in range(rng.randint(0, 3)):                   # requests arrive while others run
+            if pending:
+                p, n = pending.pop(0)
+                ids.append(eng.add_request(p, SamplingParams.greedy(max_tokens=n)))
+        for rid, tok, done in eng.step():
+            got.setdefault(rid, []).append(tok)
+    assert [got[i] for i in ids] == want
+    st = eng.stats()
+    assert st["preemptions"] > 0 and st["free_slots"] == 5 and st["free_pages"] == [-(-150 // bs)]
+
+
 def test_session_single_stream_calls(tmp_path):
     d = make_model_dir(tmp_path, "A", "float32")
     cfg, w = P.read_model_dir(d)
