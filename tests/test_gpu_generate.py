@@ -71,6 +71,34 @@ def test_temperature_and_topk_sampling(tmp_path, dtype):
     assert eng.generate(prompts[:1], greedy2) == g1          # temperature 0: the seed does not matter
 
 
+def test_topk_topp_sampling_on_the_device_equals_the_host_path(tmp_path):
+    """Decode steps draw top-k / top-p tokens inside the captured graph (and run ahead of the host);
+    with graphs off the host draws from the same candidates.  Same seeds: the same streams, and
+    the first tokens are what the plain implementation samples."""
+    d = make_model_dir(tmp_path, "B", "float32", std=0.2)
+    cfg, w = P.read_model_dir(d)
+    prompts = [random_prompt(1000, n, 90 + n) for n in (4, 21, 9, 33, 2)]
+    params = [SamplingParams(temperature=0.9, top_k=5, top_p=0.9, seed=7, max_tokens=30),
+              SamplingParams(temperature=1.2, top_k=0, top_p=0.8, seed=8, max_tokens=30),
+              SamplingParams(temperature=0.7, top_k=40, top_p=1.0, seed=9, max_tokens=30),
+              SamplingParams.with_temperature(0.8, seed=10, max_tokens=30),
+              SamplingParams.greedy(max_tokens=30)]
+    outs = []
+    for graphs in (True, False):
+        eng = Engine(str(d), dtype="float32", block_size=8, num_blocks=64, max_num_seqs=8, cuda_graphs=graphs)
+        assert eng._device_pool == graphs
+        outs.append(eng.generate(prompts, params))
+        if graphs:
+            assert any(k[2] for k in eng.runner._graphs)     # a graph with the draw in it was captured
+    assert outs[0] == outs[1]
+    toks = list(prompts[0])
+    for n in range(3):
+        v, i = P.topk_desc(P.forward_all_positions(cfg, w, toks)[-1], 64)
+        t = P.sample_topk(v, i, 0.9, 5, 0.9, P.step_seed(7, n))
+        assert t == outs[0][0][n]
+        toks.append(t)
+
+
 def test_warm_up_captures_every_bucket(tmp_path):
     d = make_model_dir(tmp_path, "C", "bfloat16")
     eng = Engine(str(d), dtype="bfloat16", max_num_seqs=5, max_model_len=600, num_blocks=64)

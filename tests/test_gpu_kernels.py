@@ -384,6 +384,49 @@ def test_sampling_kernels(ops):
     assert i3.cpu().tolist() == [[1, 2, 0, -1, -1]]
 
 
+def test_topk_in_two_stages_and_the_draw_among_the_candidates(ops):
+    """A vocabulary large enough for the two-stage top-k (64 stretches per row, then a merge), with
+    ties across stretches and rows with fewer than 64 finite entries; then the device's draw among
+    the candidates against the host's (sampling/sampler.py::sample_from_pool), parameter by parameter."""
+    import plain_llama as P
+    from zllm_b200.sampling.sampler import sample_from_pool
+    from zllm_b200.sampling.params import SamplingParams
+    g = torch.Generator().manual_seed(21)
+    V = 40003
+    lg = torch.randn(9, V, generator=g) * 3
+    lg[0, 5] = lg[0, 20000] = lg[0, 39990] = 50.0          # ties in three different stretches
+    lg[1, :] = float("-inf"); lg[1, 777] = 1.0; lg[1, 30000] = 2.0      # two finite entries
+    lg[2, 1000:1070] = 40.0                                 # more than 64 equal values in one stretch
+    vals = torch.zeros(9, 64, device=DEV)
+    idx = torch.zeros(9, 64, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        before = ops.launches
+        ops.topk(lg.to(DEV), 64, vals, idx)
+        assert ops.launches == before + 4                   # group maxima, stretches, two merges
+        for r in range(9):
+            v, i = P.topk_desc(lg[r], 64)
+            v = v + [-3.0e38] * (64 - len(v)); i = i + [-1] * (64 - len(i))
+            assert idx[r].cpu().tolist() == i, r
+            assert [float(x) for x in vals[r].cpu()] == [float(torch.tensor(x, dtype=torch.float32)) for x in v]
+    cases = [(0.8, 0, 0.9), (1.3, 5, 1.0), (0.7, 40, 0.5), (2.0, 64, 0.999), (0.01, 3, 0.3), (1.0, 1, 1.0), (0.9, 0, 0.05),
+             (0.0, 7, 0.9), (1.1, 10, 0.0)]
+    for trial in range(20):
+        seeds = [int(x) for x in torch.randint(0, 2 ** 31 - 1, (9,), generator=g)]
+        ptemp = torch.tensor([c[0] for c in cases], dtype=torch.float64)
+        topk = torch.tensor([c[1] for c in cases], dtype=torch.int32)
+        topp = torch.tensor([c[2] for c in cases], dtype=torch.float64)
+        out = torch.full((9,), -7, dtype=torch.int32, device=DEV)
+        ops.pool_draw(vals, idx, ptemp.to(DEV), topk.to(DEV), topp.to(DEV), torch.tensor(seeds, dtype=torch.int32).to(DEV), out)
+        got = out.cpu().tolist()
+        hv, hi = vals.cpu().tolist(), idx.cpu().tolist()
+        for r, (t, k, pp) in enumerate(cases):
+            if t <= 0.0:
+                assert got[r] == -7                         # not a pool row: left as it was
+            else:
+                want = sample_from_pool(hv[r], hi[r], SamplingParams(temperature=t, top_k=k, top_p=pp), seeds[r])
+                assert got[r] == want, (trial, r)
+
+
 def test_kernels_refuse_what_they_cannot_run(ops):
     from zllm_b200.errors import BackendError
     x = torch.zeros(4, 64, device=DEV)

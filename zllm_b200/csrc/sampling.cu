@@ -155,24 +155,27 @@ ZLLM_API int zllm_sample(const float* logits, const float* temps, const unsigned
 }
 
 // top-k candidates in descending order (value desc, index asc); fewer than k distinct
-// entries leave (-3e38, -1) sentinels.
-__global__ void __launch_bounds__(SAMPLE_THREADS) topk_kernel(const float* __restrict__ logits, float* __restrict__ vals,
-                                                              int* __restrict__ idxs, int V, int k) {
+// entries leave (-3e38, -1) sentinels.  One block selects among ``count`` candidates of one row:
+// K rounds of "the best strictly below the previous winner".  ``cidx`` == nullptr: candidate c is
+// vocabulary entry first + c; else its vocabulary index is cidx[c] (-1: no candidate).
+
+__device__ __forceinline__ void topk_select(const float* __restrict__ cv, const int* __restrict__ cidx, int first, int count,
+                                            float* __restrict__ vals, int* __restrict__ idxs, int k) {
     __shared__ float sv[32];
     __shared__ int si[32];
     __shared__ float win_v;
     __shared__ int win_i;
-    const int row = blockIdx.x;
-    const float* lg = logits + (size_t)row * V;
     float prev_v = INFINITY;
     int prev_i = -1;
     for (int r = 0; r < k; ++r) {
         float bv = -INFINITY;
         int bi = 0x7fffffff;
-        for (int c = threadIdx.x; c < V; c += blockDim.x) {
-            const float v = lg[c];
-            const bool below = (v < prev_v) || (v == prev_v && c > prev_i);
-            if (below && better(v, c, bv, bi)) { bv = v; bi = c; }
+        for (int c = threadIdx.x; c < count; c += blockDim.x) {
+            const int gi = cidx ? cidx[c] : first + c;
+            if (gi < 0) continue;
+            const float v = cv[c];
+            const bool below = (v < prev_v) || (v == prev_v && gi > prev_i);
+            if (below && better(v, gi, bv, bi)) { bv = v; bi = gi; }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -195,8 +198,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) topk_kernel(const float* __res
             }
             if (lane == 0) {
                 const bool none = (bi == 0x7fffffff);
-                vals[(size_t)row * k + r] = none ? -3.0e38f : bv;
-                idxs[(size_t)row * k + r] = none ? -1 : bi;
+                vals[r] = none ? -3.0e38f : bv;
+                idxs[r] = none ? -1 : bi;
                 win_v = none ? -INFINITY : bv;
                 win_i = none ? 0x7fffffff : bi;
             }
@@ -208,11 +211,255 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) topk_kernel(const float* __res
     }
 }
 
-ZLLM_API int zllm_topk(const float* logits, float* vals, int* idxs, int R, int V, int k, void* stream) {
+// the whole row in one block (any number of rows)
+__global__ void __launch_bounds__(SAMPLE_THREADS) topk_kernel(const float* __restrict__ logits, float* __restrict__ vals,
+                                                              int* __restrict__ idxs, int V, int k) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    topk_select(logits + (size_t)row * V, nullptr, 0, V, vals + (size_t)row * k, idxs + (size_t)row * k, k);
+}
+// Large vocabularies: selection by WARPS, without block barriers, and only among entries that can
+// be among the k best.  (1) the row is cut into 64 groups; the smallest of the 64 group maxima is a
+// floor: at least 64 entries are >= it, so nothing below it is among the 64 best.  (2) every one
+// of 256 stretches of the row is reduced by one warp to its entries >= the floor, best first (a
+// warp holds 32 x TOPK_E candidates in registers and runs rounds of "the largest key strictly
+// below the previous winner" with shuffles only; it stops at the floor).  (3) the stretches' lists
+// are merged the same way, 256 -> 32 -> 4 -> 1 lists.  The result is the k best of the row in the
+// order of the one-block kernel.  k <= 64, 16384 <= V <= 131072.
+#define TOPK_E 16                       // candidates per lane
+#define TOPK_WARP_SPAN (32 * TOPK_E)    // candidates per warp
+#define TOPK_STRETCHES 256              // stretches (warps) per row in step (2)
+#define TOPK_GROUPS 64
+
+// A candidate as one 64-bit key that orders like (value descending, index ascending): the float's
+// bits made monotonic in the high word, the inverted index in the low word; 0 = no candidate.
+__device__ __forceinline__ unsigned topk_mono(float v) {
+    const unsigned u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ unsigned long long topk_key(float v, int i) {
+    return ((unsigned long long)topk_mono(v) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)i);
+}
+__device__ __forceinline__ float topk_key_value(unsigned long long k) {
+    const unsigned m = (unsigned)(k >> 32);
+    return __uint_as_float((m & 0x80000000u) ? (m & 0x7FFFFFFFu) : ~m);
+}
+// Rounds over this lane's TOPK_E candidates (value cv[e], vocabulary index ci[e], -1: none) until k
+// winners are out, none is left, or the next one lies below ``floor_m`` (monotonic bits of the floor;
+// 0: no floor).  vals[0..k), idxs[0..k) get the winners, then (-3e38, -1).
+__device__ __forceinline__ void warp_topk(const float (&cv)[TOPK_E], const int (&ci)[TOPK_E], float* __restrict__ vals,
+                                          int* __restrict__ idxs, int k, unsigned floor_m) {
+    const int lane = threadIdx.x & 31;
+    for (int r = lane; r < k; r += 32) { vals[r] = -3.0e38f; idxs[r] = -1; }
+    __syncwarp();
+    unsigned long long key[TOPK_E];
+#pragma unroll
+    for (int e = 0; e < TOPK_E; ++e) key[e] = ci[e] >= 0 ? topk_key(cv[e], ci[e]) : 0ull;
+    unsigned long long prev = ~0ull;
+    for (int r = 0; r < k; ++r) {
+        unsigned long long m[TOPK_E];
+#pragma unroll
+        for (int e = 0; e < TOPK_E; ++e) m[e] = key[e] < prev ? key[e] : 0ull;
+#pragma unroll
+        for (int w = TOPK_E / 2; w > 0; w >>= 1)
+#pragma unroll
+            for (int e = 0; e < w; ++e) m[e] = m[e] > m[e + w] ? m[e] : m[e + w];
+        unsigned long long best = m[0];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        if (best == 0ull || (unsigned)(best >> 32) < floor_m) break;     // warp-uniform
+        if (lane == 0) {
+            vals[r] = topk_key_value(best);
+            idxs[r] = (int)(0xFFFFFFFFu - (unsigned)(best & 0xFFFFFFFFull));
+        }
+        prev = best;
+    }
+}
+
+// (1) grid (R, TOPK_GROUPS): the maximum of each group of the row
+__global__ void __launch_bounds__(256) topk_groupmax_kernel(const float* __restrict__ logits, float* __restrict__ gmax, int V) {
+    __shared__ float sm[8];
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x, grp = blockIdx.y;
+    const int len = (V + TOPK_GROUPS - 1) / TOPK_GROUPS;
+    const int first = grp * len, last = min(V, first + len);
+    const float* lg = logits + (size_t)row * V;
+    float m = -INFINITY;
+    for (int c = first + threadIdx.x; c < last; c += blockDim.x) m = fmaxf(m, lg[c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, sm[w]);
+        gmax[(size_t)row * TOPK_GROUPS + grp] = m;
+    }
+}
+// (2) grid (R, TOPK_STRETCHES / 8), 8 warps per block, a stretch per warp
+__global__ void __launch_bounds__(256) topk_stretch_kernel(const float* __restrict__ logits, const float* __restrict__ gmax,
+                                                           float* __restrict__ cand_v, int* __restrict__ cand_i, int V, int k) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float fl = fminf(gmax[(size_t)row * TOPK_GROUPS + lane], gmax[(size_t)row * TOPK_GROUPS + 32 + lane]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) fl = fminf(fl, __shfl_xor_sync(0xffffffffu, fl, o));
+    const int stretch = blockIdx.y * 8 + warp;
+    const int first = stretch * TOPK_WARP_SPAN;
+    const float* lg = logits + (size_t)row * V;
+    float cv[TOPK_E];
+    int ci[TOPK_E];
+#pragma unroll
+    for (int e = 0; e < TOPK_E; ++e) {
+        const int c = first + e * 32 + lane;
+        ci[e] = c < V ? c : -1;
+        cv[e] = c < V ? lg[c] : 0.f;
+    }
+    const size_t o = ((size_t)row * TOPK_STRETCHES + stretch) * k;
+    warp_topk(cv, ci, cand_v + o, cand_i + o, k, topk_mono(fl));
+}
+// (3a) grid (R, 4), 8 warps per block: 256 lists -> 32 lists, a warp takes 8 lists (8 k <= 512 slots)
+__global__ void __launch_bounds__(256) topk_merge1_kernel(const float* __restrict__ cand_v, const int* __restrict__ cand_i,
+                                                          float* __restrict__ m1_v, int* __restrict__ m1_i, int k) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x, warp = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const size_t src = ((size_t)row * TOPK_STRETCHES + warp * 8) * k;
+    float cv[TOPK_E];
+    int ci[TOPK_E];
+#pragma unroll
+    for (int e = 0; e < TOPK_E; ++e) {
+        const int c = e * 32 + lane;
+        const bool ok = c < 8 * k;
+        ci[e] = ok ? cand_i[src + c] : -1;
+        cv[e] = ok ? cand_v[src + c] : 0.f;
+    }
+    const size_t dst = ((size_t)row * 32 + warp) * k;
+    warp_topk(cv, ci, m1_v + dst, m1_i + dst, k, 0u);
+}
+// (3b) grid (R), 4 warps: 32 lists -> 4 lists -> the row's k best
+__global__ void __launch_bounds__(128) topk_merge2_kernel(const float* __restrict__ m1_v, const int* __restrict__ m1_i,
+                                                          float* __restrict__ vals, int* __restrict__ idxs, int k) {
+    __shared__ float tv[4 * 64];
+    __shared__ int ti[4 * 64];
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t src = ((size_t)row * 32 + warp * 8) * k;
+    float cv[TOPK_E];
+    int ci[TOPK_E];
+#pragma unroll
+    for (int e = 0; e < TOPK_E; ++e) {
+        const int c = e * 32 + lane;
+        const bool ok = c < 8 * k;
+        ci[e] = ok ? m1_i[src + c] : -1;
+        cv[e] = ok ? m1_v[src + c] : 0.f;
+    }
+    warp_topk(cv, ci, tv + warp * k, ti + warp * k, k, 0u);
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int e = 0; e < TOPK_E; ++e) {
+            const int c = e * 32 + lane;
+            const bool ok = c < 4 * k;
+            ci[e] = ok ? ti[c] : -1;
+            cv[e] = ok ? tv[c] : 0.f;
+        }
+        warp_topk(cv, ci, vals + (size_t)row * k, idxs + (size_t)row * k, k, 0u);
+    }
+}
+
+// cand_v / cand_i: scratch of R x (TOPK_STRETCHES + 32) x k + R x TOPK_GROUPS entries each, or nullptr
+// (one block per row).
+ZLLM_API int zllm_topk(const float* logits, float* vals, int* idxs, int R, int V, int k, float* cand_v, int* cand_i,
+                       void* stream) {
     if (R <= 0) return 0;
     if (V <= 0 || k <= 0) return ZLLM_ERR_UNSUPPORTED;
-    topk_kernel<<<R, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, vals, idxs, V, k);
-    return launch_status();
+    cudaStream_t s = (cudaStream_t)stream;
+    if (cand_v != nullptr && cand_i != nullptr && V >= 16384 && V <= TOPK_STRETCHES * TOPK_WARP_SPAN && k <= 64) {
+        float* m1_v = cand_v + (size_t)R * TOPK_STRETCHES * k;
+        int* m1_i = cand_i + (size_t)R * TOPK_STRETCHES * k;
+        float* gmax = m1_v + (size_t)R * 32 * k;
+        int rc = launch_pdl(topk_groupmax_kernel, dim3(R, TOPK_GROUPS), dim3(256), 0, s, logits, gmax, V);
+        if (rc) return rc;
+        rc = launch_pdl(topk_stretch_kernel, dim3(R, TOPK_STRETCHES / 8), dim3(256), 0, s, logits, (const float*)gmax, cand_v,
+                        cand_i, V, k);
+        if (rc) return rc;
+        rc = launch_pdl(topk_merge1_kernel, dim3(R, 4), dim3(256), 0, s, (const float*)cand_v, (const int*)cand_i, m1_v, m1_i, k);
+        if (rc) return rc;
+        return launch_pdl(topk_merge2_kernel, dim3(R), dim3(128), 0, s, (const float*)m1_v, (const int*)m1_i, vals, idxs, k);
+    }
+    return launch_pdl(topk_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, s, logits, vals, idxs, V, k);
+}
+
+// The draw among a row's descending candidates that zllm makes on the host
+// (src/backend/gpu/sampling.rs:35-56), on the device and in double precision, so that a decode
+// step with top-k / top-p sampling needs no host in between: probabilities exp((v - max) / T) of
+// the first min(top_k, valid) candidates, normalised; cut where the cumulative mass reaches
+// top_p; u from splitmix64(seed) (sampling.rs:24-30); inverse CDF.  Rows with ptemp <= 0 keep
+// what ``out`` already holds (they were sampled by the argmax / Gumbel kernel).
+__device__ __forceinline__ double splitmix01(unsigned seed) {
+    unsigned long long z = (unsigned long long)seed * 0x9E3779B97F4A7C15ull + 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return ((double)(z >> 40) + 0.5) / 16777216.0;
+}
+__global__ void pool_draw_kernel(const float* __restrict__ vals, const int* __restrict__ idxs, const double* __restrict__ ptemp,
+                                 const int* __restrict__ topk, const double* __restrict__ topp,
+                                 const unsigned* __restrict__ seeds, int* __restrict__ out, int k) {
+    __shared__ double probs[64];
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const double T = ptemp[row];
+    if (!(T > 0.0)) return;
+    const float* v = vals + (size_t)row * k;
+    const int* ix = idxs + (size_t)row * k;
+    int n = 0;
+    while (n < k && v[n] > -3.0e37f) ++n;                  // (every thread counts: k <= 64)
+    if (n == 0) { if (threadIdx.x == 0) out[row] = ix[0]; return; }
+    const int tk = topk[row];
+    const int kk = tk == 0 ? n : min(tk, n);
+    const double mx = (double)v[0];
+    for (int i = threadIdx.x; i < kk; i += blockDim.x) probs[i] = exp(((double)v[i] - mx) / T);
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    double z = 0.0;
+    for (int i = 0; i < kk; ++i) z += probs[i];
+    for (int i = 0; i < kk; ++i) probs[i] = probs[i] / z;
+    int cut = kk;
+    const double tp = topp[row];
+    if (tp > 0.0 && tp < 1.0) {
+        double cum = 0.0;
+        for (int i = 0; i < kk; ++i) {
+            cum += probs[i];
+            if (cum >= tp) { cut = i + 1; break; }
+        }
+    }
+    double zc = 0.0;
+    for (int i = 0; i < cut; ++i) zc += probs[i];
+    const double target = splitmix01(seeds[row]) * zc;
+    double acc = 0.0;
+    int pick = ix[cut - 1];
+    for (int i = 0; i < cut; ++i) {
+        acc += probs[i];
+        if (acc >= target) { pick = ix[i]; break; }
+    }
+    out[row] = pick;
+}
+
+// k <= 64
+ZLLM_API int zllm_pool_draw(const float* vals, const int* idxs, const double* ptemp, const int* topk, const double* topp,
+                            const unsigned* seeds, int* out, int R, int k, void* stream) {
+    if (R <= 0) return 0;
+    if (k <= 0 || k > 64) return ZLLM_ERR_UNSUPPORTED;
+    return launch_pdl(pool_draw_kernel, dim3(R), dim3(64), 0, (cudaStream_t)stream, vals, idxs, ptemp, topk, topp, seeds, out, k);
 }
 
 // After a decode step sampled ``out``: make the step's own inputs those of the next step, so

@@ -35,14 +35,18 @@ class StepEntry:
 class StepBuffers:
     """Pinned host + device int32 storage for a step of at most ``cap_rows`` rows."""
 
-    SECTIONS = ("token_ids", "positions", "row_slot", "want_rows", "decode_rows", "tiles", "temps", "seeds")
+    # the two float64 sections come first so that they are 8-byte aligned
+    SECTIONS = ("pool_temp", "pool_topp", "token_ids", "positions", "row_slot", "want_rows", "decode_rows", "tiles", "temps",
+                "seeds", "pool_topk")
 
     def __init__(self, cap_rows: int, cap_want: int, device):
         self.cap_rows = cap_rows
         self.cap_want = cap_want
         self.cap_tiles = cap_rows  # every portion has >= 2 rows, so tiles <= rows
         sizes = {"token_ids": cap_rows, "positions": cap_rows, "row_slot": cap_rows, "want_rows": cap_want,
-                 "decode_rows": cap_rows, "tiles": 4 * self.cap_tiles, "temps": cap_want, "seeds": cap_want}
+                 "decode_rows": cap_rows, "tiles": 4 * self.cap_tiles, "temps": cap_want, "seeds": cap_want,
+                 # candidate-pool sampling of a wanted row: temperature and top_p as float64 (two words), top_k
+                 "pool_temp": 2 * cap_want, "pool_topp": 2 * cap_want, "pool_topk": cap_want}
         self.offsets = {}
         off = 0
         for name in self.SECTIONS:

@@ -45,6 +45,8 @@ class Engine:
         self.generated = 0
         self.overlap = True            # launch the next decode step before reading this one's tokens
         self._ahead = None             # (requests, handle) of a decode step launched ahead
+        # top-k / top-p draws inside the decode graph (no host between steps); off: the host draws
+        self._device_pool = bool(ecfg.cuda_graphs and self.runner.device.type == "cuda" and hasattr(self.runner.ops, "pool_draw"))
 
     # ---- requests ------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -72,7 +74,7 @@ class Engine:
             return False
         for r in reqs:
             p = r.params
-            if p.needs_topk or p.needs_full or r.gen_index + uncommitted >= p.max_tokens \
+            if p.needs_full or (p.needs_topk and not self._device_pool) or r.gen_index + uncommitted >= p.max_tokens \
                     or len(r.tokens) + uncommitted + 1 >= self.runner.max_len:
                 return False
         return True
@@ -112,12 +114,19 @@ class Engine:
         first: List[Optional[int]] = [None] * len(plan.portions)
         if not plan.portions:
             temps = [0.0 if (p.is_greedy or p.needs_topk or p.needs_full) else p.temperature for p in dparams]
-            handle = self.runner.decode_launch([r.slot for r in dec], [r.tokens[-1] for r in dec], temps, dseeds)
+            # top-k / top-p rows are drawn among their 64 best candidates on the device when decode
+            # steps are graphs and no row needs the whole-vocabulary chain on the host
+            on_device = self._device_pool and any(p.needs_topk for p in dparams) and not any(p.needs_full for p in dparams)
+            pool = None
+            if on_device:
+                pool = ([p.temperature if p.needs_topk else 0.0 for p in dparams], [p.top_k for p in dparams],
+                        [p.top_p for p in dparams])
+            handle = self.runner.decode_launch([r.slot for r in dec], [r.tokens[-1] for r in dec], temps, dseeds, pool)
             nxt = self.runner.decode_continue(handle) if self._can_run_ahead(dec, 1) else None
             toks = self.runner.decode_collect(handle)
             if nxt is not None:
                 self._ahead = (list(dec), nxt)
-            if any(p.needs_topk or p.needs_full for p in dparams):
+            if not on_device and any(p.needs_topk or p.needs_full for p in dparams):
                 toks = self.sampler.host_finish(self.runner.last_logits, toks, dparams, dseeds)
             dtoks = toks
         else:

@@ -180,10 +180,14 @@ class ModelRunner:
 
     # ---- decode-only steps through a captured graph ----------------------------
     def decode_step(self, slots: Sequence[int], tokens: Sequence[int], temps: Sequence[float],
-                    seeds: Sequence[int]) -> torch.Tensor:
+                    seeds: Sequence[int], pool=None) -> torch.Tensor:
         """One decoded token for each slot; samples on the device (temperature <= 0: argmax)
         and returns the int32 token ids [len(slots)] on the device.  The logits of the step
-        stay in ``self.last_logits`` ([bucket, vocab], first len(slots) rows valid)."""
+        stay in ``self.last_logits`` ([bucket, vocab], first len(slots) rows valid).
+
+        ``pool`` = (temperatures, top_ks, top_ps) per slot: rows with a temperature > 0 there are
+        drawn among their 64 best candidates on the device (top-k / top-p sampling); their entry in
+        ``temps`` must then be 0.  Needs CUDA graphs."""
         entries = [StepEntry(s, (t,), (0,)) for s, t in zip(slots, tokens)]
         starts = self._prepare(entries)
         n = len(entries)
@@ -191,13 +195,21 @@ class ModelRunner:
         bucket = _bucket(n) if use_graph else n
         max_ctx = max(starts) + 1
         split_bucket = _bucket(self.ops.decode_splits(max_ctx)) if use_graph else 0
-        key = (bucket, split_bucket)
+        if pool is not None and not use_graph:
+            raise BackendError("sampling from the candidate pool on the device needs CUDA graphs")
+        key = (bucket, split_bucket, pool is not None)
         g = self._graphs.get(key)
         if g is None:
-            g = self._make_decode_graph(bucket, split_bucket, use_graph)
+            g = self._make_decode_graph(bucket, split_bucket, use_graph, pool is not None)
             self._graphs[key] = g
         buf = g["buf"]
         T, R, nd, nt, _ = fill_step(buf, entries, starts, pad_rows=bucket)
+        if pool is not None:
+            pt = buf.host_section("pool_temp").view("float64")
+            pp = buf.host_section("pool_topp").view("float64")
+            pk = buf.host_section("pool_topk")
+            pt[:bucket] = 0.0
+            pt[:n], pk[:n], pp[:n] = pool[0], pool[1], pool[2]
         # every row of the bucket is "wanted" so that the graph's shapes never change
         want = buf.host_section("want_rows")
         want[:bucket] = range(bucket)
@@ -225,10 +237,10 @@ class ModelRunner:
 
     # ---- decode steps whose tokens are read later (host work overlaps the device) ----------
     def decode_launch(self, slots: Sequence[int], tokens: Sequence[int], temps: Sequence[float],
-                      seeds: Sequence[int]):
+                      seeds: Sequence[int], pool=None):
         """``decode_step`` that does not wait: the sampled tokens are copied to pinned host memory
         behind the step and a handle is returned; ``decode_collect(handle)`` waits and reads them."""
-        out = self.decode_step(slots, tokens, temps, seeds)
+        out = self.decode_step(slots, tokens, temps, seeds, pool)
         return self._token_handle(out, len(slots), self._last_key, list(slots))
 
     def decode_continue(self, handle):
@@ -292,6 +304,12 @@ class ModelRunner:
         B = ctx.T
         seeds = buf.dev_section("seeds", B)
         self.ops.sample(logits, buf.dev_section("temps", B).view(torch.float32), seeds, g["out"])
+        if g.get("pool_vals") is not None:
+            # top-k / top-p rows: the 64 best candidates, then the draw among them, all on the device
+            self.ops.topk(logits, g["pool_vals"].shape[1], g["pool_vals"], g["pool_idx"])
+            self.ops.pool_draw(g["pool_vals"], g["pool_idx"], buf.dev_section("pool_temp", 2 * B).view(torch.float64),
+                               buf.dev_section("pool_topk", B), buf.dev_section("pool_topp", 2 * B).view(torch.float64),
+                               seeds, g["out"])
         if hasattr(self.ops, "advance_decode"):
             # the step's inputs become those of the next step: a burst replays without the host
             self.ops.advance_decode(ctx.token_ids, ctx.positions, ctx.row_slot, seeds, g["out"], g["hist"], g["counter"])
@@ -319,7 +337,7 @@ class ModelRunner:
         n = len(entries)
         bucket = _bucket(n)
         split_bucket = _bucket(self.ops.decode_splits(max(starts) + n_steps))
-        key = (bucket, split_bucket)
+        key = (bucket, split_bucket, False)
         g = self._graphs.get(key)
         if g is None:
             g = self._graphs[key] = self._make_decode_graph(bucket, split_bucket, True)
@@ -346,7 +364,7 @@ class ModelRunner:
 
     BURST_CAP = 1024
 
-    def _make_decode_graph(self, bucket: int, split_bucket: int, use_graph: bool):
+    def _make_decode_graph(self, bucket: int, split_bucket: int, use_graph: bool, pool: bool = False):
         buf = StepBuffers(bucket, bucket, self.device)
         ctx = make_context(buf, bucket, bucket, bucket, 0, 0, self.ws)
         ctx.max_context = split_bucket * self.ops.decode_split_keys if split_bucket else 0
@@ -354,7 +372,12 @@ class ModelRunner:
         out = torch.zeros(bucket, dtype=torch.int32, device=self.device)
         g = {"buf": buf, "ctx": ctx, "out": out, "logits": None, "graph": None,
              "hist": torch.zeros((self.BURST_CAP, bucket), dtype=torch.int32, device=self.device),
-             "counter": torch.zeros(1, dtype=torch.int32, device=self.device), "launches": 0}
+             "counter": torch.zeros(1, dtype=torch.int32, device=self.device), "launches": 0,
+             "pool_vals": None, "pool_idx": None}
+        if pool:
+            k = min(64, self.spec.vocab_size)
+            g["pool_vals"] = torch.zeros((bucket, k), dtype=torch.float32, device=self.device)
+            g["pool_idx"] = torch.zeros((bucket, k), dtype=torch.int32, device=self.device)
         if not use_graph:
             return g
         # neutral contents for warm-up and capture: every row is padding
@@ -391,8 +414,8 @@ class ModelRunner:
         while True:
             sb = 1
             while True:
-                if (b, sb) not in self._graphs:
-                    self._graphs[(b, sb)] = self._make_decode_graph(b, sb, True)
+                if (b, sb, False) not in self._graphs:
+                    self._graphs[(b, sb, False)] = self._make_decode_graph(b, sb, True)
                     n += 1
                 if sb >= self.ops.decode_splits(max_context):
                     break

@@ -47,6 +47,7 @@ class CudaOps:
         self.dtype = torch.bfloat16
         self._libs = {}
         self._sample_scratch = None
+        self._topk_scratch = None
         self._bound_stream = None
         self._tc_scratch = None
         self._kv_maps = {}
@@ -462,12 +463,39 @@ class CudaOps:
                                                         self._stream())
         self._check(code, "advance_decode")
 
+    TOPK_SCRATCH_ROWS = 128
+    TOPK_STRETCHES = 256                # csrc/sampling.cu
+
     def topk(self, logits, k, vals, idx):
+        """The k best entries of every row, value descending, index ascending."""
         self._dev(logits, vals, idx)
         R, V = logits.shape
         if logits.dtype != torch.float32 or vals.dtype != torch.float32 or idx.dtype != torch.int32 \
                 or tuple(vals.shape) != (R, k) or tuple(idx.shape) != (R, k):
             raise BackendError("topk: bad operand types or shapes")
+        cv = ci = None
+        if R <= self.TOPK_SCRATCH_ROWS and k <= 64:        # candidates of the two-stage kernels; fixed for graphs
+            if self._topk_scratch is None:
+                n = self.TOPK_SCRATCH_ROWS * ((self.TOPK_STRETCHES + 32) * 64 + 64)
+                self._topk_scratch = (torch.empty(n, dtype=torch.float32, device=self.device),
+                                      torch.empty(n, dtype=torch.int32, device=self.device))
+            cv, ci = self._topk_scratch
         code = self.lib("sampling").zllm_topk(_ptr(logits), _ptr(vals), _ptr(idx), c_int(R), c_int(V), c_int(k),
-                                              self._stream())
+                                              _ptr(cv), _ptr(ci), self._stream())
         self._check(code, "topk")
+        if cv is not None and 16384 <= V <= self.TOPK_STRETCHES * 512:
+            self.launches += 3               # group maxima, stretches, two merges
+
+    def pool_draw(self, vals, idx, ptemp, topk, topp, seeds, out):
+        """out[r] = a draw among row r's descending candidates (temperature ptemp[r], the first
+        topk[r] of them (0: all), cut at cumulative mass topp[r]); rows with ptemp <= 0 keep out[r].
+        ptemp, topp float64; the arithmetic is the host path's (sampling/sampler.py), in double."""
+        self._dev(vals, idx, ptemp, topk, topp, seeds, out)
+        R, k = vals.shape
+        if vals.dtype != torch.float32 or idx.dtype != torch.int32 or ptemp.dtype != torch.float64 or topp.dtype != torch.float64 \
+                or topk.dtype != torch.int32 or seeds.dtype != torch.int32 or out.dtype != torch.int32 or tuple(idx.shape) != (R, k) \
+                or min(ptemp.numel(), topk.numel(), topp.numel(), seeds.numel(), out.numel()) < R:
+            raise BackendError("pool_draw: bad operand types or shapes")
+        code = self.lib("sampling").zllm_pool_draw(_ptr(vals), _ptr(idx), _ptr(ptemp), _ptr(topk), _ptr(topp), _ptr(seeds),
+                                                   _ptr(out), c_int(R), c_int(k), self._stream())
+        self._check(code, "pool_draw")

@@ -7,8 +7,12 @@ Three ways, after the reference (zllm src/backend/gpu/batch.rs:184-194 picks
   device (argmax, or Gumbel-max with the counter-based noise of
   src/backend/gpu/shaders.rs:796-850); only token ids come back.
 * top-k / top-p: the device extracts each row's 64 best logits (BTOPK,
-  shaders.rs:852-905) and the host draws among them with splitmix64
-  (src/backend/gpu/sampling.rs:24-56).
+  shaders.rs:852-905) and the draw among them with splitmix64
+  (src/backend/gpu/sampling.rs:24-56) is made either on the host (``sample_from_pool``
+  below: mixed steps, engines without CUDA graphs) or, in double precision and with the
+  same arithmetic, by a kernel inside the captured decode step (csrc/sampling.cu,
+  ``ModelRunner.decode_step(pool=...)``), so that such requests decode without the host
+  between steps like greedy ones.
 * min-p, or top-k beyond the pool: the row's logits come to the host and the full
   chain temperature -> top-k -> softmax -> min-p -> top-p -> inverse-CDF draw of
   src/engine/sampler.rs:31-128 runs there.
