@@ -270,6 +270,24 @@ def main():
     while eng.has_unfinished():
         eng.step()
 
+    # ---- the same with top-k / top-p sampling (the draw among the candidates runs on the device) -------
+    for i in range(B):
+        eng.add_request(prompt(CONTEXT - K - W - slack - 2),
+                        SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=i, max_tokens=K + W + slack))
+    while eng.scheduler.prefilling or eng.scheduler.waiting:
+        eng.step()
+    for _ in range(W):
+        eng.step()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    n_tok_p = 0
+    for _ in range(K):
+        n_tok_p += len(eng.step())
+    torch.cuda.synchronize()
+    topp_s = time.perf_counter() - t1
+    while eng.has_unfinished():
+        eng.step()
+
     # ---- prefill of 2,048 tokens ------------------------------------------------------------
     s = runner.admit()
     toks = prompt(PROMPT)
@@ -308,6 +326,7 @@ def main():
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1),
+                   "decode_b8_top_p_e2e": round(n_tok_p / topp_s, 1),
                    "decode_b64_hbm_frac": round((weight_bytes + 64 * ctx64 * kv_per_token) / (ms64 / 1e3) / 1e9 / pk["hbm_gbs"], 4)},
         "clocks": clk,
     }

@@ -104,6 +104,7 @@ def test_warm_up_captures_every_bucket(tmp_path):
     eng = Engine(str(d), dtype="bfloat16", max_num_seqs=5, max_model_len=600, num_blocks=64)
     n = eng.warm_up()
     assert n == 4 * 3 and eng.warm_up() == 0           # rows 1, 2, 4, 8 x splits 1, 2, 4
+    assert eng.warm_up(max_batch=2, max_context=200, sampling=True) == 2      # the variants with the draw in them
     before = set(eng.runner._graphs)
     out = eng.generate([random_prompt(1536, 300, 1), random_prompt(1536, 5, 2)], SamplingParams.greedy(max_tokens=30))
     assert set(eng.runner._graphs) == before and len(out[0]) == 30

@@ -167,10 +167,11 @@ class Engine:
                     outs[rid].append(tok)
         return [outs[i] for i in ids]
 
-    def warm_up(self, max_batch: Optional[int] = None, max_context: Optional[int] = None) -> int:
+    def warm_up(self, max_batch: Optional[int] = None, max_context: Optional[int] = None, sampling: bool = False) -> int:
         """Capture every decode graph that requests up to these sizes can need (see
-        ``ModelRunner.capture_decode_graphs``); serving then never stalls on a capture."""
-        return self.runner.capture_decode_graphs(max_batch, max_context)
+        ``ModelRunner.capture_decode_graphs``); serving then never stalls on a capture.
+        ``sampling``: also the graphs that draw top-k / top-p tokens on the device."""
+        return self.runner.capture_decode_graphs(max_batch, max_context, pool=sampling and self._device_pool)
 
     def stats(self) -> dict:
         s = self.scheduler.stats()

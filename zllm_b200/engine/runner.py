@@ -401,10 +401,12 @@ class ModelRunner:
         g["graph"] = graph
         return g
 
-    def capture_decode_graphs(self, max_batch: Optional[int] = None, max_context: Optional[int] = None) -> int:
+    def capture_decode_graphs(self, max_batch: Optional[int] = None, max_context: Optional[int] = None,
+                              pool: bool = False) -> int:
         """Capture the decode graphs of every (rows, splits) bucket up to ``max_batch`` rows and
         ``max_context`` positions now, so that no step pays for a capture later (a capture takes a
-        few milliseconds).  Returns the number of graphs captured."""
+        few milliseconds).  ``pool``: also the variants that draw top-k / top-p tokens on the device.
+        Returns the number of graphs captured."""
         if not (self.ecfg.cuda_graphs and self.device.type == "cuda"):
             return 0
         max_batch = min(max_batch or self.ecfg.max_num_seqs, self.ecfg.max_num_seqs)
@@ -414,9 +416,10 @@ class ModelRunner:
         while True:
             sb = 1
             while True:
-                if (b, sb, False) not in self._graphs:
-                    self._graphs[(b, sb, False)] = self._make_decode_graph(b, sb, True)
-                    n += 1
+                for with_pool in ((False, True) if pool else (False,)):
+                    if (b, sb, with_pool) not in self._graphs:
+                        self._graphs[(b, sb, with_pool)] = self._make_decode_graph(b, sb, True, with_pool)
+                        n += 1
                 if sb >= self.ops.decode_splits(max_context):
                     break
                 sb *= 2
