@@ -63,6 +63,7 @@ def test_silu_mul(ops, dtype):
 
 
 LINEAR_SHAPES = [(1, 72, 64), (3, 200, 136), (8, 264, 520), (9, 96, 256), (16, 1000, 72), (17, 136, 2048),
+                 (5, 264, 8200), (8, 2048, 16384), (2, 40, 10240),      # few rows, long K: two CTAs share the passes over K
                  (64, 520, 264), (65, 72, 72), (127, 256, 192), (128, 384, 128), (129, 640, 320), (300, 1536, 448),
                  (515, 200, 1024)]
 

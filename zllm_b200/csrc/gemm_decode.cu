@@ -27,6 +27,8 @@
 // the rotated k and the v go straight to their cache page.
 #include "common.cuh"
 #include <cuda_pipeline.h>
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 #define MODE_STORE 0
 #define MODE_ADD 1
@@ -57,6 +59,7 @@ struct GemmDecodeParams {
     const int* table;
     int max_blocks, bs, store;
     int wide;               // weights may be read 32 bytes at a time
+    int ksplit;             // 1, or 2: the passes over K are shared by the two CTAs of a cluster
 };
 
 __device__ __forceinline__ void gd_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
@@ -116,7 +119,12 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
     __shared__ float ss_part[GD_WARPS][MP];
     __shared__ float inv_rms[MP];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int tile0 = blockIdx.x * RT;
+    // ksplit == 2 (a matrix with few rows and a long K: too few CTAs to fill the memory system):
+    // CTAs 2i and 2i + 1 form a cluster, take the even and the odd passes over K of the same rows,
+    // and rank 0 adds rank 1's partial tile (through distributed shared memory, after its own, so
+    // the order is fixed) before the epilogue.
+    const int ksplit = p.ksplit, crank = ksplit > 1 ? (int)(blockIdx.x % ksplit) : 0;
+    const int tile0 = (int)(blockIdx.x / ksplit) * RT;
     const int M = p.M, K = p.K;
     bf16* xs = xs_all + (size_t)warp * MP * GD_XSTRIDE;
     float acc[RT][NT][4];
@@ -159,11 +167,11 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
     // weights do not depend on the kernel before: fetch the first tile of the first pass, ask L2
     // for the rest of this CTA's weights, then wait
     pdl_trigger();
-    load_w(0, warp * GD_KW);
+    load_w(0, crank * GD_PASS + warp * GD_KW);
     for (int r = 0; r < RT; ++r) {
         int ra, rb;
         gd_rows(p, tile0 + r, g, ra, rb);
-        for (int ps = (r == 0 ? 1 : 0); ps < n_pass; ++ps) {
+        for (int ps = crank + (r == 0 ? ksplit : 0); ps < n_pass; ps += ksplit) {
             const int k = ps * GD_PASS + warp * GD_KW + t * 64;
             if (k < K) {
                 if (ra < p.w_rows) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.w + (size_t)ra * K + k));
@@ -173,7 +181,7 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
     }
     pdl_wait();
 
-    for (int ps = 0; ps < n_pass; ++ps) {
+    for (int ps = crank; ps < n_pass; ps += ksplit) {
         const int kb = ps * GD_PASS + warp * GD_KW;                          // this warp's 256 k of the pass
         // stage x[0..M)[kb .. kb+256) as bf16; lane takes 8 consecutive k of every row
         const int kx = kb + lane * 8;
@@ -221,7 +229,7 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
         __syncwarp();
 #pragma unroll
         for (int r = 0; r < RT; ++r) {
-            if (r > 0 || ps > 0) load_w(r, kb);
+            if (r > 0 || ps > crank) load_w(r, kb);
 #pragma unroll
             for (int s = 0; s < 4; ++s)
 #pragma unroll
@@ -264,15 +272,25 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
         inv_rms[threadIdx.x] = rsqrtf(tot / (float)K + p.eps);
     }
     __syncthreads();
+    const float* red1 = nullptr;                                             // rank 1's partial tiles, seen from rank 0
+    if (ksplit > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        red1 = cluster.map_shared_rank(red, 1);
+    }
     int rt_cur = 0;                                                          // the tile the epilogue is writing
     auto total = [&](int r16, int m) {
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < GD_WARPS; ++w) v += red[((size_t)w * RT * 16 + rt_cur * 16 + r16) * (MP + 1) + m];
+        if (red1 != nullptr) {
+#pragma unroll
+            for (int w = 0; w < GD_WARPS; ++w) v += red1[((size_t)w * RT * 16 + rt_cur * 16 + r16) * (MP + 1) + m];
+        }
         return FUSE_NORM ? v * inv_rms[m] : v;
     };
     const int mode = p.mode;
-    for (rt_cur = 0; rt_cur < RT; ++rt_cur) {
+    for (rt_cur = 0; rt_cur < RT && crank == 0; ++rt_cur) {
     const int tile = tile0 + rt_cur;
     if (tile * 16 >= p.w_rows) break;
     if (mode == MODE_STORE || mode == MODE_ADD) {
@@ -333,6 +351,7 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
         }
     }
     }   // tiles of the CTA
+    if (ksplit > 1) cg::this_cluster().sync();                               // rank 0 may still be reading rank 1's tiles
 }
 
 template <int NT, int RT, bool FUSE_NORM>
@@ -349,7 +368,23 @@ static int launch_gd(const GemmDecodeParams& p, cudaStream_t s) {
         attr_set = true;
     }
     const int tiles = (p.w_rows + 15) / 16;
-    return launch_pdl(kern, dim3((tiles + RT - 1) / RT), dim3(GD_WARPS * 32), smem, s, p);
+    const int groups = (tiles + RT - 1) / RT;
+    if (p.ksplit <= 1) return launch_pdl(kern, dim3(groups), dim3(GD_WARPS * 32), smem, s, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(groups * p.ksplit);
+    cfg.blockDim = dim3(GD_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.ksplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 template <int NT, bool FUSE_NORM>
@@ -382,6 +417,8 @@ ZLLM_API int zllm_gemm_decode(const void* x, const void* norm_w, int norm_w_bf16
     p.nq = nq; p.nkv = nkv; p.hd = hd; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages; p.table = table;
     p.max_blocks = max_blocks; p.bs = bs; p.store = store;
     p.wide = (K % 16 == 0) && (((uintptr_t)w & 31) == 0);
+    // few rows and at least four passes over K: two CTAs per group of rows (depends on the sizes only)
+    p.ksplit = (norm_w == nullptr && (p.w_rows + 15) / 16 <= 160 && K >= 4 * GD_PASS) ? 2 : 1;
     cudaStream_t s = (cudaStream_t)stream;
     const bool fuse = norm_w != nullptr;
     if (M <= 8) return fuse ? launch_gd_rt<1, true>(p, s) : launch_gd_rt<1, false>(p, s);
