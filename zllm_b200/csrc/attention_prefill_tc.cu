@@ -10,12 +10,14 @@
 //   O += P V       tcgen05.mma, M = 128, N = head_dim, K = 64 keys, with V read in place as an
 //                  MN-major operand (the cache's [position][dim] rows ARE that layout), O float32
 //                  in tensor memory; O is rescaled in tensor memory only when a row's running
-//                  maximum moved
+//                  maximum has moved by more than 2^8
 // Q, and every page of K and V ([positions][64 dims] boxes of the pool's tensor map), come by
-// TMA from one producer warp; one thread issues the MMAs; mbarriers and tcgen05.commit connect
-// the three roles.  Blocks alternate between two sets of buffers, so S of the next block is
-// computed while the softmax warps work on this one; two CTAs fit on an SM (head size 64).  A portion that starts at position p attends the prefix 0..p-1 from the
-// cache and its own rows causally; its own keys and values are already in the cache.
+// TMA from one producer warp (three K/V stages); one thread issues the MMAs; mbarriers and
+// tcgen05.commit connect the three roles.  Blocks alternate between two sets of S and P buffers,
+// so S of the next block is computed while the softmax warps work on this one; two CTAs fit on
+// an SM (head size 64).  The grid runs heads fastest and the tiles with the most keys first.
+// A portion that starts at position p attends the prefix 0..p-1 from the cache and its own
+// rows causally; its own keys and values are already in the cache.
 //
 // zllm's counterpart: coopmat_flash_attn.comp with its query offset
 // (src/backend/vulkan/mod.rs:1758-1777), whose math this follows.
@@ -100,16 +102,6 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_ld32_nowait(unsigned taddr, unsigned (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
