@@ -3,7 +3,9 @@
 Tiny A and tiny B differ in every size and option (head counts and groups, sizes
 that are no power of two, layers, vocabulary, eps, rope base and scaling, tied or
 untied head, page size).  Tiny C has head size 64 and a 4:1 group so that the
-tensor-core attention and product kernels run inside the whole-engine tests too.
+tensor-core attention and product kernels run inside the whole-engine tests too; tiny D has
+head size 128 (heads x head size larger than the width), a page of 32 positions and an odd
+vocabulary.
 """
 from __future__ import annotations
 
@@ -27,11 +29,16 @@ TINY_C = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_si
                                 original_max_position_embeddings=128),
               max_position_embeddings=1024, tie_word_embeddings=True)
 
+TINY_D = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=128, intermediate_size=384, vocab_size=777, rms_norm_eps=1e-5,
+              rope_theta=10000.0, rope_scaling=None, max_position_embeddings=1024, tie_word_embeddings=False)
+
 # name -> (config dict, page size, weight seed, std of matrices)
 TINY = {
     "A": (TINY_A, 16, 0, 0.02),
     "B": (TINY_B, 8, 1, 0.05),
     "C": (TINY_C, 16, 2, 0.04),
+    "D": (TINY_D, 32, 3, 0.05),
 }
 
 

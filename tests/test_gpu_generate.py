@@ -14,11 +14,11 @@ from configs import TINY, make_model_dir, random_prompt
 from zllm_b200 import Engine, SamplingParams, Session
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_matches_plain(tmp_path, name, dtype):
     """Sharper logits (larger weights) so that greedy choices are not rounding ties."""
-    d = make_model_dir(tmp_path, name, dtype, std=0.3 if name != "C" else 0.12)
+    d = make_model_dir(tmp_path, name, dtype, std={"C": 0.12, "D": 0.15}.get(name, 0.3))
     cfg, w = P.read_model_dir(d)
     V = cfg["vocab_size"]
     prompts = [random_prompt(V, n, 50 + n) for n in (5, 17, 33)]

@@ -29,7 +29,7 @@ def tolerances(dtype):
     return (F32_ATOL, 0.0) if dtype == "float32" else (0.0, BF16_MAX_OF_SCALE)
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_four_families(tmp_path, name, dtype):
     d = make_model_dir(tmp_path, name, dtype)
@@ -88,7 +88,7 @@ def gpu_runner(d, name, dtype, num_blocks, max_rows=512, slots=8, graphs=True):
                                                      cuda_graphs=graphs))
 
 
-@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("name", ["B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_one_by_one(tmp_path, name, dtype):
     """300 tokens decoded one at a time after a short prompt, through the graph path, for two
@@ -133,7 +133,7 @@ def test_decode_step_beyond_one_split_with_and_without_graphs(tmp_path, graphs):
             assert err <= bound, f"position {j}: {err:.3e} > {bound:.3e}"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_of_a_sequence(tmp_path, name, dtype):
     """Position 0 alone, positions 0-1, a one-token prompt then decode: the shortest contexts."""
