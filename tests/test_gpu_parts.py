@@ -1,7 +1,10 @@
 """Each part alone against the plain functions, and the generality of the assembly: a toy
 mixer with state of its own, defined HERE, is registered, built into a model beside attention
 layers (one with a window), run in an order that names a layer twice and lets an entry read
-another entry's cache, and stepped in portions -- without a change to the framework's files."""
+another entry's cache, and stepped in portions -- without a change to the framework's files.
+A second toy model does the same for a feed-forward with routing (three experts, the best one
+per row, router logits in 32-bit) and for another position encoding (a learned table added to
+the embedding output, attention without rotation)."""
 import math
 from dataclasses import dataclass
 
@@ -15,8 +18,9 @@ from gpu_util import DEV, make_cache, make_ctx
 from zllm_b200 import EngineConfig, ModelRunner, StepEntry
 from zllm_b200.config import register_architecture
 from zllm_b200.models.decoder import Runtime
-from zllm_b200.parts import (KVCacheSpec, LayerSpec, Mixer, ModelSpec, PartSpec, RunEntry, StateSpec, WeightSpec,
-                             build_part, register_mixer)
+from zllm_b200.parts import (FeedForward, KVCacheSpec, LayerSpec, Mixer, ModelSpec, PartSpec, PositionEncoding, RunEntry,
+                             StateSpec, WeightSpec, build_part, register_feed_forward, register_mixer,
+                             register_position_encoding)
 from zllm_b200.parts.feedforward import interleave_gate_up
 
 
@@ -260,3 +264,131 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     assert float((lg - ref_b).abs().max()) < 1e-4
     r.release(sb); r.release(sc)
     assert cm.free_pages() == [40, 40]
+
+
+# ------------------------------------------------------------------------------------------
+# a toy feed-forward with routing and a toy position encoding, defined in the test
+# ------------------------------------------------------------------------------------------
+
+@register_feed_forward("toy_best_expert")
+class BestExpert(FeedForward):
+    """out = p_e * down_e(relu(up_e h)^2) for the expert e with the largest router logit, p its
+    softmax probability; router logits and probabilities in float32."""
+
+    def __init__(self, hidden_size, intermediate_size, n_experts):
+        self.H, self.I, self.E = hidden_size, intermediate_size, n_experts
+
+    def weight_specs(self):
+        d = {"router": WeightSpec((self.E, self.H), "vector", ("normal", 0.5))}
+        for e in range(self.E):
+            d[f"up{e}"] = WeightSpec((self.I, self.H), "matrix", ("normal", 0.05))
+            d[f"down{e}"] = WeightSpec((self.H, self.I), "matrix", ("normal", 0.05))
+        return d
+
+    def forward(self, h, residual, ctx):
+        logits = h.float() @ self.router.float().T
+        prob, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+        for e in range(self.E):
+            rows = torch.nonzero(choice == e).flatten()
+            if rows.numel() == 0:
+                continue
+            up = torch.empty((rows.numel(), self.I), dtype=self.rt.dtype, device=h.device)
+            self.rt.ops.linear(h[rows].contiguous(), getattr(self, f"up{e}"), up, "store")
+            act = (torch.relu(up.float()) ** 2).to(self.rt.dtype)
+            y = torch.zeros((rows.numel(), self.H), dtype=torch.float32, device=h.device)
+            self.rt.ops.linear(act, getattr(self, f"down{e}"), y, "add")
+            residual[rows] += prob[rows, None] * y
+
+
+@register_position_encoding("toy_learned_absolute")
+class LearnedAbsolute(PositionEncoding):
+    """x_t += table[position_t] on the embedding output."""
+
+    def __init__(self, hidden_size, max_position):
+        self.H, self.n = hidden_size, max_position
+
+    def weight_specs(self):
+        return {"table": WeightSpec((self.n, self.H), "embedding", ("normal", 0.3))}
+
+    def on_embedding(self, x, ctx):
+        x += self.table[ctx.positions.long()].float()
+
+
+@dataclass
+class ToyRoutedConfig:
+    architecture: str = "ToyRoutedForCausalLM"
+    H: int = 48
+    V: int = 200
+
+
+def build_routed_spec(c: ToyRoutedConfig) -> ModelSpec:
+    attn = PartSpec("paged_attention", {"hidden_size": c.H, "n_heads": 3, "n_kv_heads": 3, "head_dim": 16,
+                                        "position_encoding": None, "window": None})
+    norm = PartSpec("rmsnorm", {"size": c.H, "eps": 1e-6})
+    routed = PartSpec("toy_best_expert", {"hidden_size": c.H, "intermediate_size": 40, "n_experts": 3})
+    dense = PartSpec("swiglu", {"hidden_size": c.H, "intermediate_size": 72})
+    qkvo = {f"mixer.{k}": k for k in ("q_proj", "k_proj", "v_proj", "o_proj")}
+    def names(i, ffn_names):
+        d = {"norm1.weight": f"l{i}.n1", "norm2.weight": f"l{i}.n2"}
+        d.update({k: f"l{i}.{v}" for k, v in qkvo.items()})
+        d.update({f"ffn.{k}": f"l{i}.{k}" for k in ffn_names})
+        return d
+    experts = ["router"] + [f"{w}{e}" for e in range(3) for w in ("up", "down")]
+    layers = [LayerSpec(attn, routed, norm, norm, "pre_norm", names(0, experts)),
+              LayerSpec(attn, dense, norm, norm, "pre_norm", names(1, ("gate_proj", "up_proj", "down_proj")))]
+    return ModelSpec("ToyRoutedForCausalLM", c.V, c.H, 128, layers, [RunEntry(0), RunEntry(1)], norm, "emb", {"weight": "fn"},
+                     "head", embedding_position=PartSpec("toy_learned_absolute", {"hidden_size": c.H, "max_position": 128}),
+                     embedding_position_names={"table": "pos"})
+
+
+register_architecture("ToyRoutedForCausalLM", lambda d: ToyRoutedConfig(**d), build_routed_spec)
+
+
+def plain_routed_forward(w, tokens):
+    T = len(tokens)
+    pos = torch.arange(T)
+    x = w["emb"][torch.tensor(tokens)] + w["pos"][pos]
+    for i in range(2):
+        h = P.rmsnorm(x, w[f"l{i}.n1"], 1e-6)
+        q, k, v = ((h @ w[f"l{i}.{n}_proj"].T).reshape(T, 3, 16) for n in "qkv")
+        x = x + P.causal_attention(q, k, v, 3, 3, pos, None) @ w[f"l{i}.o_proj"].T
+        h = P.rmsnorm(x, w[f"l{i}.n2"], 1e-6)
+        if i == 0:
+            prob, choice = torch.softmax(h @ w["l0.router"].T, dim=-1).max(dim=-1)
+            y = torch.stack([torch.relu(h[t] @ w[f"l0.up{int(choice[t])}"].T) ** 2 @ w[f"l0.down{int(choice[t])}"].T
+                             for t in range(T)])
+            x = x + prob[:, None] * y
+        else:
+            x = x + P.swiglu_mlp(h, w["l1.gate_proj"], w["l1.up_proj"], w["l1.down_proj"])
+    return P.rmsnorm(x, w["fn"], 1e-6) @ w["head"].T
+
+
+def test_toy_routed_feed_forward_and_learned_positions_are_registered_built_and_stepped():
+    r = ModelRunner(config=ToyRoutedConfig(), seed=6, engine_config=EngineConfig(
+        dtype="float32", block_size=8, num_blocks=24, max_num_seqs=3, max_num_batched_tokens=96, cuda_graphs=False))
+    from zllm_b200.weights.random_init import random_tensor
+    w = {n: random_tensor(n, s, 6, torch.float32, "cpu") for n, s in r.model.expected_tensors().items()}
+    assert w["pos"].shape == (128, 48) and w["l0.router"].shape == (3, 48)
+    g = torch.Generator().manual_seed(2)
+    ta = torch.randint(0, 200, (50,), generator=g).tolist()
+    tb = torch.randint(0, 200, (31,), generator=g).tolist()
+    ref_a, ref_b = plain_routed_forward(w, ta), plain_routed_forward(w, tb)
+    sa, sb = r.admit(), r.admit()
+    got_a, got_b = [], []
+    ia = ib = 0
+    for na, nb in ((9, 1), (1, 1), (25, 2), (2, 20), (13, 7)):
+        ents = []
+        if na:
+            ents.append(StepEntry(sa, ta[ia:ia + na], tuple(range(na))))
+        if nb:
+            ents.append(StepEntry(sb, tb[ib:ib + nb], tuple(range(nb))))
+        lg = r.step(ents).cpu()
+        got_a.append(lg[:na]); got_b.append(lg[na:])
+        ia += na; ib += nb
+    assert float((torch.cat(got_a) - ref_a).abs().max()) < 2e-4
+    assert float((torch.cat(got_b) - ref_b).abs().max()) < 2e-4
+    # the position table matters: the same tokens one position later give other logits
+    r.release(sa); r.release(sb)
+    sc = r.admit()
+    shifted = r.step([StepEntry(sc, [ta[0]] + ta[:8], tuple(range(9)))]).cpu()
+    assert float((shifted[1:] - ref_a[:8]).abs().max()) > 1e-2

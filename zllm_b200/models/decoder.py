@@ -48,12 +48,18 @@ def _build_layers(spec: ModelSpec):
         layers.append(Layer(build("norm", ls.norm1), build("mixer", ls.mixer), build("norm", ls.norm2),
                             build("feed_forward", ls.ffn), _REGISTRIES["arrangement"][ls.arrangement]))
     final_norm = build("norm", spec.final_norm)
-    return layers, final_norm
+    position = build("position_encoding", spec.embedding_position) if spec.embedding_position is not None else None
+    return layers, final_norm, position
 
 
-def _named_specs(spec: ModelSpec, layers: List[Layer], final_norm) -> Dict[str, WeightSpec]:
+def _named_specs(spec: ModelSpec, layers: List[Layer], final_norm, position=None) -> Dict[str, WeightSpec]:
     out: Dict[str, WeightSpec] = {}
     out[spec.embedding_name] = WeightSpec((spec.vocab_size, spec.hidden_size), "embedding", ("normal", spec.init_std))
+    if position is not None:
+        for local, ws in position.weight_specs().items():
+            if local not in spec.embedding_position_names:
+                raise ConfigError(f"no tensor name given for the embedding position encoding's {local}")
+            out[spec.embedding_position_names[local]] = ws
     for li, (ls, layer) in enumerate(zip(spec.layers, layers)):
         for pname, part in layer.parts().items():
             for local, ws in part.weight_specs().items():
@@ -70,15 +76,14 @@ def _named_specs(spec: ModelSpec, layers: List[Layer], final_norm) -> Dict[str, 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, WeightSpec]:
     """Every tensor the model folder must hold: name -> shape, role, init."""
-    layers, final_norm = _build_layers(spec)
-    return _named_specs(spec, layers, final_norm)
+    return _named_specs(spec, *_build_layers(spec))
 
 
 class DecoderModel:
     def __init__(self, spec: ModelSpec, rt: Runtime):
         self.spec = spec
         self.rt = rt
-        self.layers, self.final_norm = _build_layers(spec)
+        self.layers, self.final_norm, self.position = _build_layers(spec)
         for i, e in enumerate(spec.run_order):
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"run order entry {i} names layer {e.layer}, the model has {len(self.layers)}")
@@ -88,12 +93,14 @@ class DecoderModel:
             for part in layer.parts().values():
                 part.bind(rt)
         self.final_norm.bind(rt)
+        if self.position is not None:
+            self.position.bind(rt)
         self.embedding = None
         self.head = None
 
     # ---- weights -------------------------------------------------------
     def expected_tensors(self) -> Dict[str, WeightSpec]:
-        return _named_specs(self.spec, self.layers, self.final_norm)
+        return _named_specs(self.spec, self.layers, self.final_norm, self.position)
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         spec = self.spec
@@ -103,6 +110,8 @@ class DecoderModel:
                 local = {name: tensors[ls.tensor_names[f"{pname}.{name}"]] for name in part.weight_specs()}
                 part.load(local)
         self.final_norm.load({n: tensors[spec.final_norm_names[n]] for n in self.final_norm.weight_specs()})
+        if self.position is not None:
+            self.position.load({n: tensors[spec.embedding_position_names[n]] for n in self.position.weight_specs()})
         self.head = tensors[spec.head_name] if spec.head_name is not None else self.embedding
 
     # ---- cache needs ---------------------------------------------------
@@ -117,6 +126,8 @@ class DecoderModel:
         T = ctx.T
         x = ctx.ws.get("residual", (T, self.spec.hidden_size), torch.float32)
         ops.embedding(ctx.token_ids, self.embedding, x)
+        if self.position is not None:
+            self.position.on_embedding(x, ctx)
         for i, e in enumerate(self.spec.run_order):
             owner = i if e.cache_of is None else e.cache_of
             self.layers[e.layer].run(x, ctx, cache_views[owner], write_cache=e.cache_of is None)

@@ -105,6 +105,10 @@ class ModelSpec:
     head_name: Optional[str]            # None: the head is the embedding table (tied)
     init_std: float = 0.02
     norm_init_std: float = 0.0          # norm weights 1 + N(0, this) in random mode
+    # a position encoding that acts on the embedding output (absolute encodings); encodings that
+    # act inside a mixer (rotary) are parameters of that mixer instead
+    embedding_position: Optional[PartSpec] = None
+    embedding_position_names: Dict[str, str] = field(default_factory=dict)
 
 
 # --------------------------------------------------------------------------
