@@ -31,6 +31,16 @@ MODEL = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=16, hidden_si
              rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                                original_max_position_embeddings=8192),
              max_position_embeddings=131072, tie_word_embeddings=True)
+# layer sizes of the larger Llama shapes, for --case runs at other sizes (--shape)
+SHAPES = {
+    "1b": {},
+    "3b": dict(num_hidden_layers=28, hidden_size=3072, num_attention_heads=24, num_key_value_heads=8, head_dim=128,
+               intermediate_size=8192),
+    "8b": dict(num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+               intermediate_size=14336, tie_word_embeddings=False,
+               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                 original_max_position_embeddings=8192)),
+}
 CONTEXT = 4096
 PROMPT = 2048
 BLOCK = 16
@@ -117,10 +127,12 @@ def profile_case(args):
     import torch
     from zllm_b200 import EngineConfig, LlamaConfig, ModelRunner, StepEntry
 
-    shape = dict(MODEL)
+    shape = dict(MODEL, **SHAPES[args.shape])
     if args.layers:
         shape["num_hidden_layers"] = args.layers
     cfg = LlamaConfig.from_dict(shape)
+    pk, _ = peaks()
+    weight_bytes, kv_per_token, prefill_flops = model_numbers(cfg)
     B = args.batch
     ctx_len = args.context
     runner = ModelRunner(config=cfg, seed=2, random_on_device=True, engine_config=EngineConfig(
@@ -140,7 +152,10 @@ def profile_case(args):
             b.record(); torch.cuda.synchronize()
             times.append(a.elapsed_time(b))
             runner.release(s)
-        print(json.dumps({"case": "prefill", "tokens": args.tokens, "layers": cfg.num_hidden_layers, "ms": times}))
+        best = min(times)
+        print(json.dumps({"case": "prefill", "shape": args.shape, "tokens": args.tokens, "layers": cfg.num_hidden_layers,
+                          "ms": times, "tflops": round(prefill_flops(args.tokens) / best / 1e9, 1),
+                          "frac_of_peak": round(prefill_flops(args.tokens) / best / 1e9 / pk["bf16_tflops"], 3)}))
         return 0
     slots = [runner.admit() for _ in range(B)]
     for s in slots:
@@ -148,13 +163,16 @@ def profile_case(args):
         for i in range(0, ctx_len, PROMPT):
             runner.step([StepEntry(s, toks[i:i + PROMPT], ())])
     times = []
+    launches0 = runner.ops.launches
     for _ in range(max(2, args.steps)):
         torch.cuda.synchronize(); a.record()
         runner.decode_step(slots, rand(B), [0.0] * B, [0] * B)
         b.record(); torch.cuda.synchronize()
         times.append(a.elapsed_time(b))
-    print(json.dumps({"case": "decode", "batch": B, "context": ctx_len, "layers": cfg.num_hidden_layers, "ms": times,
-                      "launches_per_step": runner.ops.launches}))
+    gbs = (weight_bytes + B * ctx_len * kv_per_token) / min(times) / 1e6
+    print(json.dumps({"case": "decode", "shape": args.shape, "batch": B, "context": ctx_len, "layers": cfg.num_hidden_layers,
+                      "ms": times, "graphs": False, "gb_per_s": round(gbs, 1), "frac_of_peak": round(gbs / pk["hbm_gbs"], 3),
+                      "launches_per_step": (runner.ops.launches - launches0) // max(2, args.steps)}))
     return 0
 
 
@@ -170,6 +188,7 @@ def main():
     ap.add_argument("--context", type=int, default=1024, help="--case decode: cached positions per request")
     ap.add_argument("--tokens", type=int, default=PROMPT, help="--case prefill: tokens of the prompt")
     ap.add_argument("--layers", type=int, default=None, help="--case: fewer layers (profiling only)")
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="--case: layer sizes of another Llama shape")
     args = ap.parse_args()
 
     if args.impl == "reference":
