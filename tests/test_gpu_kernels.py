@@ -123,15 +123,26 @@ def test_streaming_product(ops, M, N, K, mode):
         assert err <= (2e-5 if odt == torch.float32 else 2 ** -8 * 1.5) * scale, (odt, err)
 
 
-SPLIT_K_SHAPES = [  # rows, N, K, epilogue: few 128 x 256 tiles, so the many-row kernel splits K (2..16 slices, the last
-    # slice ragged or empty) and a second kernel sums the slices in order
+SPLIT_K_SHAPES = [  # rows, N, K, epilogue: few tiles, so the many-row kernel takes tiles of 128 weight rows, splits K (2..16
+    # slices, the last slice ragged or empty) and a second kernel sums the slices in order
     (128, 2048, 8192, "add"), (200, 2048, 2048, "add"), (70, 3072, 2048, "store"), (512, 2048, 8192, "add"),
     (300, 264, 4104, "store"), (96, 520, 1352, "swiglu"), (130, 1000, 2056, "store"),
 ]
 
 
-@pytest.mark.parametrize("M,N,K,mode", SPLIT_K_SHAPES)
-def test_many_row_product_with_split_k(ops, M, N, K, mode):
+@pytest.mark.parametrize("tile", [0, 128, 256])
+@pytest.mark.parametrize("M,N,K,mode", SPLIT_K_SHAPES + [(700, 1288, 520, "store"), (1100, 640, 264, "swiglu"), (640, 904, 1032, "add")])
+def test_many_row_product_with_split_k(ops, M, N, K, mode, tile):
+    """``tile``: the kernel's tile width forced to 128 or 256 weight rows (0: chosen by the sizes),
+    so that both shapes run at every size."""
+    assert ops.lib("gemm_tc").zllm_gemm_tc_force_tile(tile) == 0
+    try:
+        _many_row_product(ops, M, N, K, mode)
+    finally:
+        ops.lib("gemm_tc").zllm_gemm_tc_force_tile(0)
+
+
+def _many_row_product(ops, M, N, K, mode):
     dtype = torch.bfloat16
     x = rnd((M, K), dtype, 5)
     if mode == "swiglu":

@@ -1,10 +1,11 @@
 // bfloat16 products for MANY rows (prompt portions) on the 5th-generation tensor cores:
 // out[m][n] = sum_k x[m][k] w[n][k], float32 accumulation in tensor memory.
 //
-// One CTA computes a 128 x 256 tile.  Operands come by TMA (cp.async.bulk.tensor, 128-byte
-// swizzle) into a 4-stage ring of shared-memory tiles [128][64] and [256][64]; one elected
-// thread issues tcgen05.mma (M = 128, N = 256, K = 16, four per stage) with the accumulator
-// in TMEM; tcgen05.commit hands stages back to the TMA warp and finally the accumulator to
+// One CTA computes a 128 x 256 tile (128 x 128 for products with few tiles and a short K: twice
+// the CTAs without splitting K).  Operands come by TMA (cp.async.bulk.tensor, 128-byte
+// swizzle) into a ring of shared-memory tiles [128][64] and [256][64] (4 stages; 6 of the narrow
+// tile); one elected thread issues tcgen05.mma (M = 128, N = tile width, K = 16, four per stage)
+// with the accumulator in TMEM; tcgen05.commit hands stages back to the TMA warp and finally the accumulator to
 // the four epilogue warps, which read it with tcgen05.ld (each warp its 32 lanes) and apply
 // the epilogue straight from registers: store, add into the float32 residual, or
 // silu(gate) * up on weights interleaved in groups of 8 gate + 8 up rows.  Rows beyond M and
@@ -24,13 +25,14 @@
 #define MODE_SWIGLU 2
 
 #define TC_BM 128
-#define TC_BN 256
+#define TC_BN 256                       // weight rows per tile; TC_BN_HALF for products with few tiles
+#define TC_BN_HALF 128
 #define TC_BK 64
 #define TC_STAGES 4
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
-#define TC_B_BYTES (TC_BN * TC_BK * 2)
-#define TC_STAGE_BYTES (TC_A_BYTES + TC_B_BYTES)
-#define TC_SMEM (TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */ + 4 * 2 * 4096 /* output staging */)
+#define TC_STAGE_BYTES_OF(BN) (TC_A_BYTES + (BN) * TC_BK * 2)
+#define TC_STAGES_OF(BN) ((BN) == TC_BN ? TC_STAGES : 6)      // the same shared memory either way
+#define TC_SMEM_OF(BN) (TC_STAGES_OF(BN) * TC_STAGE_BYTES_OF(BN) + 1024 /* alignment */ + 256 /* barriers */ + 4 * 2 * 4096 /* output staging */)
 #define TC_WAIT_LIMIT (1u << 24)
 
 __device__ int g_tc_error = 0;       // 0 ok; else 1 + index of the wait that gave up
@@ -165,19 +167,22 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x,
 // Persistent: a CTA walks the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles
 // fastest, so the CTAs running at the same time share weight panels in L2).  Two accumulators
 // of 256 columns live in TMEM: while the epilogue warps drain one, the MMA warp fills the other.
+template <int BN>
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                          const __grid_constant__ CUtensorMap map_w,
                                                          const __grid_constant__ CUtensorMap map_o, int M, int N, int K,
                                                          int mode, int out_bf16, int tiles_m, int tiles_n, int splits) {
+    constexpr int NSTAGE = TC_STAGES_OF(BN);
+    constexpr int STAGE_BYTES = TC_STAGE_BYTES_OF(BN);
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;         // swizzled tiles need 1024-byte alignment
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    // barriers: full[4], empty[4], acc_full[2], acc_empty[2]; then the TMEM slot
-    const unsigned bars = base + TC_STAGES * TC_STAGE_BYTES;
-    const unsigned bar_acc_full = bars + 8 * (2 * TC_STAGES);
+    // barriers: full[NSTAGE], empty[NSTAGE], acc_full[2], acc_empty[2]; then the TMEM slot
+    const unsigned bars = base + NSTAGE * STAGE_BYTES;
+    const unsigned bar_acc_full = bars + 8 * (2 * NSTAGE);
     const unsigned bar_acc_empty = bar_acc_full + 16;
-    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(base_ptr + TC_STAGES * TC_STAGE_BYTES + 128);
-    unsigned char* out_stage = base_ptr + TC_STAGES * TC_STAGE_BYTES + 256;      // [4 warps][2][32 rows x 128 bytes]
+    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(base_ptr + NSTAGE * STAGE_BYTES + 192);
+    unsigned char* out_stage = base_ptr + NSTAGE * STAGE_BYTES + 256;      // [4 warps][2][32 rows x 128 bytes]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // splits > 1: a unit of work is (tile, slice of K); the float32 partial tiles go to a scratch
     // [splits][M][weight rows] (map_o is then its 3-D map) and a second kernel sums them in order
@@ -186,9 +191,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     const int total_tiles = tiles_m * tiles_n * splits;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) {
+        for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(bars + 8 * s, 1);                                  // full: one arrive (expect_tx) + bytes
-            mbar_init(bars + 8 * (TC_STAGES + s), 1);                    // empty: one tcgen05.commit
+            mbar_init(bars + 8 * (NSTAGE + s), 1);                    // empty: one tcgen05.commit
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full + 8 * b, 1);                          // accumulator complete: one tcgen05.commit
@@ -198,7 +203,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     }
     if (warp == 1) {                                                     // this warp owns the tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(2 * TC_BN) : "memory");
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -213,22 +218,22 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
             int g = 0;                                                   // k steps issued over all tiles
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int ks = tile % splits, t2 = tile / splits;
-                const int m0 = (t2 % tiles_m) * TC_BM, n0 = (t2 / tiles_m) * TC_BN;
+                const int m0 = (t2 % tiles_m) * TC_BM, n0 = (t2 / tiles_m) * BN;
                 const int k_lo = ks * k_per, k_iters = max(0, min(k_all, k_lo + k_per) - k_lo);
                 for (int it = 0; it < k_iters; ++it, ++g) {
-                    const int s = g % TC_STAGES;
-                    ok = mbar_wait(bars + 8 * (TC_STAGES + s), ((g / TC_STAGES) & 1) ^ 1, 0);   // stage is free
+                    const int s = g % NSTAGE;
+                    ok = mbar_wait(bars + 8 * (NSTAGE + s), ((g / NSTAGE) & 1) ^ 1, 0);   // stage is free
                     if (!ok) break;
                     const unsigned full = bars + 8 * s;
-                    mbar_expect_tx(full, TC_STAGE_BYTES);
-                    const unsigned a_dst = base + s * TC_STAGE_BYTES;
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    const unsigned a_dst = base + s * STAGE_BYTES;
                     tma_load_2d(a_dst, &map_x, (k_lo + it) * TC_BK, m0, full);
                     tma_load_2d(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full);
                 }
             }
             if (!ok) {
                 // drain: the copies already issued must land before the CTA may exit
-                for (int q = max(0, g - TC_STAGES); q < g; ++q) mbar_wait(bars + 8 * (q % TC_STAGES), (q / TC_STAGES) & 1, 1);
+                for (int q = max(0, g - NSTAGE); q < g; ++q) mbar_wait(bars + 8 * (q % NSTAGE), (q / NSTAGE) & 1, 1);
             }
         }
     } else if (warp == 1) {
@@ -236,7 +241,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         if (lane == 0) {
             // instruction descriptor: D float32 [4,6) = 1, A and B bfloat16 [7,10) = [10,13) = 1, both
             // K-major, N >> 3 at [17,23), M >> 4 at [24,29)
-            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(TC_BN >> 3) << 17) |
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
                                    ((unsigned)(TC_BM >> 4) << 24);
             bool ok = true;
             int g = 0, j = 0;                                            // k steps consumed; tiles done by this CTA
@@ -245,20 +250,20 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                 ok = mbar_wait(bar_acc_empty + 8 * buf, ((j >> 1) & 1) ^ 1, 4);   // the epilogue has drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
-                const unsigned acc = tmem_acc + buf * TC_BN;
+                const unsigned acc = tmem_acc + buf * BN;
                 const int k_lo = (tile % splits) * k_per, k_iters = max(0, min(k_all, k_lo + k_per) - k_lo);
                 for (int it = 0; it < k_iters; ++it, ++g) {
-                    const int s = g % TC_STAGES;
-                    ok = mbar_wait(bars + 8 * s, (g / TC_STAGES) & 1, 2);         // operands have landed
+                    const int s = g % NSTAGE;
+                    ok = mbar_wait(bars + 8 * s, (g / NSTAGE) & 1, 2);         // operands have landed
                     if (!ok) break;
                     tc_fence_after();
-                    const unsigned a_addr = base + s * TC_STAGE_BYTES;
+                    const unsigned a_addr = base + s * STAGE_BYTES;
                     const unsigned long long adesc = umma_desc(a_addr);
                     const unsigned long long bdesc = umma_desc(a_addr + TC_A_BYTES);
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k)                 // 32 bytes along K per step: +2 in the address field
                         tc_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(bars + 8 * (TC_STAGES + s));               // stage free when these MMAs have read it
+                    tc_commit(bars + 8 * (NSTAGE + s));               // stage free when these MMAs have read it
                 }
                 tc_commit(bar_acc_full + 8 * buf);                       // accumulator complete (or abandoned)
             }
@@ -278,17 +283,17 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         unsigned n_staged = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
             const int ks = tile % splits, t2 = tile / splits;
-            const int m0 = (t2 % tiles_m) * TC_BM, n0 = (t2 / tiles_m) * TC_BN;
+            const int m0 = (t2 % tiles_m) * TC_BM, n0 = (t2 / tiles_m) * BN;
             const int buf = j & 1;
             const int y = m0 + q * 32;                                       // first output row of this warp
             const bool empty_slice = ks * k_per >= k_all;                    // no k step: the accumulator holds nothing
             ok = mbar_wait(bar_acc_full + 8 * buf, (j >> 1) & 1, 3);
             tc_fence_after();
             if (!ok) break;
-            const unsigned t_row = tmem_acc + buf * TC_BN + ((unsigned)(q * 32) << 16);
+            const unsigned t_row = tmem_acc + buf * BN + ((unsigned)(q * 32) << 16);
             const int n_limit = mode == MODE_SWIGLU ? 2 * N : N;
 #pragma unroll 1
-            for (int c = 0; c < TC_BN; c += 32) {
+            for (int c = 0; c < BN; c += 32) {
                 if (n0 + c >= n_limit) break;                            // warp-uniform
                 unsigned r[32];
                 tmem_ld32(t_row + c, r);
@@ -324,7 +329,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(2 * TC_BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(2 * BN) : "memory");
     }
 }
 
@@ -463,6 +468,8 @@ static int make_part_map(CUtensorMap* map, void* ptr, int splits, int M, int w_r
 // x [M,K] bf16, w [N,K] bf16 ([2N,K] for swiglu), out [M,N].  K % 8 == 0, N % 8 == 0, operands 16-byte aligned.
 // scratch (may be null): float32 workspace of scratch_bytes for products with few tiles, whose K is
 // then split over more CTAs and summed in a second pass, in a fixed order.
+static int g_force_bn = 0;
+
 ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_bf16,
                                void* scratch, long long scratch_bytes, void* stream) {
     if (M <= 0 || N <= 0) return 0;
@@ -473,27 +480,29 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
     CUtensorMap map_x, map_w, map_o;
     int e = make_map(&map_x, x, M, K, TC_BM);
     if (e) return e;
-    e = make_map(&map_w, w, w_rows, K, TC_BN);
-    if (e) return e;
     e = make_out_map(&map_o, out, M, N, out_bf16, mode == MODE_SWIGLU ? 16 : 32);
     if (e) return e;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t ce = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        if (ce != cudaSuccess) return (int)ce;
-        attr_set = true;
-    }
     static int n_sm = 0;
     if (n_sm == 0) {
         int dev = 0;
         cudaGetDevice(&dev);
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
     }
-    const int tiles_n = (w_rows + TC_BN - 1) / TC_BN, tiles_m = (M + TC_BM - 1) / TC_BM;
-    // few tiles: split K until about every SM has a unit of work, each with at least 4 k steps
-    // (the choice depends on the sizes only)
-    int splits = 1;
+    const int tiles_m = (M + TC_BM - 1) / TC_BM;
+    // Tiles of 256 weight rows; of 128 when those would leave half of the SMs without a tile.  A
+    // narrow tile loads as many bytes of x per k step for half the arithmetic, so with a long K and
+    // more than two row tiles the wide tile with K split over more CTAs is the faster one
+    // (measured: 512 rows, K 8192: 26.7 us wide, 30.5 us narrow; K 2048: 16.4 and 15.1).  The choice
+    // depends on the sizes only.
     const int k_all = (K + TC_BK - 1) / TC_BK;
+    int bn = tiles_m * ((w_rows + TC_BN - 1) / TC_BN) * 2 <= n_sm && (k_all <= 64 || tiles_m <= 2) ? TC_BN_HALF : TC_BN;
+    if (g_force_bn) bn = g_force_bn;
+    e = make_map(&map_w, w, w_rows, K, bn);
+    if (e) return e;
+    const int tiles_n = (w_rows + bn - 1) / bn;
+    // still few tiles: split K until about every SM has a unit of work, each with at least 4 k
+    // steps, and sum the slices in a second pass, in a fixed order
+    int splits = 1;
     while (tiles_n * tiles_m * splits * 2 <= n_sm && k_all / (splits * 2) >= 4 && splits < 32) splits *= 2;
     if (splits > 1 && (scratch == nullptr || (long long)splits * M * w_rows * 4 > scratch_bytes || (w_rows % 4) ||
                        ((uintptr_t)scratch & 15)))
@@ -504,14 +513,33 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
     }
     const int total = tiles_n * tiles_m * splits;
     const int grid = total < n_sm ? total : n_sm;                  // one CTA per SM walks the units
-    gemm_tc_kernel<<<grid, 192, TC_SMEM, (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode, out_bf16, tiles_m,
-                                                                  tiles_n, splits);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t ce = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_OF(TC_BN));
+        if (ce == cudaSuccess)
+            ce = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN_HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_OF(TC_BN_HALF));
+        if (ce != cudaSuccess) return (int)ce;
+        attr_set = true;
+    }
+    if (bn == TC_BN)
+        gemm_tc_kernel<TC_BN><<<grid, 192, TC_SMEM_OF(TC_BN), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode, out_bf16,
+                                                                                       tiles_m, tiles_n, splits);
+    else
+        gemm_tc_kernel<TC_BN_HALF><<<grid, 192, TC_SMEM_OF(TC_BN_HALF), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode,
+                                                                                                 out_bf16, tiles_m, tiles_n, splits);
     int rc = launch_status();
     if (rc || splits == 1) return rc;
     const long long n_thr = (long long)M * (N / 4);
     gemm_tc_reduce_kernel<<<(unsigned)((n_thr + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         (const float*)scratch, splits, M, w_rows, out, N, mode, out_bf16);
     return launch_status();
+}
+
+// Tests: force the tile width (128 or 256 weight rows; 0: by the sizes).
+ZLLM_API int zllm_gemm_tc_force_tile(int bn) {
+    if (bn != 0 && bn != TC_BN && bn != TC_BN_HALF) return ZLLM_ERR_UNSUPPORTED;
+    g_force_bn = bn;
+    return 0;
 }
 
 // The device flag that a bounded wait sets when it gives up (0: none); reading clears it.
