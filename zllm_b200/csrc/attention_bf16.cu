@@ -441,8 +441,8 @@ static int launch_decode(const void* qkv, void* out, const int* rows, int n_rows
                         (const bf16*)k_pages, (const bf16*)v_pages, table, max_blocks, bs, bs_shift, nq, nkv,
                         scale * 1.4426950408889634f, window, part_o, part_ml, max_splits);
     if (rc) return rc;
-    return launch_pdl(decode_combine_kernel<HD>, dim3(n_rows, nq), dim3(HD <= 64 ? 64 : 128), 0, s, rows, positions,
-                      row_slot, (const float*)part_o, (const float*)part_ml, (bf16*)out, nq, window, max_splits);
+    return launch_combine<HD>(n_rows, nq, n_splits, s, rows, positions, row_slot, (const float*)part_o, (const float*)part_ml,
+                              (bf16*)out, window, max_splits);
 }
 
 #define DISPATCH_HD(HDV, CALL)                                                     \

@@ -37,40 +37,91 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// out[row][head][:] = sum_s O_s e^{m_s - M} / sum_s l_s e^{m_s - M} over the row's splits, in split order
-template <int HD>
-__global__ void decode_combine_kernel(const int* __restrict__ rows, const int* __restrict__ positions,
-                                      const int* __restrict__ row_slot, const float* __restrict__ part_o,
-                                      const float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int window,
-                                      int max_splits) {
+// out[row][head][:] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the row's splits.
+// One block per (row, head).  A long context has hundreds of splits (256 at 65,536 positions) and
+// few rows, so the splits are spread over the block: for M and the denominator every thread
+// takes every blockDim-th split, for the numerator the block is G = blockDim / HD groups of HD
+// threads and group g takes the splits s = g, g + G, ...; the groups' sums are added in group
+// order.  The order of every sum is fixed by the number of splits and the block's size NTHR:
+// one group (the smallest block that covers HD) when the grid has at most 8 splits, else
+// COMBINE_THREADS; the launcher chooses from the grid's split count alone (launch_combine).
+#define COMBINE_THREADS 256
+template <int HD, int NTHR>
+__global__ void __launch_bounds__(NTHR) decode_combine_kernel(
+    const int* __restrict__ rows, const int* __restrict__ positions, const int* __restrict__ row_slot,
+    const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int window,
+    int max_splits) {
+    constexpr int nthr = NTHR, G = NTHR / HD;                // groups of HD threads (at least one)
+    __shared__ float s_red[NTHR / 32];
+    __shared__ float s_acc[NTHR];
     pdl_trigger();
     pdl_wait();
     const int row = rows[blockIdx.x];
     const int h = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     bf16* o = out + ((size_t)row * nq + h) * HD;
     if (row_slot[row] < 0) {
-        for (int d = threadIdx.x; d < HD; d += blockDim.x) o[d] = __float2bfloat16_rn(0.f);
+        for (int d = tid; d < HD; d += nthr) o[d] = __float2bfloat16_rn(0.f);
         return;
     }
     const int pos = positions[row];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int ns = (pos - lo) / SPLIT_KEYS + 1;
     const size_t base = ((size_t)blockIdx.x * nq + h) * max_splits;
-    float M = -INFINITY;
-    for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < ns; ++s) {
+    // M: the largest of the splits' maxima
+    float m = -INFINITY;
+    for (int s = tid; s < ns; s += nthr) m = fmaxf(m, part_ml[(base + s) * 2]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    float M = s_red[0];
+#pragma unroll
+    for (int w = 1; w < nthr / 32; ++w) M = fmaxf(M, s_red[w]);
+    __syncthreads();
+    // L: the denominator
+    float l = 0.f;
+    for (int s = tid; s < ns; s += nthr) {
         const float ms = part_ml[(base + s) * 2];
-        L += part_ml[(base + s) * 2 + 1] * ((ms == -INFINITY) ? 0.f : exp2f(ms - M));
+        l += part_ml[(base + s) * 2 + 1] * ((ms == -INFINITY) ? 0.f : exp2f(ms - M));
     }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    if (lane == 0) s_red[warp] = l;
+    __syncthreads();
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < nthr / 32; ++w) L += s_red[w];
     const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    // the numerator: group g sums its splits for dim d
+    const int g = tid / HD, d = tid - g * HD;
+    if (g < G) {
         float acc = 0.f;
-        for (int s = 0; s < ns; ++s) {
+#pragma unroll 4
+        for (int s = g; s < ns; s += G) {
             const float ms = part_ml[(base + s) * 2];
             acc += part_o[(base + s) * HD + d] * ((ms == -INFINITY) ? 0.f : exp2f(ms - M));
         }
-        o[d] = __float2bfloat16_rn(acc * inv);
+        s_acc[g * HD + d] = acc;
+    }
+    __syncthreads();
+    if (tid < HD) {
+        float acc = 0.f;
+#pragma unroll
+        for (int gg = 0; gg < G; ++gg) acc += s_acc[gg * HD + tid];
+        o[tid] = __float2bfloat16_rn(acc * inv);
     }
 }
 
+// The merge after a decode kernel with ``n_splits`` splits in its grid (programmatic dependent launch).
+template <int HD>
+static int launch_combine(int n_rows, int nq, int n_splits, cudaStream_t s, const int* rows, const int* positions,
+                          const int* row_slot, const float* part_o, const float* part_ml, bf16* out, int window,
+                          int max_splits) {
+    constexpr int ONE = HD <= 32 ? 32 : (HD <= 64 ? 64 : 128);
+    if (n_splits <= 8)
+        return launch_pdl(decode_combine_kernel<HD, ONE>, dim3(n_rows, nq), dim3(ONE), 0, s, rows, positions, row_slot, part_o,
+                          part_ml, out, nq, window, max_splits);
+    return launch_pdl(decode_combine_kernel<HD, COMBINE_THREADS>, dim3(n_rows, nq), dim3(COMBINE_THREADS), 0, s, rows, positions,
+                      row_slot, part_o, part_ml, out, nq, window, max_splits);
+}

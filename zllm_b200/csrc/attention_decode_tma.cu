@@ -404,8 +404,8 @@ static int launch_decode_tma_v(const CUtensorMap& mk, const CUtensorMap& mv, con
                         (const bf16*)k_pages, (const bf16*)v_pages, table, max_blocks, bs, (int)__builtin_ctz(bs), box_rows_for(bs, HD), nq, nkv,
                         scale * 1.4426950408889634f, part_o, part_ml, max_splits, (bf16*)out);
     if (rc || DIRECT) return rc;
-    return launch_pdl(decode_combine_kernel<HD>, dim3(n_rows, nq), dim3(HD <= 64 ? 64 : 128), 0, s, rows, positions,
-                      row_slot, (const float*)part_o, (const float*)part_ml, (bf16*)out, nq, 0, max_splits);
+    return launch_combine<HD>(n_rows, nq, n_splits, s, rows, positions, row_slot, (const float*)part_o, (const float*)part_ml,
+                              (bf16*)out, 0, max_splits);
 }
 
 template <int HD>
