@@ -12,10 +12,15 @@
 //                  in tensor memory; O is rescaled in tensor memory only when a row's running
 //                  maximum has moved by more than 2^8
 // Q, and every page of K and V ([positions][64 dims] boxes of the pool's tensor map), come by
-// TMA from one producer warp (three K/V stages); one thread issues the MMAs; mbarriers and
-// tcgen05.commit connect the three roles.  Blocks alternate between two sets of S and P buffers,
-// so S of the next block is computed while the softmax warps work on this one; two CTAs fit on
-// an SM (head size 64).  The grid runs heads fastest and the tiles with the most keys first.
+// TMA (three K/V stages).  Four warps have a role of their own: one loads keys, one loads values,
+// one thread issues the S products and one the O products; mbarriers and tcgen05.commit connect
+// them with the eight softmax warps.  Each role waits only for what it needs itself: S of block
+// kb + 2 is issued as soon as the softmax warps have S of block kb in registers (not when they
+// are done with it), and the keys of a later block never queue behind the values of an earlier
+// one.  (In one warp, as two threads or half-warps, the roles starve each other: spinning
+// divergent threads of a warp take turns slowly.)  Blocks alternate between two sets of S and P
+// buffers; two CTAs fit on an SM (head size 64).  The grid runs heads fastest and the tiles with
+// the most keys first.
 // A portion that starts at position p attends the prefix 0..p-1 from the cache and its own
 // rows causally; its own keys and values are already in the cache.
 //
@@ -32,7 +37,7 @@
 
 #define PT_ROWS 128
 #define PT_KEYS 64                      // keys per block: S has PT_KEYS columns of tensor memory
-#define PT_THREADS 320                  // TMA warp, MMA warp, 8 softmax warps
+#define PT_THREADS 384                  // warps: key loads, S issuer, 8 x softmax, value loads, O issuer
 #define PT_STAGES 3                     // K/V tiles in flight
 #define PT_LAZY 8.0f                     // see m_ref in the kernel
 #define PT_WAIT_LIMIT (1u << 22)
@@ -130,7 +135,7 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 // kb, and O += P V of block kb runs beside the softmax of block kb + 1.  Block kb uses set
 // kb & 1; the barriers of a set are in their phase kb >> 1.
 template <int HD>
-__global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
+__global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ tiles,
     const int* __restrict__ table, int max_blocks, int bs, int bs_shift, int box_rows, int nq, int nkv, float scale) {
@@ -152,7 +157,7 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
     unsigned char* p_ptr = base_ptr + Q_BYTES + 2 * NS * KV_BYTES;
     const unsigned bars = p_tiles + 2 * P_BYTES;
     // ring stage st = kb % NS: keys landed, values landed, keys read (S complete), values read (O += P V complete);
-    // set b = kb & 1: S complete, P written (S read, O rescaled), O += P V complete
+    // set b = kb & 1: S complete, P written (O rescaled), O += P V complete, S taken out of tensor memory
     const unsigned bar_q = bars;
     auto bar_k = [&](int st) { return bars + 8 * (1 + st); };
     auto bar_v = [&](int st) { return bars + 8 * (1 + NS + st); };
@@ -161,7 +166,8 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
     auto bar_s = [&](int b) { return bars + 8 * (1 + 4 * NS + b); };
     auto bar_p = [&](int b) { return bars + 8 * (3 + 4 * NS + b); };
     auto bar_o = [&](int b) { return bars + 8 * (5 + 4 * NS + b); };
-    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(p_ptr + 2 * P_BYTES + 8 * (7 + 4 * NS));
+    auto bar_sfree = [&](int b) { return bars + 8 * (7 + 4 * NS + b); };
+    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(p_ptr + 2 * P_BYTES + 8 * (9 + 4 * NS));
     float* xmax = reinterpret_cast<float*>(p_ptr + 2 * P_BYTES + 256);      // [2 sets][2 halves][128 rows] maxima, then [2 halves][128 rows] sums
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -187,6 +193,7 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
             mbar_init(bar_s(b), 1);                          // tcgen05.commit
             mbar_init(bar_p(b), 8);                          // one arrive per softmax warp
             mbar_init(bar_o(b), 1);                          // tcgen05.commit
+            mbar_init(bar_sfree(b), 8);                      // one arrive per softmax warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -203,15 +210,18 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
     tc_fence_after();
     const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 2 * PT_KEYS;
 
-    if (warp == 0) {
-        // ---------------- TMA producer (whole warp: lanes 0..15 key boxes, 16..31 value boxes) ----------------
-        if (lane == 0) {
+    if (warp == 0 || warp == 10) {
+        // ---------------- TMA producers: warp 0 the key boxes, warp 10 the value boxes (16 lanes each) ----------------
+        // Two warps, so each waits only for its own stages: the keys of a later block never wait
+        // behind the values of an earlier one.
+        if (warp == 0 && lane == 0) {
             mbar_expect_tx(bar_q, Q_BYTES);
             for (int hf = 0; hf < HALVES; ++hf)
                 tma_load_2d(q_tile + hf * QHALF, &map_q, h * HD + hf * 64, row0, bar_q);
         }
         const int n_box = (PT_KEYS / box_rows) * HALVES;
-        const int bidx = lane & 15, is_v = lane >> 4;
+        const int bidx = lane & 15, is_v = warp == 10;
+        const unsigned hmask = 0xffffffffu;
         const int pb = bidx / HALVES, half = bidx - pb * HALVES;
         const unsigned box_bytes = (unsigned)box_rows * 128u;
         bool ok = true;
@@ -219,52 +229,58 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
             const int st = kb % NS;
             const unsigned prev = ((kb / NS) & 1) ^ 1;       // parity of the phase in which block kb - NS used the stage
             const int key_b0 = kb * PT_KEYS + pb * box_rows;
-            bool valid = bidx < n_box && key_b0 <= last_pos;
+            bool valid = lane < 16 && bidx < n_box && key_b0 <= last_pos;
             int y = 0;
             if (valid) {
                 const int page = trow[key_b0 >> bs_shift];
                 valid = page >= 0;
                 y = (page * nkv + kvh) * bs + (key_b0 & (bs - 1));
             }
-            const unsigned m = __ballot_sync(0xffffffffu, valid);
-            // keys: the stage is free when S of block kb - NS is complete
-            if (kb >= NS) ok = __all_sync(0xffffffffu, mbar_wait(bar_kfree(st), prev, 0));
-            if (!ok) break;
-            if (lane == 0) mbar_expect_tx(bar_k(st), (unsigned)__popc(m & 0xffffu) * box_bytes);
-            __syncwarp();
-            if (valid && !is_v)
-                tma_load_2d(k_tiles + st * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_k, half * 64, y, bar_k(st));
-            // values: the stage is free when O += P V of block kb - NS is complete
-            if (kb >= NS) ok = __all_sync(0xffffffffu, mbar_wait(bar_vfree(st), prev, 1));
-            if (!ok) break;
-            // boxes that are not loaded must not hold garbage: probability 0 x NaN is NaN
-            bool zeroed = false;
-            for (int bx = 0; bx < n_box; ++bx) {
-                if ((m >> (16 + bx)) & 1u) continue;
-                const int pbb = bx / HALVES, hb = bx - pbb * HALVES;
-                uint4* z = reinterpret_cast<uint4*>(v_ptr + st * KV_BYTES + hb * KHALF + pbb * box_rows * 128);
-                for (int i = lane; i < box_rows * 8; i += 32) z[i] = make_uint4(0, 0, 0, 0);
-                zeroed = true;
+            const unsigned m = __ballot_sync(hmask, valid);
+            if (!is_v) {
+                // keys: the stage is free when S of block kb - NS is complete
+                if (kb >= NS) ok = __all_sync(hmask, mbar_wait(bar_kfree(st), prev, 0));
+                if (!ok) break;
+                if (lane == 0) mbar_expect_tx(bar_k(st), (unsigned)__popc(m) * box_bytes);
+                __syncwarp(hmask);
+                if (valid)
+                    tma_load_2d(k_tiles + st * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_k, half * 64, y, bar_k(st));
+            } else {
+                // values: the stage is free when O += P V of block kb - NS is complete
+                if (kb >= NS) ok = __all_sync(hmask, mbar_wait(bar_vfree(st), prev, 1));
+                if (!ok) break;
+                // boxes that are not loaded must not hold garbage: probability 0 x NaN is NaN
+                bool zeroed = false;
+                for (int bx = 0; bx < n_box; ++bx) {
+                    if ((m >> bx) & 1u) continue;
+                    const int pbb = bx / HALVES, hb = bx - pbb * HALVES;
+                    uint4* z = reinterpret_cast<uint4*>(v_ptr + st * KV_BYTES + hb * KHALF + pbb * box_rows * 128);
+                    for (int i = lane; i < box_rows * 8; i += 32) z[i] = make_uint4(0, 0, 0, 0);
+                    zeroed = true;
+                }
+                if (zeroed) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp(hmask);
+                if (lane == 0) mbar_expect_tx(bar_v(st), (unsigned)__popc(m) * box_bytes);
+                __syncwarp(hmask);
+                if (valid)
+                    tma_load_2d(v_tiles + st * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_v, half * 64, y, bar_v(st));
             }
-            if (zeroed) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_expect_tx(bar_v(st), (unsigned)__popc(m >> 16) * box_bytes);
-            __syncwarp();
-            if (valid && is_v)
-                tma_load_2d(v_tiles + st * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_v, half * 64, y, bar_v(st));
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            // D float32, A and B bfloat16; N >> 3 at [17,23), M >> 4 at [24,29); bit 16: B is MN-major
+    } else if (warp == 1 || warp == 11) {
+        // ---------------- MMA issuers: warp 1 issues S = Q K^T, warp 11 issues O += P V (one lane each) ----------------
+        // Two warps, so neither product waits for what only the other needs: S of block kb + 2 is
+        // issued as soon as its keys have landed and the softmax warps have taken S of block kb out of
+        // tensor memory; O += P V of block kb as soon as P is written and the values have landed.
+        // D float32, A and B bfloat16; N >> 3 at [17,23), M >> 4 at [24,29); bit 16: B is MN-major
+        if (warp == 1 && lane == 0) {
             const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(PT_KEYS >> 3) << 17) |
                                      ((unsigned)(PT_ROWS >> 4) << 24);
-            const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) |
-                                     ((unsigned)(PT_ROWS >> 4) << 24);
-            // S[kb & 1] = Q K(kb)^T
-            auto issue_s = [&](int kb) -> bool {
+            bool ok = mbar_wait(bar_q, 0, 2);
+            for (int kb = 0; kb < n_blocks && ok; ++kb) {
                 const int b = kb & 1, st = kb % NS;
-                if (!mbar_wait(bar_k(st), (kb / NS) & 1, 3)) return false;
+                ok = mbar_wait(bar_k(st), (kb / NS) & 1, 3);
+                if (ok && kb >= 2) ok = mbar_wait(bar_sfree(b), ((kb - 2) >> 1) & 1, 10);   // S of block kb - 2 is in registers
+                if (!ok) break;
                 tc_fence_after();
                 const unsigned kt = k_tiles + st * KV_BYTES;
 #pragma unroll
@@ -273,11 +289,15 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
                            umma_desc(kt + (ks >> 2) * KHALF + (ks & 3) * 32, 16), idesc_s, ks > 0 ? 1u : 0u);
                 tc_commit(bar_s(b));
                 tc_commit(bar_kfree(st));
-                return true;
-            };
-            bool ok = mbar_wait(bar_q, 0, 2);
-            ok = ok && issue_s(0);
-            if (n_blocks > 1) ok = ok && issue_s(1);
+            }
+            if (!ok) {                                       // let the others run into their own limits quickly
+                for (int b = 0; b < 2; ++b) tc_commit(bar_s(b));
+                for (int st = 0; st < NS; ++st) tc_commit(bar_kfree(st));
+            }
+        } else if (warp == 11 && lane == 0) {
+            const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) |
+                                     ((unsigned)(PT_ROWS >> 4) << 24);
+            bool ok = true;
             for (int kb = 0; kb < n_blocks && ok; ++kb) {
                 const int b = kb & 1, st = kb % NS;
                 ok = mbar_wait(bar_p(b), (kb >> 1) & 1, 4) && mbar_wait(bar_v(st), (kb / NS) & 1, 5);
@@ -290,10 +310,11 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
                            idesc_o, (kb > 0 || j > 0) ? 1u : 0u);
                 tc_commit(bar_o(b));
                 tc_commit(bar_vfree(st));
-                if (kb + 2 < n_blocks) ok = issue_s(kb + 2);  // S[b] is free: the softmax warps have read block kb
             }
-            if (!ok) for (int b = 0; b < 2; ++b) { tc_commit(bar_s(b)); tc_commit(bar_o(b)); }
-            if (!ok) for (int st = 0; st < NS; ++st) { tc_commit(bar_kfree(st)); tc_commit(bar_vfree(st)); }
+            if (!ok) {
+                for (int b = 0; b < 2; ++b) tc_commit(bar_o(b));
+                for (int st = 0; st < NS; ++st) tc_commit(bar_vfree(st));
+            }
         }
     } else {
         // ---------------- softmax: warps 2..9, two threads per query row ----------------
@@ -327,6 +348,9 @@ __global__ void __launch_bounds__(PT_THREADS) prefill_tc_kernel(
 #pragma unroll
                 for (int i = 0; i < HK; ++i) sv[i] = __uint_as_float(v[i]);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sfree(b));        // S[b] may be overwritten with block kb + 2
             float mx = -INFINITY;
             if (kb * PT_KEYS + PT_KEYS - 1 > pos0) {         // the block reaches past the first row's own key
 #pragma unroll
