@@ -18,9 +18,8 @@
 // kb + 2 is issued as soon as the softmax warps have S of block kb in registers (not when they
 // are done with it), and the keys of a later block never queue behind the values of an earlier
 // one.  (In one warp, as two threads or half-warps, the roles starve each other: spinning
-// divergent threads of a warp take turns slowly.)  Blocks alternate between two sets of S and P
-// buffers; two CTAs fit on an SM (head size 64).  The grid runs heads fastest and the tiles with
-// the most keys first.
+// divergent threads of a warp take turns slowly.)  Two CTAs fit on an SM (head size 64).  The
+// grid runs heads fastest and the tiles with the most keys first.
 // A portion that starts at position p attends the prefix 0..p-1 from the cache and its own
 // rows causally; its own keys and values are already in the cache.
 //
@@ -38,7 +37,6 @@
 #define PT_ROWS 128
 #define PT_KEYS 64                      // keys per block: S has PT_KEYS columns of tensor memory
 #define PT_THREADS 384                  // warps: key loads, S issuer, 8 x softmax, value loads, O issuer
-#define PT_STAGES 3                     // K/V tiles in flight
 #define PT_LAZY 8.0f                     // see m_ref in the kernel
 #define PT_WAIT_LIMIT (1u << 22)
 
@@ -130,12 +128,14 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 
 // tiles [n_tiles][4] = (first row, rows (<= 128), slot, position of first row)
 //
-// Blocks alternate between two sets of buffers (S in tensor memory; K, V and P in shared
-// memory), so the tensor core computes S of block kb + 1 while the softmax warps work on block
-// kb, and O += P V of block kb runs beside the softmax of block kb + 1.  Block kb uses set
-// kb & 1; the barriers of a set are in their phase kb >> 1.
-template <int HD>
-__global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kernel(
+// NSB buffers of S in tensor memory, NPB tiles of P and NS stages of K and V in shared memory;
+// CTAS CTAs are to fit on an SM.  Block kb uses S buffer kb % NSB (its barriers are in their phase
+// kb / NSB), P buffer kb % NPB and stage kb % NS.  An S buffer is free again as soon as the
+// softmax warps have it in registers, so one is enough for the tensor core to compute S of block
+// kb + 1 beside the softmax of block kb; O += P V of block kb runs beside the softmax of block
+// kb + 1 when there are two P tiles.
+template <int HD, int NSB, int NPB, int NS, int CTAS>
+__global__ void __launch_bounds__(PT_THREADS, CTAS) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ tiles,
     const int* __restrict__ table, int max_blocks, int bs, int bs_shift, int box_rows, int nq, int nkv, float scale) {
@@ -145,19 +145,19 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
     constexpr int Q_BYTES = HALVES * QHALF;
     constexpr int KV_BYTES = HALVES * KHALF;
     constexpr int P_BYTES = (PT_KEYS / 64) * QHALF;          // [128 rows][PT_KEYS keys] as K-major halves of 64 keys
-    constexpr int TMEM_COLS = 256;                           // S: 2 x PT_KEYS columns, O: HD columns
-    static_assert(2 * PT_KEYS + HD <= TMEM_COLS, "tensor memory");
+    constexpr int TMEM_COLS = NSB * PT_KEYS + HD <= 128 ? 128 : 256;     // S: NSB x PT_KEYS columns, O: HD columns
+    static_assert(NSB * PT_KEYS + HD <= TMEM_COLS, "tensor memory");
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    // Q | K ring | V ring | P0 P1 | barriers
-    constexpr int NS = PT_STAGES;
+    // Q | K ring | V ring | P tiles | barriers
     const unsigned q_tile = base, k_tiles = base + Q_BYTES, v_tiles = k_tiles + NS * KV_BYTES, p_tiles = v_tiles + NS * KV_BYTES;
     unsigned char* v_ptr = base_ptr + Q_BYTES + NS * KV_BYTES;
     unsigned char* p_ptr = base_ptr + Q_BYTES + 2 * NS * KV_BYTES;
-    const unsigned bars = p_tiles + 2 * P_BYTES;
+    const unsigned bars = p_tiles + NPB * P_BYTES;
     // ring stage st = kb % NS: keys landed, values landed, keys read (S complete), values read (O += P V complete);
-    // set b = kb & 1: S complete, P written (O rescaled), O += P V complete, S taken out of tensor memory
+    // S buffer kb % NSB: S complete, S taken out of tensor memory; P buffer kb % NPB: P written
+    // (O rescaled), O += P V complete
     const unsigned bar_q = bars;
     auto bar_k = [&](int st) { return bars + 8 * (1 + st); };
     auto bar_v = [&](int st) { return bars + 8 * (1 + NS + st); };
@@ -167,8 +167,8 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
     auto bar_p = [&](int b) { return bars + 8 * (3 + 4 * NS + b); };
     auto bar_o = [&](int b) { return bars + 8 * (5 + 4 * NS + b); };
     auto bar_sfree = [&](int b) { return bars + 8 * (7 + 4 * NS + b); };
-    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(p_ptr + 2 * P_BYTES + 8 * (9 + 4 * NS));
-    float* xmax = reinterpret_cast<float*>(p_ptr + 2 * P_BYTES + 256);      // [2 sets][2 halves][128 rows] maxima, then [2 halves][128 rows] sums
+    volatile unsigned* tmem_slot = reinterpret_cast<volatile unsigned*>(p_ptr + NPB * P_BYTES + 8 * (9 + 4 * NS));
+    float* xmax = reinterpret_cast<float*>(p_ptr + NPB * P_BYTES + 256);      // [2 sets][2 halves][128 rows] maxima, then [2 halves][128 rows] sums
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // Heads run fastest over the grid and later tiles (which see more keys) come first, so the
@@ -189,11 +189,13 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
             mbar_init(bar_kfree(st), 1);                     // tcgen05.commit
             mbar_init(bar_vfree(st), 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < NSB; ++b) {
             mbar_init(bar_s(b), 1);                          // tcgen05.commit
+            mbar_init(bar_sfree(b), 8);                      // one arrive per softmax warp
+        }
+        for (int b = 0; b < NPB; ++b) {
             mbar_init(bar_p(b), 8);                          // one arrive per softmax warp
             mbar_init(bar_o(b), 1);                          // tcgen05.commit
-            mbar_init(bar_sfree(b), 8);                      // one arrive per softmax warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -208,10 +210,10 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + 2 * PT_KEYS;
+    const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + NSB * PT_KEYS;
 
-    if (warp == 0 || warp == 10) {
-        // ---------------- TMA producers: warp 0 the key boxes, warp 10 the value boxes (16 lanes each) ----------------
+    if (warp == 0 || warp == 2) {
+        // ---------------- TMA producers: warp 0 the key boxes, warp 2 the value boxes (16 lanes each) ----------------
         // Two warps, so each waits only for its own stages: the keys of a later block never wait
         // behind the values of an earlier one.
         if (warp == 0 && lane == 0) {
@@ -220,7 +222,7 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
                 tma_load_2d(q_tile + hf * QHALF, &map_q, h * HD + hf * 64, row0, bar_q);
         }
         const int n_box = (PT_KEYS / box_rows) * HALVES;
-        const int bidx = lane & 15, is_v = warp == 10;
+        const int bidx = lane & 15, is_v = warp == 2;
         const unsigned hmask = 0xffffffffu;
         const int pb = bidx / HALVES, half = bidx - pb * HALVES;
         const unsigned box_bytes = (unsigned)box_rows * 128u;
@@ -266,8 +268,8 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
                     tma_load_2d(v_tiles + st * KV_BYTES + half * KHALF + pb * box_rows * 128, &map_v, half * 64, y, bar_v(st));
             }
         }
-    } else if (warp == 1 || warp == 11) {
-        // ---------------- MMA issuers: warp 1 issues S = Q K^T, warp 11 issues O += P V (one lane each) ----------------
+    } else if (warp == 1 || warp == 3) {
+        // ---------------- MMA issuers: warp 1 issues S = Q K^T, warp 3 issues O += P V (one lane each) ----------------
         // Two warps, so neither product waits for what only the other needs: S of block kb + 2 is
         // issued as soon as its keys have landed and the softmax warps have taken S of block kb out of
         // tensor memory; O += P V of block kb as soon as P is written and the values have landed.
@@ -277,9 +279,9 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
                                      ((unsigned)(PT_ROWS >> 4) << 24);
             bool ok = mbar_wait(bar_q, 0, 2);
             for (int kb = 0; kb < n_blocks && ok; ++kb) {
-                const int b = kb & 1, st = kb % NS;
+                const int b = kb % NSB, st = kb % NS;
                 ok = mbar_wait(bar_k(st), (kb / NS) & 1, 3);
-                if (ok && kb >= 2) ok = mbar_wait(bar_sfree(b), ((kb - 2) >> 1) & 1, 10);   // S of block kb - 2 is in registers
+                if (ok && kb >= NSB) ok = mbar_wait(bar_sfree(b), ((kb - NSB) / NSB) & 1, 10);   // S of block kb - NSB is in registers
                 if (!ok) break;
                 tc_fence_after();
                 const unsigned kt = k_tiles + st * KV_BYTES;
@@ -291,16 +293,16 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
                 tc_commit(bar_kfree(st));
             }
             if (!ok) {                                       // let the others run into their own limits quickly
-                for (int b = 0; b < 2; ++b) tc_commit(bar_s(b));
+                for (int b = 0; b < NSB; ++b) tc_commit(bar_s(b));
                 for (int st = 0; st < NS; ++st) tc_commit(bar_kfree(st));
             }
-        } else if (warp == 11 && lane == 0) {
+        } else if (warp == 3 && lane == 0) {
             const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) |
                                      ((unsigned)(PT_ROWS >> 4) << 24);
             bool ok = true;
             for (int kb = 0; kb < n_blocks && ok; ++kb) {
-                const int b = kb & 1, st = kb % NS;
-                ok = mbar_wait(bar_p(b), (kb >> 1) & 1, 4) && mbar_wait(bar_v(st), (kb / NS) & 1, 5);
+                const int b = kb % NPB, st = kb % NS;
+                ok = mbar_wait(bar_p(b), (kb / NPB) & 1, 4) && mbar_wait(bar_v(st), (kb / NS) & 1, 5);
                 if (!ok) break;
                 tc_fence_after();
                 const unsigned pt = p_tiles + b * P_BYTES, vt = v_tiles + st * KV_BYTES;
@@ -312,18 +314,18 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
                 tc_commit(bar_vfree(st));
             }
             if (!ok) {
-                for (int b = 0; b < 2; ++b) tc_commit(bar_o(b));
+                for (int b = 0; b < NPB; ++b) tc_commit(bar_o(b));
                 for (int st = 0; st < NS; ++st) tc_commit(bar_vfree(st));
             }
         }
     } else {
-        // ---------------- softmax: warps 2..9, two threads per query row ----------------
+        // ---------------- softmax: warps 4..11, two threads per query row ----------------
         // Warps w and w + 4 share the 32 rows of TMEM lane quadrant w & 3; ``half`` says which half
         // of a block's keys (and, for O, of the head's dims) a thread takes.  The two threads of a
         // row exchange their half-maxima through shared memory (one named barrier per quadrant).
         constexpr int HK = PT_KEYS / 2;                      // keys of a block per thread
         constexpr int HO = HD / 2;                           // dims of O per thread
-        const int q = warp & 3, half = (warp - 2) >> 2;
+        const int q = warp & 3, half = (warp - 4) >> 2;
         const int r = q * 32 + lane;                         // row of the tile = TMEM lane
         const unsigned lane_base = (unsigned)(q * 32) << 16;
         const int my_pos = pos0 + r;                         // the last key this row sees
@@ -335,22 +337,22 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
         float m_ref = -INFINITY, l_run = 0.f;                // l_run: this thread's half of the row's sum
         bool ok = true;
         for (int kb = 0; kb < n_blocks; ++kb) {
-            const int b = kb & 1;
-            const unsigned ph = (kb >> 1) & 1;
+            const int b = kb & 1;                            // set of the maxima's exchange buffer
+            const int sb = kb % NSB, pb = kb % NPB;          // S and P buffers of the block
             const int key0 = kb * PT_KEYS + half * HK;       // first key of this thread's half
-            ok = ok && mbar_wait(bar_s(b), ph, 6);
+            ok = ok && mbar_wait(bar_s(sb), (kb / NSB) & 1, 6);
             tc_fence_after();
             // the row's scores of this half, once, into registers
             float sv[HK];
             {
                 unsigned v[HK];
-                tmem_ld32(tmem_s + b * PT_KEYS + half * HK + lane_base, v);
+                tmem_ld32(tmem_s + sb * PT_KEYS + half * HK + lane_base, v);
 #pragma unroll
                 for (int i = 0; i < HK; ++i) sv[i] = __uint_as_float(v[i]);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_sfree(b));        // S[b] may be overwritten with block kb + 2
+            if (lane == 0) mbar_arrive(bar_sfree(sb));       // the buffer may be overwritten with S of block kb + NSB
             float mx = -INFINITY;
             if (kb * PT_KEYS + PT_KEYS - 1 > pos0) {         // the block reaches past the first row's own key
 #pragma unroll
@@ -373,7 +375,7 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
                 m_ref = m_new;
                 l_run *= corr;
                 if (kb > 0) {
-                    ok = ok && mbar_wait(bar_o((kb - 1) & 1), ((kb - 1) >> 1) & 1, 7);   // O is complete up to block kb - 1
+                    ok = ok && mbar_wait(bar_o((kb - 1) % NPB), ((kb - 1) / NPB) & 1, 7);   // O is complete up to block kb - 1
                     tc_fence_after();
 #pragma unroll 1
                     for (int c = 0; c < HO; c += 32) {
@@ -387,9 +389,9 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
                 }
             }
             const float msafe = (m_ref == -INFINITY) ? 0.f : m_ref;
-            // P[b] was last read by the products of block kb - 2
-            if (kb >= 2) ok = ok && mbar_wait(bar_o(b), ph ^ 1, 9);
-            unsigned char* pt = p_ptr + b * P_BYTES;
+            // the P buffer was last read by the products of block kb - NPB
+            if (kb >= NPB) ok = ok && mbar_wait(bar_o(pb), ((kb - NPB) / NPB) & 1, 9);
+            unsigned char* pt = p_ptr + pb * P_BYTES;
             float rs = 0.f;
 #pragma unroll
             for (int ch = 0; ch < HK / 8; ++ch) {                            // 16-byte chunks of 8 keys
@@ -411,13 +413,13 @@ __global__ void __launch_bounds__(PT_THREADS, HD == 64 ? 2 : 1) prefill_tc_kerne
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the MMA reads P through the async proxy
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_p(b));
+            if (lane == 0) mbar_arrive(bar_p(pb));
         }
         // the finished rows: O / l as bfloat16, each thread its half of the dims
         xmax[(4 + half) * PT_ROWS + r] = l_run;
         asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
         const float l_row = l_run + xmax[(4 + (half ^ 1)) * PT_ROWS + r];
-        ok = ok && mbar_wait(bar_o((n_blocks - 1) & 1), ((n_blocks - 1) >> 1) & 1, 8);
+        ok = ok && mbar_wait(bar_o((n_blocks - 1) % NPB), ((n_blocks - 1) / NPB) & 1, 8);
         tc_fence_after();
         const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
 #pragma unroll 1
@@ -477,7 +479,7 @@ static int make_map(CUtensorMap* map, const void* ptr, long long rows, long long
     return r == CUDA_SUCCESS ? 0 : ZLLM_ERR_UNSUPPORTED;
 }
 
-template <int HD>
+template <int HD, int NSB, int NPB, int NS, int CTAS>
 static int launch_prefill_tc(const void* qkv, int T, void* out, const int* tiles, int n_tiles, const void* k_pages,
                              const void* v_pages, long long num_pages, const int* table, int max_blocks, int bs, int nq,
                              int nkv, float scale, cudaStream_t s) {
@@ -489,9 +491,9 @@ static int launch_prefill_tc(const void* qkv, int T, void* out, const int* tiles
     if (e) return e;
     e = make_map(&mv, v_pages, num_pages * nkv * bs, HD, box_rows);
     if (e) return e;
-    const size_t smem = 1024 + (size_t)(HD / 64) * (PT_ROWS + 2 * PT_STAGES * PT_KEYS) * 128 +
-                        2 * (size_t)(PT_KEYS / 64) * PT_ROWS * 128 + 256 + 6 * PT_ROWS * sizeof(float);
-    auto kern = prefill_tc_kernel<HD>;
+    const size_t smem = 1024 + (size_t)(HD / 64) * (PT_ROWS + 2 * NS * PT_KEYS) * 128 +
+                        NPB * (size_t)(PT_KEYS / 64) * PT_ROWS * 128 + 256 + 6 * PT_ROWS * sizeof(float);
+    auto kern = prefill_tc_kernel<HD, NSB, NPB, NS, CTAS>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t ce = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -514,14 +516,17 @@ ZLLM_API int zllm_attention_prefill_tc(const void* qkv, int T, void* out, const 
         (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15))
         return ZLLM_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (hd == 64)
-        return launch_prefill_tc<64>(qkv, T, out, tiles, n_tiles, k_pages, v_pages, num_pages, table, max_blocks, bs, nq,
-                                     nkv, scale, s);
-    if (hd == 128)
-        return launch_prefill_tc<128>(qkv, T, out, tiles, n_tiles, k_pages, v_pages, num_pages, table, max_blocks, bs, nq,
-                                      nkv, scale, s);
+#define PT_ARGS qkv, T, out, tiles, n_tiles, k_pages, v_pages, num_pages, table, max_blocks, bs, nq, nkv, scale, s
+    // S buffers, P buffers, K/V stages, CTAs per SM (measured, 2,048 tokens at prefix 30,720):
+    // head size 64: one S buffer and two stages 1,084 us, two and three 1,127 us; head size 128:
+    // two CTAs per SM (one S, one P buffer, two stages) 2,108 us, one CTA with two and three 2,088 us
+    if (hd == 64) return launch_prefill_tc<64, 1, 2, 2, 2>(PT_ARGS);
+    if (hd == 128) return launch_prefill_tc<128, 2, 2, 3, 1>(PT_ARGS);
+#undef PT_ARGS
     return ZLLM_ERR_UNSUPPORTED;
 }
+
+
 
 // The device flag that a bounded wait sets when it gives up (0: none); reading clears it.
 ZLLM_API int zllm_attention_prefill_tc_error(void) {
