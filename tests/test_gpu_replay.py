@@ -224,10 +224,9 @@ def test_llama_1b_layer_sizes(tmp_path, dtype):
 
 
 @pytest.mark.parametrize("name", ["C", "D"])
-def test_large_mixed_step_with_decoded_rows_on_a_second_stream(tmp_path, name):
-    """A step of more than 512 rows that holds decoded rows beside a prompt portion: the decoded
-    rows' attention kernels run on a second stream beside the portion's.  The logits must be those
-    of the plain implementation, and bit for bit those of the same step on one stream."""
+def test_large_mixed_step_with_decoded_rows(tmp_path, name):
+    """A step of more than 512 rows that holds two decoded rows around a prompt portion: the
+    many-row products, the tiled attention and the split attention in one step."""
     dtype = "bfloat16"
     d = make_model_dir(tmp_path, name, dtype)
     cfg, w = P.read_model_dir(d)
@@ -235,16 +234,10 @@ def test_large_mixed_step_with_decoded_rows_on_a_second_stream(tmp_path, name):
     pa, pb, pc = random_prompt(V, 70, 11), random_prompt(V, 301, 12), random_prompt(V, 640, 13)
     refs = [P.forward_all_positions(cfg, w, p) for p in (pa, pb, pc)]
     _, rel = tolerances(dtype)
-    outs = []
-    for fork_rows in (512, 10 ** 9):
-        r = gpu_runner(d, name, dtype, num_blocks=4 * (1100 // TINY[name][1]), max_rows=1024, graphs=False)
-        r.ops.FORK_MIN_ROWS = fork_rows
-        sa, sb, sc = r.admit(), r.admit(), r.admit()
-        r.step([StepEntry(sa, pa[:69], ()), StepEntry(sb, pb[:300], ())])
-        lg = r.step([StepEntry(sa, pa[69:], (0,)), StepEntry(sc, pc, (0, 300, 639)), StepEntry(sb, pb[300:], (0,))]).float().cpu()
-        r.ops.check_async_errors()
-        outs.append(lg.clone())
-        assert (r.ops._side is not None) == (fork_rows == 512)
+    r = gpu_runner(d, name, dtype, num_blocks=4 * (1100 // TINY[name][1]), max_rows=1024, graphs=False)
+    sa, sb, sc = r.admit(), r.admit(), r.admit()
+    r.step([StepEntry(sa, pa[:69], ()), StepEntry(sb, pb[:300], ())])
+    lg = r.step([StepEntry(sa, pa[69:], (0,)), StepEntry(sc, pc, (0, 300, 639)), StepEntry(sb, pb[300:], (0,))]).float().cpu()
+    r.ops.check_async_errors()
     want = torch.stack([refs[0][69], refs[2][0], refs[2][300], refs[2][639], refs[1][300]])
-    assert float((outs[0] - want).abs().max()) <= rel * float(want.abs().max())
-    assert torch.equal(outs[0], outs[1])
+    assert float((lg - want).abs().max()) <= rel * float(want.abs().max())

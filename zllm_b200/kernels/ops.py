@@ -51,7 +51,6 @@ class CudaOps:
         self._bound_stream = None
         self._tc_scratch = None
         self._kv_maps = {}
-        self._side = None
         self.launches = 0
 
     # ------------------------------------------------------------------
@@ -169,7 +168,6 @@ class CudaOps:
     SAMPLE_SCRATCH_ROWS = 1024
     TC_SCRATCH_BYTES = 64 * 1024 * 1024
     DECODE_MAX_ROWS = 16
-    FORK_MIN_ROWS = 512                 # smaller steps are bound by the host: no extra calls there
 
     def _gemm_decode(self, x, norm_w, eps, w, out, mode, M, N, K, rope=None):
         """The fused decode product (csrc/gemm_decode.cu).  rope: (ctx, rot, cache, nq, nkv, hd, store)."""
@@ -387,19 +385,6 @@ class CudaOps:
             return False
         lib = self.lib("attention_bf16")
         tb = cache.block_table
-        # A large mixed step: the decoded rows' kernels run on a second stream beside the portions'
-        # kernel (they share nothing but their inputs) and join before the next product
-        fork = ctx.n_decode > 0 and ctx.n_tiles > 0 and qkv.shape[0] >= self.FORK_MIN_ROWS \
-            and not torch.cuda.is_current_stream_capturing()
-        if fork:
-            if self._side is None:
-                self._side = (torch.cuda.Stream(self.device), torch.cuda.Event(), torch.cuda.Event())
-            side, forked, joined = self._side
-            main = torch.cuda.current_stream(self.device)
-            forked.record(main)
-            side.wait_event(forked)
-            bound = self._bound_stream
-            self._bound_stream = c_void_p(side.cuda_stream)
         if ctx.n_decode > 0:
             max_splits = max(1, -(-tb.shape[1] * cache.block_size // self.decode_split_keys))
             n_splits = min(max_splits, ctx.fixed_splits or self.decode_splits(ctx.max_context))
@@ -426,9 +411,6 @@ class CudaOps:
                     c_int(n_splits), c_int(max_splits), self._stream())
                 self._check(code, "attention_decode_bf16")
             self.launches += 1                  # split kernel + combine kernel
-        if fork:
-            joined.record(side)
-            self._bound_stream = bound
         bs = cache.block_size
         if ctx.n_tiles > 0 and not window and hd in (64, 128) and (16 if hd == 128 else 8) <= bs <= 128 \
                 and bs & (bs - 1) == 0:
@@ -444,8 +426,6 @@ class CudaOps:
                 _ptr(tb), c_int(tb.shape[1]), c_int(cache.block_size), c_int(nq), c_int(nkv), c_int(hd),
                 c_float(scale), c_int(window or 0), self._stream())
             self._check(code, "attention_prefill_bf16")
-        if fork:
-            main.wait_event(joined)
         return True
 
     # ---- sampling --------------------------------------------------------
