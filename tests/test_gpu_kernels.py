@@ -326,6 +326,49 @@ def test_prefill_attention_when_the_maximum_keeps_moving(ops, slope, hd, nq, nkv
     assert err <= 0.03, err
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_prefill_attention_of_a_partial_tile_does_not_depend_on_what_ran_before(ops, hd):
+    """A portion of 69 rows fills half a tile: the tile's other rows are another request's queries
+    (large ones here), and the key boxes beyond position 68 are never loaded.  Whatever an earlier
+    kernel left in shared memory there must not reach the real rows (not even their rounding, by
+    way of a decision the rows of a warp take together): the same step gives the same bits before
+    and after attention over large and very different data."""
+    dtype = torch.bfloat16
+    nq, nkv, bs = 8, 2, 16
+    scale = 1.0 / math.sqrt(hd)
+    g = torch.Generator().manual_seed(21)
+    cm = make_cache(nkv, hd, bs, 200, 3, 1400, dtype)
+    view = cm.view(0)
+    view.k_pages.copy_(torch.randn(view.k_pages.shape, generator=g).to(dtype))
+    view.v_pages.copy_(torch.randn(view.v_pages.shape, generator=g).to(dtype))
+    s, s_b = cm.admit(), cm.admit()
+    ctx = make_ctx(cm, [(s, 69), (s_b, 100)])
+    qkv = torch.randn(169, (nq + 2 * nkv) * hd, generator=g) * 0.5
+    qkv[69:] *= 8.0
+    qkv = qkv.to(dtype).to(DEV)
+    outs = []
+    for big in (30.0, -50.0, None):
+        out = torch.zeros(169, nq * hd, dtype=dtype, device=DEV)
+        ops.paged_attention(qkv, out, ctx, view, nq, nkv, hd, scale, None)
+        outs.append(out.cpu().clone())
+        if big is None:
+            break
+        # dirty every SM's shared memory: 1,024 rows of scores of the size ``big``
+        cm2 = make_cache(nkv, hd, bs, 80, 2, 1100, dtype)
+        s2 = cm2.admit()
+        v2 = cm2.view(0)
+        v2.k_pages.fill_(big)
+        v2.v_pages.fill_(big)
+        ctx2 = make_ctx(cm2, [(s2, 1024)])
+        q2 = torch.full((1024, (nq + 2 * nkv) * hd), abs(big), dtype=dtype, device=DEV)
+        ops.paged_attention(q2, torch.zeros(1024, nq * hd, dtype=dtype, device=DEV), ctx2, v2, nq, nkv, hd, scale, None)
+    ops.check_async_errors()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    want = torch.zeros(169, nq * hd)
+    REF.paged_attention(qkv.cpu().float(), want, cpu_ctx(ctx), CpuCacheView(view), nq, nkv, hd, scale, None)
+    assert float((outs[0].float() - want).abs().max()) <= 0.03
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_window_edge(ops, dtype):
     """The key just outside the window is made dominant: it must NOT be seen; the one just

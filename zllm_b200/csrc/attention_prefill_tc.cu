@@ -367,11 +367,15 @@ __global__ void __launch_bounds__(PT_THREADS, CTAS) prefill_tc_kernel(
             xmax[(b * 2 + half) * PT_ROWS + r] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
             const float m_blk = fmaxf(mx, xmax[(b * 2 + (half ^ 1)) * PT_ROWS + r]) * scale;
-            if (__any_sync(0xffffffffu, m_blk > m_ref + PT_LAZY)) {
-                // (the same decision in both warps of the quadrant) move the reference to the true
-                // maximum and rescale l and this thread's half of O
-                const float m_new = fmaxf(m_ref, m_blk);
-                const float corr = (m_ref == -INFINITY) ? 0.f : ex2_approx(m_ref - m_new);
+            // A row decides for itself (both its threads alike); the rows of the warp that do not
+            // move keep their reference and a factor of exactly 1, so a row's result does not depend
+            // on its neighbours in the tile.  Rows beyond the tile's own (their scores come from
+            // other requests' queries and from key boxes that were never loaded) never move.
+            const bool need = r < n_rows && m_blk > m_ref + PT_LAZY;
+            if (__any_sync(0xffffffffu, need)) {
+                // move the reference to the true maximum and rescale l and this thread's half of O
+                const float m_new = need ? fmaxf(m_ref, m_blk) : m_ref;
+                const float corr = !need ? 1.f : ((m_ref == -INFINITY) ? 0.f : ex2_approx(m_ref - m_new));
                 m_ref = m_new;
                 l_run *= corr;
                 if (kb > 0) {
