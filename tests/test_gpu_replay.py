@@ -245,3 +245,36 @@ def test_large_mixed_step_with_decoded_rows(tmp_path, name):
     want = torch.stack([refs[0][69], refs[2][0], refs[2][300], refs[2][639], refs[1][300]])
     assert float((outs[0] - want).abs().max()) <= rel * float(want.abs().max())
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_bfloat16_steps_give_the_same_bits_whatever_ran_before(tmp_path, name):
+    """The same schedule of steps (portions that fill tiles partly, mixed steps, decoding through
+    graphs) on fresh pools, before and after another model has used the GPU: every logit bit for
+    bit the same.  Results must not depend on what earlier kernels left behind."""
+    dtype = "bfloat16"
+    d = make_model_dir(tmp_path, name, dtype)
+    V = TINY[name][0]["vocab_size"]
+    other = "D" if name == "C" else "C"
+    d_other = make_model_dir(tmp_path, other, dtype)
+    pa, pb = random_prompt(V, 200, 41), random_prompt(V, 150, 42)
+
+    def schedule():
+        r = gpu_runner(d, name, dtype, num_blocks=3 * (400 // TINY[name][1]), max_rows=512)
+        sa, sb = r.admit(), r.admit()
+        got = [r.step([StepEntry(sa, pa[:69], (0, 68))]).float().cpu().clone(),
+               r.step([StepEntry(sa, pa[69:70], (0,)), StepEntry(sb, pb[:131], (5, 130))]).float().cpu().clone(),
+               r.step([StepEntry(sb, pb[131:133], (0, 1)), StepEntry(sa, pa[70:199], (0, 128))]).float().cpu().clone()]
+        for i in range(12):
+            r.decode_step([sa, sb], [pa[199] if i == 0 else 7 + i, pb[133 + i]], [0.0, 0.0], [0, 0])
+            got.append(r.last_logits[:2].float().cpu().clone())
+        r.ops.check_async_errors()
+        return got
+
+    first = schedule()
+    ro = gpu_runner(d_other, other, dtype, num_blocks=2 * (700 // TINY[other][1]), max_rows=1024, graphs=False)
+    so = ro.admit()
+    ro.step([StepEntry(so, random_prompt(TINY[other][0]["vocab_size"], 600, 43), (599,))])
+    second = schedule()
+    for i, (x, y) in enumerate(zip(first, second)):
+        assert torch.equal(x, y), f"step {i}"
