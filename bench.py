@@ -24,7 +24,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# Llama-3.2-1B shape (BASELINE.json configs[2])
+# Llama-3.2-1B shape: the configuration the headline numbers are quoted on
 MODEL = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=16, hidden_size=2048, num_attention_heads=32,
              num_key_value_heads=8, head_dim=64, intermediate_size=8192, vocab_size=128256, rms_norm_eps=1e-5,
              rope_theta=500000.0,
