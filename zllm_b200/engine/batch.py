@@ -182,10 +182,15 @@ class Workspace:
         self.device = torch.device(device)
         self._bufs = {}
         self._retired = []
+        self._views = {}                # (name, shape, dtype) -> the view handed out last time
 
     def get(self, name: str, shape, dtype, cap=None) -> torch.Tensor:
         """A [rows, ...] view of the buffer ``name``.  The buffer is made for ``cap`` rows
         (default: the step's row limit) the first time and only ever grows."""
+        vkey = (name, shape, dtype) if type(shape) is tuple else (name, tuple(shape), dtype)
+        view = self._views.get(vkey)
+        if view is not None:            # a step asks for the same few views layer after layer
+            return view
         rows = shape[0]
         rest = tuple(shape[1:])
         key = (name, rest, dtype)
@@ -194,9 +199,13 @@ class Workspace:
             cap = max(rows, self.max_rows if cap is None else cap)
             if buf is not None:
                 self._retired.append(buf)
+                self._views = {k: v for k, v in self._views.items() if (k[0], tuple(k[1][1:]), k[2]) != key}
             buf = torch.empty((cap, *rest), dtype=dtype, device=self.device)
             self._bufs[key] = buf
-        return buf[:rows]
+        if len(self._views) > 4096:     # many distinct row counts over a long run: start over
+            self._views.clear()
+        view = self._views[vkey] = buf[:rows]
+        return view
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in list(self._bufs.values()) + self._retired)
