@@ -133,6 +133,15 @@ def test_random_orders_never_lose_or_double_a_page(seed):
                     cm.advance(s, new_len)
                 else:
                     assert cm.free_pages() == before          # a refused growth takes nothing
+        elif op < 0.92 and live:
+            s = rng.choice(list(live))
+            n = rng.randint(0, live[s])
+            before = cm.free_pages()
+            try:
+                cm.truncate(s, n)
+                live[s] = n
+            except MemoryError_:
+                assert cm.free_pages() == before              # a refused truncation changes nothing
         elif live:
             s = rng.choice(list(live))
             cm.free_slot(s)
@@ -144,3 +153,56 @@ def test_random_orders_never_lose_or_double_a_page(seed):
         cm.free_slot(s)
     cm.check_integrity()
     assert cm.free_pages() == [24, 24] and len(cm.free_slots) == 5
+
+
+def test_truncate_gives_back_the_pages_beyond_and_growth_continues_there():
+    cm = make(n_pages=12, bs=4, max_len=48, needs=[(KVCacheSpec(1, 16), None)])
+    s = cm.admit()
+    assert cm.ensure(s, 21)
+    cm.advance(s, 21)
+    assert cm.free_pages() == [12 - 6]
+    cm.truncate(s, 9)                                # positions 0..8 stay: 3 pages
+    cm.check_integrity()
+    assert cm.length[s] == 9 and cm.free_pages() == [12 - 3]
+    assert all(cm.groups[0].table[s, b] != NO_PAGE for b in range(3)) and cm.groups[0].table[s, 3] == NO_PAGE
+    assert cm.ensure(s, 14)
+    cm.advance(s, 14)
+    cm.check_integrity()
+    assert cm.free_pages() == [12 - 4]
+    cm.truncate(s, 14)                               # nothing to do
+    with pytest.raises(MemoryError_):
+        cm.truncate(s, 15)
+    cm.truncate(s, 0)
+    cm.check_integrity()
+    assert cm.free_pages() == [12] and cm.length[s] == 0
+    cm.free_slot(s)
+    with pytest.raises(MemoryError_):
+        cm.truncate(s, 0)
+
+
+def test_truncate_with_a_window_and_with_state():
+    cm = make(n_pages=8, bs=4, max_len=64, needs=[(KVCacheSpec(1, 16, window=6), None), (KVCacheSpec(1, 16), None)])
+    s = cm.admit()
+    assert cm.ensure(s, 30)
+    cm.advance(s, 30)                                # the window group holds the pages of keys 25..29 only
+    cm.check_integrity()
+    cm.truncate(s, 29)                               # the query at 29 sees keys 24..28: page 6 is still there
+    cm.check_integrity()
+    with pytest.raises(MemoryError_, match="given back"):
+        cm.truncate(s, 20)                           # keys 15..19 went back to the pool long ago
+    assert cm.length[s] == 29
+    cm.truncate(s, 0)                                # a reset is always possible
+    cm.check_integrity()
+    assert cm.free_pages() == [8, 8]
+    assert cm.ensure(s, 5)
+    cm.advance(s, 5)
+    cm.check_integrity()
+    st = make(needs=[(StateSpec((3,)), None), (KVCacheSpec(1, 16), None)], allocate=True)
+    s2 = st.admit()
+    assert st.ensure(s2, 6)
+    st.advance(s2, 6)
+    st.view(0).state[s2] += 1.0
+    with pytest.raises(MemoryError_, match="state"):
+        st.truncate(s2, 3)
+    st.truncate(s2, 0)
+    assert float(st.view(0).state[s2].abs().sum()) == 0.0

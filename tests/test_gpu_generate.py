@@ -177,6 +177,10 @@ def test_session_single_stream_calls(tmp_path):
     assert float((lg.cpu() - ref[19]).abs().max()) < 1e-4 and ses.position == 20
     t = ses.generate_token(toks[20:21])
     assert t == int(ref[20].argmax()) and ses.position == 21
+    ses.truncate_to(12)                          # back to position 12, then the same tokens again
+    assert ses.position == 12
+    lg = ses.forward_logits(toks[12:21])
+    assert float((lg.cpu() - ref[20]).abs().max()) < 1e-4 and ses.position == 21
     ses.reset_position()
     assert ses.position == 0
     allp = ses.forward_all_logits(toks)

@@ -278,6 +278,39 @@ class CacheManager:
                     g.dirty.add(slot)
             g.first_live[slot] = max(g.first_live[slot], keep_from)
 
+    def truncate(self, slot: int, new_len: int) -> None:
+        """Forget the positions from ``new_len`` on (the reference's ``truncate_to``,
+        zllm src/backend/candle/backend.rs:95-114): pages wholly beyond them go back to their
+        pools.  Refused when a windowed group has already given back pages that the next query at
+        ``new_len`` would need, or when a mixer keeps per-request state (it cannot be rewound)."""
+        if not self.live[slot]:
+            raise MemoryError_(f"slot {slot} is not live")
+        if not 0 <= new_len <= self.length[slot]:
+            raise MemoryError_(f"slot {slot}: cannot truncate {self.length[slot]} positions to {new_len}")
+        if new_len == self.length[slot]:
+            return
+        if new_len > 0:
+            if self.state:
+                raise MemoryError_("a model with per-request state cannot be truncated (only reset to 0)")
+            for g in self.groups:
+                if g._first_needed_block(new_len) < g.first_live[slot]:
+                    raise MemoryError_(f"slot {slot}: the window's pages before position {new_len} were given back")
+        for g in self.groups:
+            keep = -(-new_len // g.block_size)           # >= first_live when new_len > 0 (checked above)
+            for b in range(max(keep, g.first_live[slot]), g.n_blocks[slot]):
+                p = int(g.table[slot, b])
+                if p != NO_PAGE:
+                    g.pool.release(p, slot)
+                    g.table[slot, b] = NO_PAGE
+                    g.dirty.add(slot)
+            g.n_blocks[slot] = min(g.n_blocks[slot], keep)
+            if new_len == 0:
+                g.first_live[slot] = 0
+        if new_len == 0:
+            for t in self.state.values():
+                t[slot].zero_()
+        self.length[slot] = new_len
+
     def sync_tables(self) -> None:
         """Copy the table rows that changed since the last call to the device."""
         for g in self.groups:

@@ -223,6 +223,10 @@ class Session:
         self.runner.release(self.slot)
         self.slot = self.runner.admit()
 
+    def truncate_to(self, n: int) -> None:
+        """Keep the first ``n`` cached positions (backend.rs:95-114): the next call continues at n."""
+        self.runner.truncate(self.slot, n)
+
     def close(self) -> None:
         if self.slot is not None:
             self.runner.release(self.slot)

@@ -119,6 +119,10 @@ class ModelRunner:
     def cached_len(self, slot: int) -> int:
         return self.cache.length[slot]
 
+    def truncate(self, slot: int, new_len: int) -> None:
+        """Forget the slot's positions from ``new_len`` on; the next step continues there."""
+        self.cache.truncate(slot, new_len)
+
     # ---- the step ----------------------------------------------------------
     def _prepare(self, entries: Sequence[StepEntry]):
         if not entries:
