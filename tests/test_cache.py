@@ -206,3 +206,139 @@ def test_truncate_with_a_window_and_with_state():
         st.truncate(s2, 3)
     st.truncate(s2, 0)
     assert float(st.view(0).state[s2].abs().sum()) == 0.0
+
+
+def shared(n_pages=12, bs=4, slots=4, max_len=64):
+    return CacheManager([(KVCacheSpec(1, 16), None), (KVCacheSpec(2, 16), None)], bs, n_pages, slots, max_len,
+                        torch.float32, "cpu", allocate=False, prefix_sharing=True)
+
+
+def fill(cm, slot, tokens, upto=None):
+    upto = len(tokens) if upto is None else upto
+    assert cm.ensure(slot, upto)
+    cm.advance(slot, upto)
+    cm.register_prefix(slot, tokens, upto)
+
+
+def test_a_second_request_takes_over_the_full_pages_of_a_prefix():
+    cm = shared()
+    a = list(range(100, 119))                        # 19 tokens: 4 full pages of 4 and 3 more
+    s0 = cm.admit()
+    assert cm.adopt_prefix(s0, a) == 0               # nothing registered yet
+    fill(cm, s0, a)
+    cm.check_integrity()
+    s1 = cm.admit()
+    b = a[:13] + [7, 8, 9]                           # the same first 3 pages, then other tokens
+    assert cm.adopt_prefix(s1, b) == 12 and cm.length[s1] == 12
+    for g in cm.groups:
+        assert list(g.table[s1, :3]) == list(g.table[s0, :3]) and g.table[s1, 3] == NO_PAGE
+    cm.check_integrity()
+    assert cm.free_pages() == [12 - 5, 12 - 5]       # s1 holds no page of its own yet
+    fill(cm, s1, b)
+    cm.check_integrity()
+    assert cm.free_pages() == [12 - 6, 12 - 6]
+    # the block with the LAST token is never taken over: one position is left to compute
+    s2 = cm.admit()
+    assert cm.adopt_prefix(s2, a[:16]) == 12
+    assert cm.adopt_prefix(s2, a[:16]) == 0          # only into an empty slot
+    cm.free_slot(s2)
+    cm.free_slot(s0)                                 # shared pages stay with s1; a's 4th page stays findable
+    cm.check_integrity()
+    assert cm.free_pages() == [12 - 4, 12 - 4]       # s1: 3 shared + 1 own full... and its partial page
+    cm.free_slot(s1)
+    cm.check_integrity()
+    assert cm.free_pages() == [12, 12]               # everything is free or reclaimable
+    s3 = cm.admit()
+    assert cm.adopt_prefix(s3, a) == 16              # and still findable after everybody left
+    assert cm.prefix_hits == 12 + 12 + 16
+    cm.check_integrity()
+
+
+def test_registered_pages_are_reclaimed_oldest_first_when_the_stack_is_empty():
+    cm = shared(n_pages=6, bs=4)
+    a, b = list(range(10, 19)), list(range(50, 59))  # 2 full pages + 1 token each
+    for toks in (a, b):
+        s = cm.admit()
+        fill(cm, s, toks)
+        cm.free_slot(s)
+    cm.check_integrity()
+    assert cm.free_pages() == [6, 6] and len(cm.groups[0].pool.free) == 2   # 4 registered pages wait to be found
+    s = cm.admit()
+    assert cm.ensure(s, 13)                          # 4 pages: the 2 free ones and a's two (the oldest)
+    cm.advance(s, 13)
+    cm.check_integrity()
+    t = cm.admit()
+    assert cm.adopt_prefix(t, a) == 0                # a's pages are gone
+    assert cm.adopt_prefix(t, b) == 8                # b's are still there
+    cm.check_integrity()
+    assert not cm.ensure(t, 20)                      # 3 more pages, none left
+    cm.free_slot(s)
+    assert cm.ensure(t, 20)
+    cm.check_integrity()
+
+
+def test_truncate_into_a_shared_page_is_refused_and_a_sole_holder_unregisters():
+    cm = shared()
+    a = list(range(30, 47))
+    s0 = cm.admit()
+    fill(cm, s0, a)
+    s1 = cm.admit()
+    assert cm.adopt_prefix(s1, a) == 16
+    with pytest.raises(MemoryError_, match="shared"):
+        cm.truncate(s1, 6)
+    cm.truncate(s1, 8)                               # at a page's edge: fine
+    cm.check_integrity()
+    cm.free_slot(s0)
+    cm.truncate(s1, 6)                               # now the only holder: the page stops being findable
+    cm.check_integrity()
+    s2 = cm.admit()
+    assert cm.adopt_prefix(s2, a) == 4
+    cm.check_integrity()
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_random_orders_with_shared_prefixes(seed):
+    rng = random.Random(100 + seed)
+    cm = shared(n_pages=20, bs=4, slots=5, max_len=40)
+    stems = [[rng.randrange(50) for _ in range(40)] for _ in range(3)]
+    live = {}
+    for _ in range(500):
+        op = rng.random()
+        if op < 0.3 and cm.has_free_slot():
+            s = cm.admit()
+            stem = rng.choice(stems)
+            cut = rng.randrange(1, 40)
+            toks = stem[:cut] + [rng.randrange(50) for _ in range(rng.randrange(1, 40 - cut + 1))]
+            n = cm.adopt_prefix(s, toks)
+            assert n % 4 == 0 and n < len(toks) and cm.length[s] == n
+            live[s] = toks
+        elif op < 0.85 and live:
+            s = rng.choice(list(live))
+            new_len = min(len(live[s]), cm.length[s] + rng.choice([1, 1, 2, 5, 13]))
+            if new_len > cm.length[s] and cm.ensure(s, new_len):
+                cm.advance(s, new_len)
+                cm.register_prefix(s, live[s], new_len)
+        elif op < 0.9 and live:
+            s = rng.choice(list(live))
+            try:
+                cm.truncate(s, rng.randint(0, cm.length[s]))
+            except MemoryError_:
+                pass
+        elif live:
+            s = rng.choice(list(live))
+            cm.free_slot(s)
+            del live[s]
+        cm.check_integrity()
+        # a shared page holds the same tokens for all its holders
+        for g in cm.groups:
+            for p in range(g.pool.num_pages):
+                hs = sorted(g.pool.holders[p])
+                if len(hs) > 1:
+                    blocks = [list(g.table[s]).index(p) for s in hs]
+                    assert len(set(blocks)) == 1
+                    b = blocks[0]
+                    assert len({tuple(live[s][:4 * b + 4]) for s in hs}) == 1
+    for s in list(live):
+        cm.free_slot(s)
+    cm.check_integrity()
+    assert cm.free_pages() == [20, 20]

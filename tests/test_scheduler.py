@@ -211,3 +211,34 @@ def test_random_workloads_keep_every_page_accounted(seed=3):
         r = sch.requests[rid]
         assert outs[rid] == [token_for(r, n + k) for k in range(min(mt, 40 - n))]
     assert cm.free_pages() == [20] and len(cm.free_slots) == 4
+
+
+def test_a_request_with_a_known_prefix_starts_behind_it():
+    cm = CacheManager([(KVCacheSpec(1, 16), None)], 4, 32, 4, 64, torch.float32, "cpu", allocate=False,
+                      prefix_sharing=True)
+    sch = Scheduler(cm, 16, 64)
+    stem = list(range(200, 222))                             # 22 tokens: 5 full pages of 4
+    a = sch.add(stem, SamplingParams.greedy(max_tokens=3))
+    drain(cm, sch)
+    assert sch.requests[a].state == FINISHED and cm.prefix_hits == 0
+    assert cm.free_pages() == [32]                           # everything is free or waits to be found
+    log = []
+    b = sch.add(stem[:18] + [5, 6, 7], SamplingParams.greedy(max_tokens=2))
+    run_step(cm, sch, log)
+    plan, _ = log[0]
+    assert [(p.request.id, p.start, p.n, p.completes) for p in plan.portions] == [(b, 16, 5, True)]
+    assert cm.prefix_hits == 16 and sch.stats()["prefix_hits"] == 16
+    drain(cm, sch)
+    # a preempted request finds its own pages again when it is resumed
+    c = sch.add(list(range(300, 330)), SamplingParams.greedy(max_tokens=4))
+    run_step(cm, sch)
+    run_step(cm, sch)
+    rc = sch.requests[c]
+    assert rc.num_computed == 30
+    sch._preempt(sch.running.pop())
+    log = []
+    run_step(cm, sch, log)
+    plan, _ = log[0]
+    assert plan.portions[0].start == 28 and plan.portions[0].request.id == c      # 7 full pages taken over
+    drain(cm, sch)
+    assert cm.free_pages() == [32]

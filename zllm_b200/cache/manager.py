@@ -25,6 +25,7 @@ head in one page are one contiguous run.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -38,29 +39,72 @@ NO_PAGE = -1
 
 
 class PagePool:
-    """Free stack of page ids with an owner per page (integrity checks are cheap)."""
+    """Free stack of page ids; every page knows who holds it (integrity checks are cheap).
+
+    A page is held by one request, or -- when it is registered under the hash of the token
+    prefix it completes (``register``) -- by any number of requests that share that prefix.  A
+    registered page whose last holder let go keeps its contents and stays findable until the
+    free stack is empty and it is the least recently released one (mod.rs:1912-1929).
+    """
 
     def __init__(self, num_pages: int):
         self.num_pages = int(num_pages)
         self.free: List[int] = list(range(self.num_pages - 1, -1, -1))  # pop() yields page 0 first
-        self.owner: List[Optional[int]] = [None] * self.num_pages
+        self.holders: List[set] = [set() for _ in range(self.num_pages)]
+        self.hash_of: List[Optional[int]] = [None] * self.num_pages     # prefix hash of a registered page
+        self.by_hash: Dict[int, int] = {}
+        self.reclaimable: "OrderedDict[int, None]" = OrderedDict()      # registered, no holder; oldest first
 
     def alloc(self, owner: int) -> Optional[int]:
-        if not self.free:
+        if self.free:
+            p = self.free.pop()
+        elif self.reclaimable:
+            p, _ = self.reclaimable.popitem(last=False)
+            del self.by_hash[self.hash_of[p]]
+            self.hash_of[p] = None
+        else:
             return None
-        p = self.free.pop()
-        assert self.owner[p] is None, f"page {p} handed out while owned by slot {self.owner[p]}"
-        self.owner[p] = owner
+        assert not self.holders[p], f"page {p} handed out while held by slots {sorted(self.holders[p])}"
+        self.holders[p].add(owner)
         return p
 
     def release(self, page: int, owner: int) -> None:
-        if self.owner[page] != owner:
-            raise MemoryError_(f"page {page} freed by slot {owner} but owned by {self.owner[page]}")
-        self.owner[page] = None
-        self.free.append(page)
+        if owner not in self.holders[page]:
+            raise MemoryError_(f"page {page} freed by slot {owner} but held by {sorted(self.holders[page])}")
+        self.holders[page].discard(owner)
+        if self.holders[page]:
+            return
+        if self.hash_of[page] is not None:
+            self.reclaimable[page] = None
+        else:
+            self.free.append(page)
 
     def n_free(self) -> int:
-        return len(self.free)
+        return len(self.free) + len(self.reclaimable)
+
+    # ---- pages shared by their prefix ------------------------------------
+    def register(self, page: int, h: int) -> None:
+        """Make a full page findable under the hash of the tokens up to its end."""
+        if self.hash_of[page] is None and h not in self.by_hash:
+            self.hash_of[page] = h
+            self.by_hash[h] = page
+
+    def unregister(self, page: int) -> None:
+        if self.hash_of[page] is not None:
+            del self.by_hash[self.hash_of[page]]
+            self.hash_of[page] = None
+            if page in self.reclaimable:
+                del self.reclaimable[page]
+                self.free.append(page)
+
+    def lookup(self, h: int) -> Optional[int]:
+        return self.by_hash.get(h)
+
+    def share(self, page: int, owner: int) -> None:
+        """One more holder for a registered page."""
+        assert self.hash_of[page] is not None
+        self.reclaimable.pop(page, None)
+        self.holders[page].add(owner)
 
 
 @dataclass
@@ -119,7 +163,8 @@ class CacheManager:
     """Slots, groups, pools, tables and state arrays for one model."""
 
     def __init__(self, cache_needs: Sequence[Tuple[object, Optional[int]]], block_size: int, num_pages: int,
-                 max_slots: int, max_len: int, dtype: torch.dtype, device, allocate: bool = True):
+                 max_slots: int, max_len: int, dtype: torch.dtype, device, allocate: bool = True,
+                 prefix_sharing: bool = False):
         if num_pages * block_size < 1:
             raise ConfigError("cache pool must hold at least one page")
         self.block_size = int(block_size)
@@ -152,6 +197,13 @@ class CacheManager:
         self.live: List[bool] = [False] * max_slots
         self.length: List[int] = [0] * max_slots                             # positions cached per slot
         self.views: Dict[int, object] = {}
+        # pages are shared by their token prefix only when every layer keeps all positions and no
+        # mixer has state of its own: a prefix is then fully described by its pages
+        self.prefix_sharing = bool(prefix_sharing) and not self._state_entries and \
+            all(g.window is None for g in self.groups) and bool(self.groups)
+        self._hashed: Dict[int, Tuple[int, int]] = {}   # slot -> (blocks hashed so far, hash of the last)
+        self.prefix_hits = 0                 # positions taken over from registered pages
+        self.prefix_misses = 0               # positions of prompts that had to be computed
         if allocate:
             self._allocate()
 
@@ -211,6 +263,7 @@ class CacheManager:
             g.dirty.add(slot)
         self.live[slot] = False
         self.length[slot] = 0
+        self._hashed.pop(slot, None)
         self.free_slots.append(slot)
 
     # ---- queries for the scheduler -------------------------------------
@@ -295,6 +348,18 @@ class CacheManager:
             for g in self.groups:
                 if g._first_needed_block(new_len) < g.first_live[slot]:
                     raise MemoryError_(f"slot {slot}: the window's pages before position {new_len} were given back")
+        if new_len % self.block_size:
+            # the page that is kept partly will be written again: nobody else may rely on it
+            b = new_len // self.block_size
+            for g in self.groups:
+                p = int(g.table[slot, b])
+                if p != NO_PAGE and len(g.pool.holders[p]) > 1:
+                    raise MemoryError_(f"slot {slot}: position {new_len} lies in a page shared with other requests")
+            for g in self.groups:
+                p = int(g.table[slot, b])
+                if p != NO_PAGE:
+                    g.pool.unregister(p)
+        self._hashed.pop(slot, None)
         for g in self.groups:
             keep = -(-new_len // g.block_size)           # >= first_live when new_len > 0 (checked above)
             for b in range(max(keep, g.first_live[slot]), g.n_blocks[slot]):
@@ -311,6 +376,56 @@ class CacheManager:
                 t[slot].zero_()
         self.length[slot] = new_len
 
+    # ---- pages shared by their token prefix (mod.rs:1941-1947,2276-2317) --------------
+    def _next_hash(self, h: int, tokens: Sequence[int], b: int) -> int:
+        bs = self.block_size
+        return hash((h,) + tuple(tokens[b * bs:(b + 1) * bs]))
+
+    def adopt_prefix(self, slot: int, tokens: Sequence[int]) -> int:
+        """For a slot that holds nothing yet: take over the longest run of registered pages whose
+        chained hashes match the full blocks of ``tokens`` -- never the block with the last token,
+        so that at least one position is left to compute.  Returns the positions taken over
+        (the slot's cached length afterwards)."""
+        if not self.prefix_sharing or not self.live[slot] or self.length[slot] != 0 or \
+                any(g.n_blocks[slot] for g in self.groups):
+            return 0
+        max_reuse = (len(tokens) - 1) // self.block_size
+        h, run = 0, []
+        for b in range(max_reuse):
+            h = self._next_hash(h, tokens, b)
+            pages = [g.pool.lookup(h) for g in self.groups]
+            if any(p is None for p in pages):
+                break
+            run.append((h, pages))
+        for b, (_, pages) in enumerate(run):
+            for g, p in zip(self.groups, pages):
+                g.pool.share(p, slot)
+                g.table[slot, b] = p
+        n = len(run)
+        if n:
+            for g in self.groups:
+                g.n_blocks[slot] = n
+                g.dirty.add(slot)
+            self._hashed[slot] = (n, run[-1][0])
+        self.length[slot] = n * self.block_size
+        self.prefix_hits += n * self.block_size
+        self.prefix_misses += len(tokens) - n * self.block_size
+        return n * self.block_size
+
+    def register_prefix(self, slot: int, tokens: Sequence[int], upto: int) -> None:
+        """The slot's full pages below position ``upto`` (all written) become findable by the hash
+        of the tokens up to their end."""
+        if not self.prefix_sharing:
+            return
+        nb = min(upto, len(tokens), self.length[slot]) // self.block_size
+        done, h = self._hashed.get(slot, (0, 0))
+        for b in range(done, nb):
+            h = self._next_hash(h, tokens, b)
+            for g in self.groups:
+                g.pool.register(int(g.table[slot, b]), h)
+        if nb > done:
+            self._hashed[slot] = (nb, h)
+
     def sync_tables(self) -> None:
         """Copy the table rows that changed since the last call to the device."""
         for g in self.groups:
@@ -323,25 +438,36 @@ class CacheManager:
 
     # ---- integrity ------------------------------------------------------
     def check_integrity(self) -> None:
-        """No page lost, held twice or free while owned; raises AssertionError otherwise."""
+        """No page lost, held by a slot that does not list it, free or reclaimable while held,
+        shared without being registered; raises AssertionError otherwise."""
         for g in self.groups:
-            held: Dict[int, int] = {}
+            held: Dict[int, set] = {}
             for slot in range(self.max_slots):
                 row = g.table[slot]
                 pages = [int(p) for p in row if p != NO_PAGE]
                 if not self.live[slot]:
                     assert not pages, f"group {g.index}: dead slot {slot} holds pages {pages}"
+                assert len(set(pages)) == len(pages), f"group {g.index}: slot {slot} lists a page twice"
                 for b, p in enumerate(row):
                     if p == NO_PAGE:
                         continue
                     assert g.first_live[slot] <= b < g.n_blocks[slot], f"page outside live range in slot {slot}"
-                    assert p not in held, f"group {g.index}: page {p} held by slots {held[p]} and {slot}"
-                    held[int(p)] = slot
-                    assert g.pool.owner[int(p)] == slot
-            free = g.pool.free
+                    held.setdefault(int(p), set()).add(slot)
+            pool = g.pool
+            for p in range(pool.num_pages):
+                assert pool.holders[p] == held.get(p, set()), (
+                    f"group {g.index}: page {p} held by {sorted(pool.holders[p])} but listed by {sorted(held.get(p, set()))}")
+                if len(pool.holders[p]) > 1:
+                    assert pool.hash_of[p] is not None, f"group {g.index}: page {p} is shared but not registered"
+                if pool.hash_of[p] is not None:
+                    assert pool.by_hash.get(pool.hash_of[p]) == p
+            free, rec = pool.free, list(pool.reclaimable)
             assert len(set(free)) == len(free), f"group {g.index}: a page is on the free stack twice"
-            assert not (set(free) & set(held)), f"group {g.index}: a held page is on the free stack"
-            assert len(free) + len(held) == g.pool.num_pages, (
-                f"group {g.index}: {g.pool.num_pages - len(free) - len(held)} pages lost")
+            assert not (set(free) & set(held)) and not (set(rec) & set(held)), f"group {g.index}: a held page is free"
+            assert not (set(free) & set(rec))
+            assert all(pool.hash_of[p] is not None for p in rec) and all(pool.hash_of[p] is None for p in free)
+            assert len(pool.by_hash) == sum(h is not None for h in pool.hash_of)
+            assert len(free) + len(rec) + len(held) == pool.num_pages, (
+                f"group {g.index}: {pool.num_pages - len(free) - len(rec) - len(held)} pages lost")
         assert len(set(self.free_slots)) == len(self.free_slots)
         assert sum(self.live) + len(self.free_slots) == self.max_slots

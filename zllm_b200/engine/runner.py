@@ -85,7 +85,8 @@ class ModelRunner:
         if num_blocks is None:
             num_blocks = self.ecfg.max_num_seqs * (-(-self.max_len // bs))
             num_blocks = min(num_blocks, self._blocks_that_fit(needs, bs))
-        self.cache = CacheManager(needs, bs, num_blocks, self.ecfg.max_num_seqs, self.max_len, self.dtype, self.device)
+        self.cache = CacheManager(needs, bs, num_blocks, self.ecfg.max_num_seqs, self.max_len, self.dtype, self.device,
+                                  prefix_sharing=self.ecfg.prefix_sharing)
         self.max_rows = self.ecfg.max_num_batched_tokens
         self.ws = Workspace(self.max_rows, self.device)
         self.buffers = StepBuffers(self.max_rows, self.max_rows, self.device)

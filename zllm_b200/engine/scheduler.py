@@ -150,7 +150,8 @@ class Scheduler:
                     return                      # keep the order: nobody overtakes the head
                 queue.popleft()
                 r.slot = self.cache.admit()
-                r.num_computed = 0
+                # full pages of a prefix that an earlier request left registered are taken over
+                r.num_computed = self.cache.adopt_prefix(r.slot, r.tokens)
                 r.state = PREFILLING
                 self.prefilling.append(r)
 
@@ -234,10 +235,12 @@ class Scheduler:
         out = []
         for r, tok in zip(plan.decodes, decode_tokens):
             r.num_computed += 1
+            self.cache.register_prefix(r.slot, r.tokens, r.num_computed)
             out.append(self._produce(r, int(tok)))
         for p, tok in zip(plan.portions, first_tokens):
             r = p.request
             r.num_computed += p.n
+            self.cache.register_prefix(r.slot, r.tokens, r.num_computed)
             if p.completes:
                 self.prefilling.remove(r)
                 r.state = RUNNING
@@ -270,4 +273,5 @@ class Scheduler:
     def stats(self) -> dict:
         return {"waiting": len(self.waiting), "prefilling": len(self.prefilling), "running": len(self.running),
                 "preempted": len(self.preempted), "preemptions": self.preemptions, "finished": self.finished,
-                "free_pages": self.cache.free_pages(), "free_slots": len(self.cache.free_slots)}
+                "free_pages": self.cache.free_pages(), "free_slots": len(self.cache.free_slots),
+                "prefix_hits": self.cache.prefix_hits, "prefix_misses": self.cache.prefix_misses}
