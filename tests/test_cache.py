@@ -342,3 +342,15 @@ def test_random_orders_with_shared_prefixes(seed):
         cm.free_slot(s)
     cm.check_integrity()
     assert cm.free_pages() == [20, 20]
+
+
+def test_a_hash_collision_is_not_a_match():
+    from zllm_b200.cache.manager import PagePool
+    pool = PagePool(4)
+    p = pool.alloc(0)
+    pool.register(p, 1234, (0, (1, 2, 3, 4)))
+    assert pool.lookup(1234, (0, (1, 2, 3, 4))) == p
+    assert pool.lookup(1234, (0, (9, 2, 3, 4))) is None      # the same hash, other tokens
+    q = pool.alloc(1)
+    pool.register(q, 1234, (0, (9, 2, 3, 4)))                # the hash is taken: q stays unregistered
+    assert pool.hash_of[q] is None and pool.lookup(1234, (0, (1, 2, 3, 4))) == p

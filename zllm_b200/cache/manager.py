@@ -52,6 +52,7 @@ class PagePool:
         self.free: List[int] = list(range(self.num_pages - 1, -1, -1))  # pop() yields page 0 first
         self.holders: List[set] = [set() for _ in range(self.num_pages)]
         self.hash_of: List[Optional[int]] = [None] * self.num_pages     # prefix hash of a registered page
+        self.key_of: List[Optional[tuple]] = [None] * self.num_pages    # (hash before the page, its tokens): told apart from a collision
         self.by_hash: Dict[int, int] = {}
         self.reclaimable: "OrderedDict[int, None]" = OrderedDict()      # registered, no holder; oldest first
 
@@ -61,7 +62,7 @@ class PagePool:
         elif self.reclaimable:
             p, _ = self.reclaimable.popitem(last=False)
             del self.by_hash[self.hash_of[p]]
-            self.hash_of[p] = None
+            self.hash_of[p] = self.key_of[p] = None
         else:
             return None
         assert not self.holders[p], f"page {p} handed out while held by slots {sorted(self.holders[p])}"
@@ -83,22 +84,25 @@ class PagePool:
         return len(self.free) + len(self.reclaimable)
 
     # ---- pages shared by their prefix ------------------------------------
-    def register(self, page: int, h: int) -> None:
-        """Make a full page findable under the hash of the tokens up to its end."""
+    def register(self, page: int, h: int, key: tuple) -> None:
+        """Make a full page findable under the hash ``h`` of the tokens up to its end; ``key`` =
+        (hash before the page, the page's tokens) is kept to tell a match from a collision."""
         if self.hash_of[page] is None and h not in self.by_hash:
             self.hash_of[page] = h
+            self.key_of[page] = key
             self.by_hash[h] = page
 
     def unregister(self, page: int) -> None:
         if self.hash_of[page] is not None:
             del self.by_hash[self.hash_of[page]]
-            self.hash_of[page] = None
+            self.hash_of[page] = self.key_of[page] = None
             if page in self.reclaimable:
                 del self.reclaimable[page]
                 self.free.append(page)
 
-    def lookup(self, h: int) -> Optional[int]:
-        return self.by_hash.get(h)
+    def lookup(self, h: int, key: tuple) -> Optional[int]:
+        p = self.by_hash.get(h)
+        return p if p is not None and self.key_of[p] == key else None
 
     def share(self, page: int, owner: int) -> None:
         """One more holder for a registered page."""
@@ -377,9 +381,11 @@ class CacheManager:
         self.length[slot] = new_len
 
     # ---- pages shared by their token prefix (mod.rs:1941-1947,2276-2317) --------------
-    def _next_hash(self, h: int, tokens: Sequence[int], b: int) -> int:
+    def _next_hash(self, h: int, tokens: Sequence[int], b: int):
+        """(hash of the tokens up to the end of block b, the key that confirms a match)."""
         bs = self.block_size
-        return hash((h,) + tuple(tokens[b * bs:(b + 1) * bs]))
+        key = (h, tuple(tokens[b * bs:(b + 1) * bs]))
+        return hash(key), key
 
     def adopt_prefix(self, slot: int, tokens: Sequence[int]) -> int:
         """For a slot that holds nothing yet: take over the longest run of registered pages whose
@@ -392,8 +398,8 @@ class CacheManager:
         max_reuse = (len(tokens) - 1) // self.block_size
         h, run = 0, []
         for b in range(max_reuse):
-            h = self._next_hash(h, tokens, b)
-            pages = [g.pool.lookup(h) for g in self.groups]
+            h, key = self._next_hash(h, tokens, b)
+            pages = [g.pool.lookup(h, key) for g in self.groups]
             if any(p is None for p in pages):
                 break
             run.append((h, pages))
@@ -420,9 +426,9 @@ class CacheManager:
         nb = min(upto, len(tokens), self.length[slot]) // self.block_size
         done, h = self._hashed.get(slot, (0, 0))
         for b in range(done, nb):
-            h = self._next_hash(h, tokens, b)
+            h, key = self._next_hash(h, tokens, b)
             for g in self.groups:
-                g.pool.register(int(g.table[slot, b]), h)
+                g.pool.register(int(g.table[slot, b]), h, key)
         if nb > done:
             self._hashed[slot] = (nb, h)
 
