@@ -116,3 +116,38 @@ def test_workspace_keeps_a_buffer_that_had_to_grow():
     assert any(t.data_ptr() == old and float(t.sum()) == 48.0 for t in ws._retired)
     assert ws.get("partials", (3, 8), torch.float32, cap=3).data_ptr() == b.data_ptr()
     assert ws.bytes() == (2 + 5) * 8 * 4
+
+
+def test_prefix_sharing_and_truncation_leave_the_tokens_unchanged(tmp_path):
+    """The engine with the reference kernels on the CPU: requests with common prefixes take over
+    each other's pages (also after a preemption, and with pages reclaimed in between); a
+    session goes back and forth with ``truncate_to``.  Every token is the plain implementation's."""
+    from zllm_b200 import Session
+    d = make_model_dir(tmp_path, "A", "float32", std=0.3)
+    cfg, w = P.read_model_dir(d)
+    stem = random_prompt(512, 45, 60)
+    prompts = [stem + random_prompt(512, n, 61 + n) for n in (4, 11, 2)] + [stem[:30], random_prompt(512, 20, 70)]
+    want = [P.greedy_generate(cfg, w, p, 7) for p in prompts]
+    for nb, budget in ((40, 64), (10, 9)):
+        ecfg = EngineConfig(dtype="float32", device="cpu", block_size=16 if nb == 40 else 8, num_blocks=nb, max_num_seqs=3,
+                            max_num_batched_tokens=budget, cuda_graphs=False, prefix_sharing=True)
+        eng = Engine(str(d), ops=RefOps(), engine_config=ecfg)
+        assert eng.generate(prompts, SamplingParams.greedy(max_tokens=7)) == want
+        st = eng.stats()
+        eng.runner.cache.check_integrity()
+        assert st["prefix_hits"] > 0 and st["free_pages"] == [nb]
+        assert eng.generate(prompts[:2], SamplingParams.greedy(max_tokens=7)) == want[:2]   # found again later
+    assert st["preemptions"] > 0
+    ses = Session(eng.runner, chunk=5)
+    toks = prompts[1]
+    ref = P.forward_all_positions(cfg, w, toks)
+    ses.forward_logits(toks[:33])
+    for back in (32, 17, 0, 8):                      # 17 lies inside a page that other requests registered
+        try:
+            ses.truncate_to(back)
+        except MemoryError_:
+            ses.truncate_to(back - back % 8)
+        lg = ses.forward_logits(toks[ses.position:40])
+        assert float((lg - ref[39]).abs().max()) < 1e-4
+    ses.close()
+    eng.runner.cache.check_integrity()
