@@ -27,7 +27,7 @@ class EngineConfig:
     seed: int = 0
     device: str = "cuda:0"
     cuda_graphs: bool = True           # replay captured graphs for decode-only steps
-    prefix_sharing: bool = False       # requests take over the full cache pages of a prompt prefix seen before
+    prefix_sharing: bool = True        # requests take over the full cache pages of a prompt prefix seen before
 
     def validate(self) -> "EngineConfig":
         if self.dtype not in DTYPES:
