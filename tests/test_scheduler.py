@@ -183,10 +183,14 @@ def test_cancel_frees_wherever_the_request_is():
     assert cm.free_pages() == [32] and len(cm.free_slots) == 2
 
 
-def test_random_workloads_keep_every_page_accounted(seed=3):
+@pytest.mark.parametrize("sharing", [False, True])
+def test_random_workloads_keep_every_page_accounted(sharing, seed=3):
     import random
     rng = random.Random(seed)
-    cm, sch = make(n_pages=20, bs=4, slots=4, budget=12, max_len=40)
+    cm = CacheManager([(KVCacheSpec(1, 16), None)], 4, 20, 4, 40, torch.float32, "cpu", allocate=False,
+                      prefix_sharing=sharing)
+    sch = Scheduler(cm, 12, 40)
+    stems = [[rng.randrange(500) for _ in range(20)] for _ in range(2)]
     expect = {}
     outs = {}
     pending = 25
@@ -194,7 +198,9 @@ def test_random_workloads_keep_every_page_accounted(seed=3):
         if pending and rng.random() < 0.3:
             n = rng.randint(1, 20)
             mt = rng.randint(1, 15)
-            rid = sch.add([rng.randrange(500) for _ in range(n)], SamplingParams.greedy(max_tokens=mt))
+            cut = rng.randint(0, n)                              # prompts begin with a piece of a common stem
+            prompt = rng.choice(stems)[:cut] + [rng.randrange(500) for _ in range(n - cut)]
+            rid = sch.add(prompt, SamplingParams.greedy(max_tokens=mt))
             expect[rid] = (n, mt)
             pending -= 1
         if rng.random() < 0.02 and sch.running:
@@ -211,6 +217,7 @@ def test_random_workloads_keep_every_page_accounted(seed=3):
         r = sch.requests[rid]
         assert outs[rid] == [token_for(r, n + k) for k in range(min(mt, 40 - n))]
     assert cm.free_pages() == [20] and len(cm.free_slots) == 4
+    assert (cm.prefix_hits > 0) == sharing
 
 
 def test_a_request_with_a_known_prefix_starts_behind_it():
