@@ -86,8 +86,8 @@ def test_model_spec_is_data():
     assert m.kind == "paged_attention" and m.params["n_kv_heads"] == 1 and m.params["head_dim"] == 32
     assert spec.layers[0].ffn.params == {"hidden_size": 96, "intermediate_size": 256}
     assert spec.layers[0].norm1.params["eps"] == 1e-6
-    assert spec.head_name == "lm_head.weight"
-    assert architecture("LlamaForCausalLM").build_spec(LlamaConfig.from_dict(TINY_A)).head_name is None
+    assert spec.head_name == "lm_head.weight" and spec.head_optional and not spec.tie_head
+    assert architecture("LlamaForCausalLM").build_spec(LlamaConfig.from_dict(TINY_A)).tie_head
 
 
 def test_engine_config_validation():

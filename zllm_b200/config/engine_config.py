@@ -14,6 +14,7 @@ from typing import Optional
 from ..errors import ConfigError
 
 DTYPES = ("bfloat16", "float32")
+MAX_SEQS = 1024                       # rows of one decode step (csrc/sampling.cu advance_decode_kernel)
 
 
 @dataclass
@@ -36,6 +37,9 @@ class EngineConfig:
             v = getattr(self, k)
             if not isinstance(v, int) or v <= 0:
                 raise ConfigError(f"engine setting {k} must be a positive integer, found {v!r}")
+        if self.max_num_seqs > MAX_SEQS:
+            raise ConfigError(f"engine setting max_num_seqs is at most {MAX_SEQS} (one block of the decode-advance "
+                              f"kernel covers a step's rows), found {self.max_num_seqs}")
         if self.num_blocks is not None and self.num_blocks <= 0:
             raise ConfigError(f"engine setting num_blocks must be positive, found {self.num_blocks}")
         if self.max_model_len is not None and self.max_model_len <= 0:

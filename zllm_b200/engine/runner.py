@@ -65,12 +65,12 @@ class ModelRunner:
         self.spec = arch.build_spec(self.config)
         rt = Runtime(self.dtype, self.device, ops)
         self.model = DecoderModel(self.spec, rt)
-        expected = self.model.expected_tensors()
         if model_dir is not None:
-            tensors = load_checked(model_dir, expected, self.dtype, self.device)
+            tensors = load_checked(model_dir, self.model.required_tensors(), self.dtype, self.device,
+                                   optional=self.model.optional_tensors(), ignored=self.spec.ignored_tensors)
         else:
             tensors = {}
-            for name, ws in expected.items():
+            for name, ws in self.model.expected_tensors().items():
                 dt = target_dtype(torch.bfloat16 if self.dtype == torch.bfloat16 else torch.float32, ws.role, self.dtype)
                 # drawn on the CPU (the same values everywhere) unless the caller asks for speed
                 t = random_tensor(name, ws, seed or 0, dt, self.device if random_on_device else "cpu", init_std, norm_std)

@@ -9,6 +9,7 @@ head is the embedding table (fork.rs:761-764).
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
@@ -69,14 +70,35 @@ def _named_specs(spec: ModelSpec, layers: List[Layer], final_norm, position=None
                 out[ls.tensor_names[key]] = ws
     for local, ws in final_norm.weight_specs().items():
         out[spec.final_norm_names[local]] = ws
-    if spec.head_name is not None:
-        out[spec.head_name] = WeightSpec((spec.vocab_size, spec.hidden_size), "matrix", ("normal", spec.init_std))
+    if spec.head_name is not None and not spec.head_optional:
+        out[spec.head_name] = _head_spec(spec)
     return out
 
 
-def expected_tensors(spec: ModelSpec) -> Dict[str, WeightSpec]:
+def _head_spec(spec: ModelSpec) -> WeightSpec:
+    return WeightSpec((spec.vocab_size, spec.hidden_size), "matrix", ("normal", spec.init_std))
+
+
+def optional_tensors(spec: ModelSpec) -> Dict[str, WeightSpec]:
+    """Tensors a folder may hold or lack: the output head of a model whose head falls back to the
+    embedding table when it is absent."""
+    if spec.head_name is not None and spec.head_optional:
+        return {spec.head_name: _head_spec(spec)}
+    return {}
+
+
+def required_tensors(spec: ModelSpec) -> Dict[str, WeightSpec]:
     """Every tensor the model folder must hold: name -> shape, role, init."""
     return _named_specs(spec, *_build_layers(spec))
+
+
+def expected_tensors(spec: ModelSpec) -> Dict[str, WeightSpec]:
+    """The tensors the random-weights mode writes: the required ones, and an optional head
+    unless the configuration ties it."""
+    out = required_tensors(spec)
+    if not spec.tie_head:
+        out.update(optional_tensors(spec))
+    return out
 
 
 class DecoderModel:
@@ -99,8 +121,18 @@ class DecoderModel:
         self.head = None
 
     # ---- weights -------------------------------------------------------
-    def expected_tensors(self) -> Dict[str, WeightSpec]:
+    def required_tensors(self) -> Dict[str, WeightSpec]:
         return _named_specs(self.spec, self.layers, self.final_norm, self.position)
+
+    def optional_tensors(self) -> Dict[str, WeightSpec]:
+        return optional_tensors(self.spec)
+
+    def expected_tensors(self) -> Dict[str, WeightSpec]:
+        """Required tensors plus the optional ones the configuration asks for (random mode)."""
+        out = self.required_tensors()
+        if not self.spec.tie_head:
+            out.update(self.optional_tensors())
+        return out
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         spec = self.spec
@@ -112,7 +144,16 @@ class DecoderModel:
         self.final_norm.load({n: tensors[spec.final_norm_names[n]] for n in self.final_norm.weight_specs()})
         if self.position is not None:
             self.position.load({n: tensors[spec.embedding_position_names[n]] for n in self.position.weight_specs()})
-        self.head = tensors[spec.head_name] if spec.head_name is not None else self.embedding
+        # a head tensor that is there is used; without one the head is the embedding table
+        head = tensors.get(spec.head_name) if spec.head_name is not None else None
+        if head is None and spec.head_name is not None and not spec.head_optional:
+            raise ConfigError(f"the output head {spec.head_name!r} was not given")
+        if spec.head_optional and (head is None) != bool(spec.tie_head):
+            warnings.warn(f"{spec.architecture}: the configuration says the output head is "
+                          f"{'tied' if spec.tie_head else 'untied'}, the weights "
+                          f"{'lack' if head is None else 'hold'} {spec.head_name!r}; "
+                          f"{'the embedding table' if head is None else 'the stored tensor'} is used")
+        self.head = head if head is not None else self.embedding
 
     # ---- cache needs ---------------------------------------------------
     def cache_needs(self):

@@ -62,7 +62,13 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
         final_norm=PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}),
         embedding_name="model.embed_tokens.weight",
         final_norm_names={"weight": "model.norm.weight"},
-        head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
+        # the head is tied iff the folder has no lm_head.weight (fork.rs:761-764); the flag only
+        # decides what the random-weights mode writes
+        head_name="lm_head.weight",
+        head_optional=True,
+        tie_head=bool(cfg.tie_word_embeddings),
+        # older checkpoints store each layer's rotary frequencies; they follow from the configuration
+        ignored_tensors=("*.rotary_emb.inv_freq",),
     )
 
 

@@ -102,13 +102,21 @@ class ModelSpec:
     final_norm: PartSpec
     embedding_name: str
     final_norm_names: Dict[str, str]
-    head_name: Optional[str]            # None: the head is the embedding table (tied)
+    head_name: Optional[str]            # None: the head is always the embedding table
     init_std: float = 0.02
     norm_init_std: float = 0.0          # norm weights 1 + N(0, this) in random mode
     # a position encoding that acts on the embedding output (absolute encodings); encodings that
     # act inside a mixer (rotary) are parameters of that mixer instead
     embedding_position: Optional[PartSpec] = None
     embedding_position_names: Dict[str, str] = field(default_factory=dict)
+    # True: a folder may lack ``head_name``, and the head is then the embedding table.  The tensor's
+    # presence decides, as in the reference (quantized_llama_fork.rs:761-764), not a flag.
+    head_optional: bool = False
+    # what the configuration says about tying: the random-weights mode writes no head tensor when
+    # true; at load a disagreement with what the folder holds is warned about, presence wins
+    tie_head: bool = False
+    # fnmatch patterns of tensors a folder may hold and the model does not read
+    ignored_tensors: Tuple[str, ...] = ()
 
 
 # --------------------------------------------------------------------------

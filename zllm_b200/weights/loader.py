@@ -15,6 +15,7 @@ tensor-core products take bfloat16 operands.
 """
 from __future__ import annotations
 
+from fnmatch import fnmatchcase
 from typing import Dict, Mapping, Tuple
 
 import torch
@@ -36,12 +37,17 @@ def target_dtype(stored: torch.dtype, role: str, engine_dtype: torch.dtype) -> t
 
 
 def check_names(expected: Mapping[str, WeightSpec], found: Mapping[str, Tuple[torch.dtype, Tuple[int, ...]]],
-                optional=()) -> None:
-    """Raise one ModelError listing every missing, unexpected and mis-shaped tensor."""
-    missing = [n for n in expected if n not in found and n not in optional]
-    unexpected = [n for n in found if n not in expected and n not in optional]
+                optional: Mapping[str, WeightSpec] = None, ignored=()) -> None:
+    """Raise one ModelError listing every missing, unexpected and mis-shaped tensor.
+
+    ``optional``: tensors that may be absent (checked like the others when present).
+    ``ignored``: fnmatch patterns of names a folder may hold and nobody reads."""
+    optional = optional or {}
+    missing = [n for n in expected if n not in found]
+    unexpected = [n for n in found if n not in expected and n not in optional
+                  and not any(fnmatchcase(n, pat) for pat in ignored)]
     wrong = []
-    for n, spec in expected.items():
+    for n, spec in list(expected.items()) + list(optional.items()):
         if n in found and tuple(found[n][1]) != tuple(spec.shape):
             wrong.append(f"{n}: expected {list(spec.shape)}, found {list(found[n][1])}")
     if missing or unexpected or wrong:
@@ -56,15 +62,20 @@ def check_names(expected: Mapping[str, WeightSpec], found: Mapping[str, Tuple[to
 
 
 def load_checked(model_dir, expected: Mapping[str, WeightSpec], engine_dtype: torch.dtype, device,
-                 optional=()) -> Dict[str, torch.Tensor]:
-    """Read every expected tensor from the folder onto ``device`` in its target dtype."""
+                 optional: Mapping[str, WeightSpec] = None, ignored=()) -> Dict[str, torch.Tensor]:
+    """Read every expected tensor, and every optional one that is there, from the folder onto
+    ``device`` in its target dtype."""
     where = open_model_files(model_dir)
-    found = {n: f.meta(n) for n, f in where.items()}
-    check_names(expected, found, optional)
-    out = {}
-    for name, spec in expected.items():
-        if name not in where:
-            continue
-        t = where[name].tensor(name)
-        out[name] = t.to(device=device, dtype=target_dtype(t.dtype, spec.role, engine_dtype)).contiguous()
+    try:
+        found = {n: f.meta(n) for n, f in where.items()}
+        check_names(expected, found, optional, ignored)
+        out = {}
+        for name, spec in list(expected.items()) + list((optional or {}).items()):
+            if name not in where:
+                continue
+            t = where[name].tensor(name)
+            out[name] = t.to(device=device, dtype=target_dtype(t.dtype, spec.role, engine_dtype)).contiguous()
+    finally:
+        for f in {id(f): f for f in where.values()}.values():
+            f.close()           # tensors that are still views keep the file's map alive themselves
     return out
