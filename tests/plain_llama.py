@@ -10,7 +10,12 @@ It rests on the formulas only: the reference is Rust (candle + WGSL shaders),
 no Rust toolchain or GGUF model is available where this suite runs, so the
 reference's model code can be neither imported nor compiled, and it ships no
 golden numbers.  What anchors this file is (1) the cited formulas, (2) the
-identities the reference's own tests assert, restated in ``test_plain.py``.
+identities the reference's own tests assert, restated in ``test_plain.py``,
+(3) a second statement written along the reference's own path
+(``plain_reference_path.py``: permuted weights with interleaved rotation, a
+table of frequency divisors, a cache that grows token by token) with which it
+must agree to rounding (``test_two_statements.py``), and (4) the numbers under
+``tests/golden/``, which pin both against drift.
 """
 from __future__ import annotations
 
@@ -64,44 +69,52 @@ def read_model_dir(model_dir):
 # --------------------------------------------------------------------------
 
 
-def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None, dtype=torch.float32) -> torch.Tensor:
-    """theta_j = base^(-2j/head_dim), divided by per-pair divisors f_j.
+def llama3_divisors(head_dim: int, theta: float, scaling: dict) -> list:
+    """The divisors f_j a converter stores in ``rope_freqs.weight`` for llama3 scaling (the
+    reference only consumes them, fork.rs:584-590, 722-734).  With wavelength lambda_j =
+    2*pi/theta_j: f_j = 1 if lambda_j < L/hi, f_j = F if lambda_j > L/lo, else theta_j / theta'_j
+    with theta'_j = (1-s) theta_j/F + s theta_j and s = (L/lambda_j - lo)/(hi - lo).  Python floats
+    (double), one value per pair."""
+    F = float(scaling["factor"])
+    lo = float(scaling["low_freq_factor"])
+    hi = float(scaling["high_freq_factor"])
+    L = float(scaling["original_max_position_embeddings"])
+    out = []
+    for j in range(0, head_dim, 2):
+        th = float(theta) ** (-j / head_dim)
+        lam = 2.0 * math.pi / th
+        if lam < L / hi:
+            out.append(1.0)
+        elif lam > L / lo:
+            out.append(F)
+        else:
+            s = (L / lam - lo) / (hi - lo)
+            out.append(th / ((1.0 - s) * th / F + s * th))
+    return out
 
-    zllm src/backend/candle/quantized_llama_fork.rs:579-583 (theta_j) and
-    :584-590 (division by ``rope_freqs`` divisors).  The reference takes the
-    llama3 divisors precomputed from the GGUF; from a ``config.json`` they come
-    from ``rope_scaling``: with wavelength lambda_j = 2*pi/theta_j,
-    f_j = 1 if lambda_j < L/hi, f_j = F if lambda_j > L/lo, else
-    theta'_j = (1-s) theta_j/F + s theta_j with s = (L/lambda_j - lo)/(hi - lo).
-    ``linear`` scaling multiplies every theta_j by 1/F (fork.rs:592-597).
+
+def rope_inv_freq(head_dim: int, theta: float, scaling: dict | None, dtype=torch.float32) -> torch.Tensor:
+    """theta_j = 1 / base^(i/head_dim) for i = 0, 2, 4, ..., divided by per-pair divisors f_j.
+
+    zllm src/backend/candle/quantized_llama_fork.rs:579-583 computes theta_j with every operand
+    f32 (``1f32 / freq_base.powf(i as f32 / head_dim as f32)``) and :584-590 divides by the f32
+    divisors in f32; ``dtype`` float32 does exactly that, float64 the same in double (for
+    comparisons).  ``linear`` scaling multiplies every theta_j by 1/F (fork.rs:592-597).
     """
-    j = torch.arange(0, head_dim, 2, dtype=torch.float64)
-    inv = 1.0 / (float(theta) ** (j / head_dim))
+    i = torch.arange(0, head_dim, 2, dtype=dtype)
+    inv = 1.0 / torch.pow(torch.tensor(float(theta), dtype=dtype), i / torch.tensor(float(head_dim), dtype=dtype))
     if scaling:
         kind = scaling.get("rope_type", scaling.get("type"))
         if kind == "llama3":
-            F = float(scaling["factor"])
-            lo = float(scaling["low_freq_factor"])
-            hi = float(scaling["high_freq_factor"])
-            L = float(scaling["original_max_position_embeddings"])
-            out = []
-            for th in inv.tolist():
-                lam = 2.0 * math.pi / th
-                if lam < L / hi:
-                    out.append(th)
-                elif lam > L / lo:
-                    out.append(th / F)
-                else:
-                    s = (L / lam - lo) / (hi - lo)
-                    out.append((1.0 - s) * th / F + s * th)
-            inv = torch.tensor(out, dtype=torch.float64)
+            f = torch.tensor(llama3_divisors(head_dim, theta, scaling), dtype=dtype)
+            inv = inv / f
         elif kind == "linear":
-            inv = inv / float(scaling["factor"])
+            inv = inv * (torch.tensor(1.0, dtype=dtype) / float(scaling["factor"]))
         elif kind in (None, "default"):
             pass
         else:
             raise ValueError(f"plain implementation: rope scaling {kind!r} not restated")
-    return inv.to(dtype)
+    return inv
 
 
 def rope_tables(inv_freq: torch.Tensor, positions: torch.Tensor):
@@ -200,8 +213,10 @@ def forward_all_positions(cfg: dict, w: dict, tokens, dtype=torch.float32, inter
     eps = cfg["rms_norm_eps"]
     W = {k: v.to(dtype) if v.is_floating_point() else v for k, v in w.items()}
     pos = torch.arange(T)
-    inv = rope_inv_freq(hd, cfg.get("rope_theta", 10000.0), cfg.get("rope_scaling"))
-    cos, sin = rope_tables(inv, pos)  # float32 product, as the reference
+    # float32 theta_j and a float32 product, as the reference; all in double when asked for double
+    inv = rope_inv_freq(hd, cfg.get("rope_theta", 10000.0), cfg.get("rope_scaling"),
+                        torch.float64 if dtype == torch.float64 else torch.float32)
+    cos, sin = rope_tables(inv, pos)
     cos, sin = cos.to(dtype), sin.to(dtype)
     x = W["model.embed_tokens.weight"][tokens]
     for i in range(cfg["num_hidden_layers"]):
@@ -218,8 +233,8 @@ def forward_all_positions(cfg: dict, w: dict, tokens, dtype=torch.float32, inter
         x = x + swiglu_mlp(h, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"],
                            W[p + "mlp.down_proj.weight"])
     xn = rmsnorm(x, W["model.norm.weight"], eps)
-    head = W.get("lm_head.weight")
-    if head is None or cfg.get("tie_word_embeddings", False):
+    head = W.get("lm_head.weight")            # tied iff the folder has no head tensor (fork.rs:761-764)
+    if head is None:
         head = W["model.embed_tokens.weight"]
     logits = xn @ head.T
     if return_hidden:

@@ -70,11 +70,35 @@ def test_llama3_divisors():
     assert torch.allclose(inv[lam > 64], inv0[lam > 64] / 8.0)              # long ones divided by the factor
     mid = (lam >= 16) & (lam <= 64)
     assert mid.any() and ((inv[mid] <= inv0[mid]) & (inv[mid] >= inv0[mid] / 8.0)).all()
-    # the package's own rotary part states the same formula independently
+    # the package's own rotary part states the same formula independently (float32, as the reference)
     from zllm_b200.parts.rotary import inverse_frequencies
-    assert torch.allclose(inverse_frequencies(32, 500000.0, sc), inv, rtol=1e-12)
+    got = inverse_frequencies(32, 500000.0, sc)
+    assert got.dtype == torch.float32 and torch.allclose(got.double(), inv, rtol=3e-7, atol=0)
+    assert torch.allclose(got, P.rope_inv_freq(32, 500000.0, sc), rtol=2.5e-7, atol=0)
     lin = P.rope_inv_freq(32, 10000.0, dict(rope_type="linear", factor=4.0), torch.float64)
     assert torch.allclose(lin, P.rope_inv_freq(32, 10000.0, None, torch.float64) / 4.0)
+
+
+def test_theta_in_float32_as_the_reference_and_how_far_double_precision_tables_are():
+    """fork.rs:579-583 computes theta_j in f32; tables made from double-precision theta_j rounded
+    once differ from the reference's by up to an ulp of theta_j times the position.  Stated here
+    for the largest sizes in use (head size 64, base 500000, llama3 factor 32, 131072 positions)."""
+    sc = dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+              original_max_position_embeddings=8192)
+    f32 = P.rope_inv_freq(64, 500000.0, sc)
+    f64 = P.rope_inv_freq(64, 500000.0, sc, torch.float64)
+    assert f32.dtype == torch.float32
+    rel = ((f32.double() - f64) / f64).abs().max()
+    assert float(rel) < 2.4e-7                                  # two float32 roundings and a powf
+    far = float(((f32.double() - f64.float().double()).abs() * 131071).max())
+    assert far < 0.02                                           # radians at the last position: 0.003 typical
+    # the engine's tables are the float32 product of the float32 theta_j (fork.rs:631-637)
+    from zllm_b200.parts.rotary import inverse_frequencies
+    assert torch.allclose(inverse_frequencies(64, 500000.0, sc), f32, rtol=2.5e-7, atol=0)
+    ff = [0.0, 2.0] + [1.0] * 30                                # explicit divisors; 0 leaves a pair alone
+    e = inverse_frequencies(64, 10000.0, None, ff)
+    b = inverse_frequencies(64, 10000.0, None)
+    assert e[0] == b[0] and e[1] == b[1] / 2 and torch.equal(e[2:], b[2:])
 
 
 def test_portions_with_rectangular_masks_equal_single_shot(tmp_path):
