@@ -5,7 +5,8 @@ that are no power of two, layers, vocabulary, eps, rope base and scaling, tied o
 untied head, page size).  Tiny C has head size 64 and a 4:1 group so that the
 tensor-core attention and product kernels run inside the whole-engine tests too; tiny D has
 head size 128 (heads x head size larger than the width), a page of 32 positions and an odd
-vocabulary.
+vocabulary.  Tiny E has head size 80 (the mma.sync attention kernels, key rows that share
+cache lines), a 3:1 group and linear rope scaling.
 """
 from __future__ import annotations
 
@@ -33,12 +34,20 @@ TINY_D = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_si
               num_key_value_heads=2, head_dim=128, intermediate_size=384, vocab_size=777, rms_norm_eps=1e-5,
               rope_theta=10000.0, rope_scaling=None, max_position_embeddings=1024, tie_word_embeddings=False)
 
+# head size 80: a key row of 160 bytes is no whole number of 128-byte cache lines and none of the
+# TMA or tcgen05 attention kernels takes it; a 3:1 group, linear rope scaling, an odd width
+TINY_E = dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=168, num_attention_heads=6,
+              num_key_value_heads=2, head_dim=80, intermediate_size=200, vocab_size=641, rms_norm_eps=3e-6,
+              rope_theta=100000.0, rope_scaling=dict(rope_type="linear", factor=2.0),
+              max_position_embeddings=768, tie_word_embeddings=False)
+
 # name -> (config dict, page size, weight seed, std of matrices)
 TINY = {
     "A": (TINY_A, 16, 0, 0.02),
     "B": (TINY_B, 8, 1, 0.05),
     "C": (TINY_C, 16, 2, 0.04),
     "D": (TINY_D, 32, 3, 0.05),
+    "E": (TINY_E, 16, 4, 0.05),
 }
 
 

@@ -125,99 +125,10 @@ def test_attention_part_whole_and_in_portions(dtype, nq, nkv, hd, H, window):
 
 
 # ------------------------------------------------------------------------------------------
-# a toy mixer with per-request state of fixed size, defined in the test
+# a toy architecture with a stateful mixer: defined in tests/toy_arch.py, a plug-in module of the
+# test-suite (so that the command line programs can load it too), not in the package
 # ------------------------------------------------------------------------------------------
-
-@register_mixer("toy_running_mean")
-class RunningMean(Mixer):
-    """out_t = W * mean(h_0..h_t): the state is the running sum and the count."""
-
-    def __init__(self, hidden_size):
-        self.H = hidden_size
-        self.proj = None
-
-    def weight_specs(self):
-        return {"proj": WeightSpec((self.H, self.H), "matrix", ("normal", 0.05))}
-
-    def cache_spec(self):
-        return StateSpec((self.H + 1,), "float32")
-
-    def forward(self, h, residual, ctx, cache, write_cache=True):
-        r = 0
-        for e in ctx.entries:                              # rows of one request are in order
-            n = len(e.tokens)
-            st = cache.state[e.slot]
-            csum = torch.cumsum(h[r:r + n].float(), 0) + st[:self.H]
-            cnt = st[self.H] + torch.arange(1, n + 1, device=h.device)
-            mean = (csum / cnt[:, None]).to(self.rt.dtype)
-            self.rt.ops.linear(mean.contiguous(), self.proj, residual[r:r + n], "add")
-            st[:self.H] = csum[-1]
-            st[self.H] = cnt[-1]
-            r += n
-
-
-@dataclass
-class ToyConfig:
-    architecture: str = "ToyHybridForCausalLM"
-    H: int = 64
-    V: int = 300
-
-
-def build_toy_spec(c: ToyConfig) -> ModelSpec:
-    rot = PartSpec("rotary", {"rot_dim": 16, "theta": 10000.0, "max_position": 256})
-    def attn(window):
-        return PartSpec("paged_attention", {"hidden_size": c.H, "n_heads": 4, "n_kv_heads": 2, "head_dim": 16,
-                                            "position_encoding": rot, "window": window})
-    norm = PartSpec("rmsnorm", {"size": c.H, "eps": 1e-5})
-    ffn = PartSpec("swiglu", {"hidden_size": c.H, "intermediate_size": 96})
-    def names(i, mixer_names):
-        d = {"norm1.weight": f"l{i}.n1", "norm2.weight": f"l{i}.n2", "ffn.gate_proj": f"l{i}.g",
-             "ffn.up_proj": f"l{i}.u", "ffn.down_proj": f"l{i}.d"}
-        d.update({f"mixer.{k}": f"l{i}.{k}" for k in mixer_names})
-        return d
-    qkvo = ("q_proj", "k_proj", "v_proj", "o_proj")
-    layers = [LayerSpec(attn(None), ffn, norm, norm, "pre_norm", names(0, qkvo)),
-              LayerSpec(PartSpec("toy_running_mean", {"hidden_size": c.H}), ffn, norm, norm, "pre_norm", names(1, ("proj",))),
-              LayerSpec(attn(12), ffn, norm, norm, "pre_norm", names(2, qkvo))]
-    # layer 0 runs twice with caches of its own; the last entry runs layer 0 a third time
-    # and reads the cache that run entry 0 wrote
-    order = [RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(0), RunEntry(1), RunEntry(0, cache_of=0)]
-    return ModelSpec("ToyHybridForCausalLM", c.V, c.H, 256, layers, order, norm, "emb", {"weight": "fn"}, None)
-
-
-register_architecture("ToyHybridForCausalLM", lambda d: ToyConfig(**d), build_toy_spec)
-
-
-def plain_toy_forward(w, tokens, H=64):
-    """Whole-sequence statement of the toy model with the plain functions."""
-    T = len(tokens)
-    pos = torch.arange(T)
-    cos, sin = P.rope_tables(P.rope_inv_freq(16, 10000.0, None), pos)
-    x = w["emb"][torch.tensor(tokens)]
-    kv0 = None
-
-    def attn(i, h, window, reuse=None):
-        q = P.apply_rope((h @ w[f"l{i}.q_proj"].T).reshape(T, 4, 16), cos, sin, False)
-        if reuse is None:
-            k = P.apply_rope((h @ w[f"l{i}.k_proj"].T).reshape(T, 2, 16), cos, sin, False)
-            v = (h @ w[f"l{i}.v_proj"].T).reshape(T, 2, 16)
-        else:
-            k, v = reuse
-        return P.causal_attention(q, k, v, 4, 2, pos, window) @ w[f"l{i}.o_proj"].T, (k, v)
-
-    for e, (layer, cache_of) in enumerate([(0, None), (1, None), (2, None), (0, None), (1, None), (0, 0)]):
-        h = P.rmsnorm(x, w[f"l{layer}.n1"], 1e-5)
-        if layer == 1:
-            mean = torch.cumsum(h, 0) / torch.arange(1, T + 1)[:, None]
-            x = x + mean @ w["l1.proj"].T
-        else:
-            y, kv = attn(layer, h, 12 if layer == 2 else None, kv0 if cache_of is not None else None)
-            if e == 0:
-                kv0 = kv
-            x = x + y
-        h = P.rmsnorm(x, w[f"l{layer}.n2"], 1e-5)
-        x = x + P.swiglu_mlp(h, w[f"l{layer}.g"], w[f"l{layer}.u"], w[f"l{layer}.d"])
-    return P.rmsnorm(x, w["fn"], 1e-5) @ w["emb"].T
+from toy_arch import ToyConfig, plain_toy_forward, plain_toy_greedy          # noqa: E402  (registers the architecture)
 
 
 def test_toy_mixer_with_state_is_registered_built_and_stepped():
@@ -228,10 +139,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     # entry 5 reads entry 0's cache and owns none
     assert [(g.window, g.entries) for g in cm.groups] == [(None, [0, 3]), (12, [2])]
     assert sorted(cm.state) == [1, 4] and cm.view(5) is None
-    w = {}
-    for name in r.model.expected_tensors():
-        pass
-    # collect the weights the runner drew, by their names
+    # the weights the runner drew, by their names
     exp = r.model.expected_tensors()
     from zllm_b200.weights.random_init import random_tensor
     w = {n: random_tensor(n, s, 4, torch.float32, "cpu") for n, s in exp.items()}
@@ -264,6 +172,56 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     assert float((lg - ref_b).abs().max()) < 1e-4
     r.release(sb); r.release(sc)
     assert cm.free_pages() == [40, 40]
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+def test_toy_architecture_generates_through_the_engine(tmp_path, graphs):
+    """The toy architecture through ``Engine.generate``: greedy streams with a stop token, four
+    requests through three slots.  With graphs on, its stateful mixer runs inside captured decode
+    graphs (and the run-ahead), where it knows its rows' requests by device-side slots only."""
+    from zllm_b200 import Engine, SamplingParams
+    from zllm_b200.weights import write_random_model
+    d = write_random_model(tmp_path / "toy", ToyConfig(), 4, "float32", std=0.2, norm_std=0.1)
+    w = P.read_safetensors(d / "model.safetensors")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 299, (n,), generator=g).tolist() for n in (5, 23, 2, 11)]
+    free_run = [plain_toy_greedy(w, p, 14) for p in prompts]
+    stop = free_run[1][6]
+    want = [plain_toy_greedy(w, p, 14, stop=(stop,)) for p in prompts]
+    eng = Engine(str(d), dtype="float32", block_size=4, num_blocks=80, max_num_seqs=3, max_num_batched_tokens=24,
+                 cuda_graphs=graphs)
+    assert eng.generate(prompts, SamplingParams.greedy(max_tokens=14)) == free_run
+    got = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=14, stop_token_ids=(stop,)))
+    assert got == want
+    if graphs:
+        assert eng.runner._graphs and all(g["graph"] is not None for g in eng.runner._graphs.values())
+    eng.runner.cache.check_integrity()
+    assert eng.stats()["free_slots"] == 3 and eng.stats()["free_pages"] == [80, 80]
+
+
+def test_toy_architecture_through_trace_run_as_a_plugin(tmp_path):
+    """``bin/trace_run`` on the toy architecture's model folder: the program learns the architecture
+    from the plug-in module named in ZLLM_PLUGINS, nothing of the framework's files changes."""
+    import os
+    import traces as TR
+    from zllm_b200.weights import write_random_model
+    d = write_random_model(tmp_path / "toy", ToyConfig(), 4, "float32", std=0.2, norm_std=0.1)
+    w = P.read_safetensors(d / "model.safetensors")
+    g = torch.Generator().manual_seed(5)
+    reqs = [(f"r{i}", torch.randint(0, 300, (n,), generator=g).tolist()) for i, n in enumerate((9, 40, 3, 26))]
+    ref = {rid: plain_toy_forward(w, toks) for rid, toks in reqs}
+    steps = TR.family_whole(reqs, "w.") + TR.family_tail(reqs, 8, "t.") + TR.family_portions(reqs, prefix="p.") \
+        + TR.family_mixed(reqs, 192, 3, 1, "m.")
+    tests_dir = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, ZLLM_PLUGINS="toy_arch",
+               PYTHONPATH=tests_dir + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    got = TR.replay_program(d, "float32", steps, 192, tmp_path / "out", 300, extra_args=("--block-size", "4"), env=env)
+    for prefix in ("w.", "t.", "p.", "m."):
+        TR.compare(got, ref, reqs, prefix, 1e-4, 0.0, f"toy {prefix}")
+    for rid, toks in reqs:                           # the ways of cutting agree among themselves
+        for p_ in range(len(toks)):
+            for prefix in ("t.", "p.", "m."):
+                assert float((got[("w." + rid, p_)] - got[(prefix + rid, p_)]).abs().max()) < 2e-5
 
 
 # ------------------------------------------------------------------------------------------

@@ -173,7 +173,9 @@ def replay_program(model_dir, dtype, steps, max_tokens, out_dir, vocab, extra_ar
 
 
 def compare(got, reference, reqs, prefix, atol, rtol_of_scale, what):
-    """Every (request, position) of ``got`` against the plain logits ``reference[rid][pos]``."""
+    """Every (request, position) of ``got`` against the plain logits ``reference[rid][pos]``.
+    The worst error, as a fraction of the request's largest |logit|, is recorded under ``what``."""
+    from gpu_util import observe
     worst, worst_at = 0.0, None
     for rid, toks in reqs:
         ref = reference[rid]
@@ -185,6 +187,8 @@ def compare(got, reference, reqs, prefix, atol, rtol_of_scale, what):
             bound = atol + rtol_of_scale * scale
             if err > worst:
                 worst, worst_at = err, (rid, p)
+            if rtol_of_scale > 0:
+                observe(what, err, scale, rtol_of_scale)
             assert err <= bound, (f"{what}: request {rid} position {p} (first wrong place): "
                                   f"max abs error {err:.3e} > {bound:.3e}")
     return worst, worst_at

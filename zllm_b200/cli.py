@@ -50,12 +50,7 @@ def cmd_generate(args) -> int:
     try:
         eng = Engine(str(model_dir), dtype=args.dtype, max_num_seqs=1, block_size=args.block_size,
                      max_model_len=args.max_seq_len)
-        stops = []
-        eos = eng.config.eos_token_id
-        if isinstance(eos, int):
-            stops = [eos]
-        elif isinstance(eos, (list, tuple)):
-            stops = [int(e) for e in eos]
+        stops = list(eng.runner.spec.stop_token_ids)        # the architecture's end-of-text ids
         params = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, seed=args.seed,
                                 max_tokens=args.max_tokens, stop_token_ids=tuple(stops))
         rid = eng.add_request(prompt_ids, params)

@@ -5,7 +5,8 @@ After zllm src/backend/arch.rs:21-64: one table, a lookup that ignores case
 (``detect``: ``unsupported GGUF architecture "x"``).  An entry carries the
 typed-config reader and the function that turns a configuration into a
 ``ModelSpec`` (layers listed part by part); no other file needs to know the
-name.
+name.  Architectures defined outside the package come in as plug-in modules
+named in ``ZLLM_PLUGINS``.
 """
 from __future__ import annotations
 
@@ -53,6 +54,23 @@ def architecture_of(config_json: dict) -> ArchEntry:
     return architecture(archs[0])
 
 
+_plugins_loaded = False
+
+
 def _ensure_builtin():
-    # The built-in architectures register themselves on import.
+    """The built-in architectures register themselves on import.  So do plug-ins: every module
+    named in the environment variable ZLLM_PLUGINS (comma-separated, importable from sys.path) is
+    imported once; a plug-in registers its parts and its architecture with the ``register_*``
+    functions, and the command line, ``bin/trace_run`` and the Python entry points then take its
+    model folders like any other."""
+    global _plugins_loaded
     from ..models import llama  # noqa: F401
+    if not _plugins_loaded:
+        _plugins_loaded = True
+        import importlib
+        import os
+        for mod in filter(None, (m.strip() for m in os.environ.get("ZLLM_PLUGINS", "").split(","))):
+            try:
+                importlib.import_module(mod)
+            except ImportError as e:
+                raise ConfigError(f"ZLLM_PLUGINS names {mod!r}, which cannot be imported: {e}") from e

@@ -311,14 +311,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
         const int page = trow[blk];
         return page >= 0 ? pages + (((size_t)page * nkv + kvh) * bs + off) * HD : nullptr;
     };
-    // (rows shorter than a 128-byte line bypass L1: a line fetched before the wait would hold the
-    // stale bytes of the row's own key)
+    // (a key row that is not a whole number of 128-byte lines -- every head size but 64 and 128 --
+    // shares a line with its neighbour, so these loads bypass L1: a line fetched before the wait
+    // for the row before this one would hold the stale bytes of the row's own key)
     auto load_k_row = [&](int j, const bf16* krow) {         // j must be a compile-time index after unrolling
 #pragma unroll
         for (int pq = 0; pq < HD / 32; ++pq) {
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (krow != nullptr) v = (HD >= 64) ? *reinterpret_cast<const uint4*>(krow + 32 * pq + 8 * t)
-                                                : __ldcg(reinterpret_cast<const uint4*>(krow + 32 * pq + 8 * t));
+            if (krow != nullptr) v = (HD % 64 == 0) ? *reinterpret_cast<const uint4*>(krow + 32 * pq + 8 * t)
+                                                    : __ldcg(reinterpret_cast<const uint4*>(krow + 32 * pq + 8 * t));
             kf[j][2 * pq][0] = v.x; kf[j][2 * pq][1] = v.y;
             kf[j][2 * pq + 1][0] = v.z; kf[j][2 * pq + 1][1] = v.w;
         }
@@ -637,9 +638,10 @@ ZLLM_API int zllm_attention_decode_bf16_noalloc(const void* qkv, void* out, cons
                                                 char* err, int err_len) {
     if (n_rows <= 0) return 0;
     if (nkv <= 0 || nq <= 0 || nq % nkv || nq / nkv > 16 || n_splits <= 0 || n_splits > 65535 || nkv > 65535 ||
-        hd % 16 || hd < 16 || hd > 128 || !(scale > 0.f)) {
+        hd % 16 || hd < 16 || hd > 128 || !(scale > 0.f) || bs <= 0 || max_blocks <= 0) {
         noalloc_msg(err, err_len, "attention_decode_noalloc: head size must be 16..128 in steps of 16, nq a multiple "
-                                  "of nkv with at most 16 query heads per kv head, scale > 0, n_splits in 1..65535");
+                                  "of nkv with at most 16 query heads per kv head, scale > 0, n_splits in 1..65535, "
+                                  "page size and pages per request positive");
         return ZLLM_ERR_UNSUPPORTED;
     }
     const unsigned long long need = (unsigned long long)n_rows * nq * n_splits * (hd + 2);

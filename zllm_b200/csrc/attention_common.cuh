@@ -50,7 +50,7 @@ template <int HD, int NTHR>
 __global__ void __launch_bounds__(NTHR) decode_combine_kernel(
     const int* __restrict__ rows, const int* __restrict__ positions, const int* __restrict__ row_slot,
     const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int window,
-    int max_splits) {
+    int max_splits, int n_splits) {
     constexpr int nthr = NTHR, G = NTHR / HD;                // groups of HD threads (at least one)
     __shared__ float s_red[NTHR / 32];
     __shared__ float s_acc[NTHR];
@@ -66,7 +66,9 @@ __global__ void __launch_bounds__(NTHR) decode_combine_kernel(
     }
     const int pos = positions[row];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int ns = (pos - lo) / SPLIT_KEYS + 1;
+    // never beyond what the split kernel's grid wrote (a caller that passed too few splits for
+    // this row gets the keys of the splits it asked for, not someone else's partials)
+    const int ns = min((pos - lo) / SPLIT_KEYS + 1, n_splits);
     const size_t base = ((size_t)blockIdx.x * nq + h) * max_splits;
     // M: the largest of the splits' maxima
     float m = -INFINITY;
@@ -121,7 +123,7 @@ static int launch_combine(int n_rows, int nq, int n_splits, cudaStream_t s, cons
     constexpr int ONE = HD <= 32 ? 32 : (HD <= 64 ? 64 : 128);
     if (n_splits <= 8)
         return launch_pdl(decode_combine_kernel<HD, ONE>, dim3(n_rows, nq), dim3(ONE), 0, s, rows, positions, row_slot, part_o,
-                          part_ml, out, nq, window, max_splits);
+                          part_ml, out, nq, window, max_splits, n_splits);
     return launch_pdl(decode_combine_kernel<HD, COMBINE_THREADS>, dim3(n_rows, nq), dim3(COMBINE_THREADS), 0, s, rows, positions,
-                      row_slot, part_o, part_ml, out, nq, window, max_splits);
+                      row_slot, part_o, part_ml, out, nq, window, max_splits, n_splits);
 }

@@ -23,6 +23,13 @@
 //    it.  The kernels write every partial they later read, so nothing needs clearing; but two
 //    calls that overlap on the GPU (different streams, or a graph replayed concurrently)
 //    race on it.  Keep calls on one device ordered.
+//  * n_splits must cover the longest row: ceil(keys of the row / 256).  The host cannot check
+//    it (positions live on the device); a row that needs more splits than were passed is
+//    merged from the splits that were computed only, i.e. its oldest n_splits * 256 keys.
+//  * The kernels are launched with programmatic dependent launch and read rows, positions,
+//    row_slot, table and every key and value older than a row's own position BEFORE they wait
+//    for the kernel launched just before them on the stream.  That kernel may write qkv, out
+//    and the keys and values at the rows' own positions, nothing else of the operands.
 #pragma once
 
 #ifdef __cplusplus

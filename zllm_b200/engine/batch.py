@@ -4,8 +4,11 @@ The reference's step takes parallel arrays ``tokens[m], positions[m], slots[m]``
 rows of one slot at consecutive positions are a prompt portion, and causality
 inside a portion comes from the positions alone because every row's key and
 value are written before any row attends (zllm src/backend/gpu/mod.rs:2165,
-2245-2253, 2485-2491).  The same here, plus what tiled kernels want: which rows
-are single decoded tokens, and the portions cut into query tiles.
+2245-2253, 2485-2491).  The same here, plus which rows are single decoded
+tokens.  What a particular kernel wants beyond that (the attention kernels'
+query tiles, say) is not described here: a part may register a *planner* that
+writes its own integer tables into the step buffer's auxiliary region, which
+goes to the device with the same single copy.
 
 All integer arrays of a step live in ONE pinned host buffer and ONE device
 buffer with fixed section offsets, so a step costs one host-to-device copy and
@@ -18,9 +21,6 @@ from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
-
-QUERY_TILE = 128         # rows of one portion that one attention tile covers (csrc/attention_bf16.cu PF_QROWS)
-
 
 @dataclass
 class StepEntry:
@@ -36,15 +36,15 @@ class StepBuffers:
     """Pinned host + device int32 storage for a step of at most ``cap_rows`` rows."""
 
     # the two float64 sections come first so that they are 8-byte aligned
-    SECTIONS = ("pool_temp", "pool_topp", "token_ids", "positions", "row_slot", "want_rows", "decode_rows", "tiles", "temps",
+    SECTIONS = ("pool_temp", "pool_topp", "token_ids", "positions", "row_slot", "want_rows", "decode_rows", "aux", "temps",
                 "seeds", "pool_topk")
 
     def __init__(self, cap_rows: int, cap_want: int, device):
         self.cap_rows = cap_rows
         self.cap_want = cap_want
-        self.cap_tiles = cap_rows  # every portion has >= 2 rows, so tiles <= rows
         sizes = {"token_ids": cap_rows, "positions": cap_rows, "row_slot": cap_rows, "want_rows": cap_want,
-                 "decode_rows": cap_rows, "tiles": 4 * self.cap_tiles, "temps": cap_want, "seeds": cap_want,
+                 # the parts' own tables of a step (see ``AuxRegion``)
+                 "decode_rows": cap_rows, "aux": 4 * cap_rows + 64, "temps": cap_want, "seeds": cap_want,
                  # candidate-pool sampling of a wanted row: temperature and top_p as float64 (two words), top_k
                  "pool_temp": 2 * cap_want, "pool_topp": 2 * cap_want, "pool_topk": cap_want}
         self.offsets = {}
@@ -82,6 +82,23 @@ class StepBuffers:
             self._pending = True
 
 
+class AuxRegion:
+    """Hands out pieces of the step buffer's auxiliary section to the planners of a step.
+    ``take(n)`` returns (host int32 view of n words, its offset in the section)."""
+
+    def __init__(self, host_view):
+        self.host = host_view
+        self.used = 0
+
+    def take(self, n: int):
+        if self.used + n > self.host.shape[0]:
+            raise MemoryError(f"the step buffer's auxiliary region holds {self.host.shape[0]} words; "
+                              f"{self.used + n} were asked for")
+        off = self.used
+        self.used += n
+        return self.host[off:off + n], off
+
+
 @dataclass
 class StepContext:
     """What parts and kernels see of a step."""
@@ -94,8 +111,7 @@ class StepContext:
     want_rows: torch.Tensor      # [R] int32
     decode_rows: torch.Tensor    # [n_decode] int32 rows that are single decoded tokens
     n_decode: int
-    tiles: torch.Tensor          # [n_tiles, 4] int32: first row, rows, slot, position of first row
-    n_tiles: int
+    aux: dict                    # name -> int32 device table a part's planner wrote for this step
     max_context: int             # largest position + 1 among the rows (bounds split counts)
     ws: object = None            # workspace
     entries: Optional[List[StepEntry]] = None
@@ -103,11 +119,14 @@ class StepContext:
     fixed_splits: int = 0        # > 0: the split count a captured graph was recorded with
 
 
-def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[int], pad_rows: int = 0):
-    """Write the step's arrays into ``buf`` (host side) and return the counts.
+def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[int], pad_rows: int = 0, planners=()):
+    """Write the step's arrays into ``buf`` (host side) and return the counts
+    (rows, wanted rows, decoded rows, the planners' tables, largest context).
 
     ``starts[i]`` is the position of entry i's first token.  ``pad_rows`` > 0
     pads the row arrays to that many rows with slot -1 (for graph buckets).
+    ``planners``: callables ``(entries, starts, aux: AuxRegion) -> {name: (offset, shape)}`` of
+    the model's parts; each writes what its kernels want to know about this step.
     """
     buf.begin_fill()
     tok = buf.host_section("token_ids")
@@ -115,11 +134,9 @@ def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[i
     rs = buf.host_section("row_slot")
     want = buf.host_section("want_rows")
     dec = buf.host_section("decode_rows")
-    tiles = buf.host_section("tiles")
     r = 0
     nw = 0
     nd = 0
-    nt = 0
     max_ctx = 0
     for e, start in zip(entries, starts):
         n = len(e.tokens)
@@ -134,11 +151,6 @@ def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[i
         if n == 1:
             dec[nd] = r
             nd += 1
-        else:
-            for q0 in range(0, n, QUERY_TILE):
-                m = min(QUERY_TILE, n - q0)
-                tiles[4 * nt:4 * nt + 4] = (r + q0, m, e.slot, start + q0)
-                nt += 1
         max_ctx = max(max_ctx, start + n)
         r += n
     T = r
@@ -150,10 +162,22 @@ def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[i
             dec[nd] = i
             nd += 1
         T = pad_rows
-    return T, nw, nd, nt, max_ctx
+    plans = {}
+    if planners:
+        aux = AuxRegion(buf.host_section("aux"))
+        for plan in planners:
+            plans.update(plan(entries, starts, aux))
+    return T, nw, nd, plans, max_ctx
 
 
-def make_context(buf: StepBuffers, T, R, nd, nt, max_ctx, ws, entries=None, starts=None) -> StepContext:
+def make_context(buf: StepBuffers, T, R, nd, plans, max_ctx, ws, entries=None, starts=None) -> StepContext:
+    aux_dev = buf.dev_section("aux")
+    aux = {}
+    for name, (off, shape) in (plans or {}).items():
+        n = 1
+        for d in shape:
+            n *= d
+        aux[name] = aux_dev[off:off + n].view(*shape)
     return StepContext(
         T=T, R=R,
         token_ids=buf.dev_section("token_ids", T),
@@ -162,8 +186,7 @@ def make_context(buf: StepBuffers, T, R, nd, nt, max_ctx, ws, entries=None, star
         want_rows=buf.dev_section("want_rows", R),
         decode_rows=buf.dev_section("decode_rows", nd),
         n_decode=nd,
-        tiles=buf.dev_section("tiles", 4 * nt).view(-1, 4) if nt else buf.dev_section("tiles", 0).view(0, 4),
-        n_tiles=nt,
+        aux=aux,
         max_context=max_ctx,
         ws=ws, entries=list(entries) if entries is not None else None, starts=list(starts) if starts else None,
     )

@@ -51,7 +51,7 @@ class Engine:
     # ---- requests ------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
                     request_id: Optional[int] = None) -> int:
-        V = self.config.vocab_size
+        V = self.runner.spec.vocab_size
         for t in prompt_token_ids:
             if not 0 <= int(t) < V:
                 raise RequestError(f"token id {t} is outside the vocabulary of {V}")

@@ -90,6 +90,7 @@ class ModelRunner:
         self.max_rows = self.ecfg.max_num_batched_tokens
         self.ws = Workspace(self.max_rows, self.device)
         self.buffers = StepBuffers(self.max_rows, self.max_rows, self.device)
+        self._planners = self.model.step_planners()
         self._graphs: Dict[tuple, dict] = {}
         self._token_ring = None
         self._last_key = None
@@ -162,10 +163,10 @@ class ModelRunner:
         The tensor is a view of a reused buffer: read it before the next step."""
         starts = self._prepare(entries)
         buf = self.buffers
-        T, R, nd, nt, max_ctx = fill_step(buf, entries, starts)
+        T, R, nd, plans, max_ctx = fill_step(buf, entries, starts, planners=self._planners)
         buf.upload()
         self.cache.sync_tables()
-        ctx = make_context(buf, T, R, nd, nt, max_ctx, self.ws, entries, starts)
+        ctx = make_context(buf, T, R, nd, plans, max_ctx, self.ws, entries, starts)
         logits = self._forward(ctx)
         for e, s in zip(entries, starts):
             self.cache.advance(e.slot, s + len(e.tokens))
@@ -208,7 +209,7 @@ class ModelRunner:
             g = self._make_decode_graph(bucket, split_bucket, use_graph, pool is not None)
             self._graphs[key] = g
         buf = g["buf"]
-        T, R, nd, nt, _ = fill_step(buf, entries, starts, pad_rows=bucket)
+        fill_step(buf, entries, starts, pad_rows=bucket)
         if pool is not None:
             pt = buf.host_section("pool_temp").view("float64")
             pp = buf.host_section("pool_topp").view("float64")
@@ -231,6 +232,7 @@ class ModelRunner:
         else:
             g["ctx"].max_context = max_ctx          # no captured shape to honour: size the step as it is
             g["ctx"].fixed_splits = 0
+            g["ctx"].entries, g["ctx"].starts = list(entries), list(starts)
             self._decode_body(g)
         for e, s in zip(entries, starts):
             self.cache.advance(e.slot, s + 1)
@@ -371,7 +373,7 @@ class ModelRunner:
 
     def _make_decode_graph(self, bucket: int, split_bucket: int, use_graph: bool, pool: bool = False):
         buf = StepBuffers(bucket, bucket, self.device)
-        ctx = make_context(buf, bucket, bucket, bucket, 0, 0, self.ws)
+        ctx = make_context(buf, bucket, bucket, bucket, None, 0, self.ws)
         ctx.max_context = split_bucket * self.ops.decode_split_keys if split_bucket else 0
         ctx.fixed_splits = split_bucket
         out = torch.zeros(bucket, dtype=torch.int32, device=self.device)

@@ -378,6 +378,25 @@ class CudaOps:
             maps = self._kv_maps[key] = tuple(bufs)
         return maps
 
+    QUERY_TILE = 128        # query rows of one tile of the prefill attention kernels (PF_QROWS in csrc)
+
+    @classmethod
+    def plan_query_tiles(cls, entries, starts, aux):
+        """The step planner of the attention path: every portion (an entry of two tokens or more)
+        cut into tiles of QUERY_TILE rows, as [first row, rows, slot, position of the first row]."""
+        q = cls.QUERY_TILE
+        n = sum(-(-len(e.tokens) // q) for e in entries if len(e.tokens) > 1)
+        host, off = aux.take(4 * n)
+        r = i = 0
+        for e, start in zip(entries, starts):
+            m = len(e.tokens)
+            if m > 1:
+                for q0 in range(0, m, q):
+                    host[i:i + 4] = (r + q0, min(q, m - q0), e.slot, start + q0)
+                    i += 4
+            r += m
+        return {"query_tiles": (off, (n, 4))}
+
     def _attention_bf16(self, qkv, out, ctx, cache, nq, nkv, hd, scale, window) -> bool:
         """Tensor-core attention: decoded rows by the split kernel, portions by the tiled kernel.
         False: head size or group not taken, every row goes to the plain kernel."""
@@ -412,17 +431,19 @@ class CudaOps:
                 self._check(code, "attention_decode_bf16")
             self.launches += 1                  # split kernel + combine kernel
         bs = cache.block_size
-        if ctx.n_tiles > 0 and not window and hd in (64, 128) and (16 if hd == 128 else 8) <= bs <= 128 \
+        tiles = ctx.aux.get("query_tiles")
+        n_tiles = tiles.shape[0] if tiles is not None else 0
+        if n_tiles > 0 and not window and hd in (64, 128) and (16 if hd == 128 else 8) <= bs <= 128 \
                 and bs & (bs - 1) == 0:
             # the tcgen05 kernel: Q and pages by TMA, S and O in tensor memory
             code = self.lib("attention_prefill_tc").zllm_attention_prefill_tc(
-                _ptr(qkv), c_int(qkv.shape[0]), _ptr(out), _ptr(ctx.tiles), c_int(ctx.n_tiles), _ptr(cache.k_pages),
+                _ptr(qkv), c_int(qkv.shape[0]), _ptr(out), _ptr(tiles), c_int(n_tiles), _ptr(cache.k_pages),
                 _ptr(cache.v_pages), c_longlong(cache.k_pages.shape[0]), _ptr(tb), c_int(tb.shape[1]), c_int(bs),
                 c_int(nq), c_int(nkv), c_int(hd), c_float(scale), self._stream())
             self._check(code, "attention_prefill_tc")
-        elif ctx.n_tiles > 0:
+        elif n_tiles > 0:
             code = lib.zllm_attention_prefill_bf16(
-                _ptr(qkv), _ptr(out), _ptr(ctx.tiles), c_int(ctx.n_tiles), _ptr(cache.k_pages), _ptr(cache.v_pages),
+                _ptr(qkv), _ptr(out), _ptr(tiles), c_int(n_tiles), _ptr(cache.k_pages), _ptr(cache.v_pages),
                 _ptr(tb), c_int(tb.shape[1]), c_int(cache.block_size), c_int(nq), c_int(nkv), c_int(hd),
                 c_float(scale), c_int(window or 0), self._stream())
             self._check(code, "attention_prefill_bf16")

@@ -160,6 +160,18 @@ class DecoderModel:
         """Per run entry: (cache spec of its mixer or None, cache_of)."""
         return [(self.layers[e.layer].mixer.cache_spec(), e.cache_of) for e in self.spec.run_order]
 
+    def step_planners(self):
+        """The planners of the model's parts, each once: callables that write a part's own tables
+        for a step into the step buffer (``parts.base.Part.step_planner``)."""
+        seen, out = set(), []
+        for layer in self.layers:
+            for part in layer.parts().values():
+                pl = part.step_planner()
+                if pl is not None and pl not in seen:
+                    seen.add(pl)
+                    out.append(pl)
+        return tuple(out)
+
     # ---- one forward over the step's rows ------------------------------
     def forward(self, ctx, cache_views) -> Optional[torch.Tensor]:
         """Runs the rows of ``ctx``; returns float32 logits [R, V] for ``ctx.want_rows`` (None if R == 0)."""

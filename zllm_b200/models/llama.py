@@ -17,6 +17,15 @@ from ..config.registry import register_architecture
 from ..parts.base import LayerSpec, ModelSpec, PartSpec, RunEntry
 
 
+def _as_ids(eos) -> tuple:
+    """config.json gives one end-of-text id or a list of them (or none)."""
+    if isinstance(eos, bool) or eos is None:
+        return ()
+    if isinstance(eos, int):
+        return (eos,)
+    return tuple(int(e) for e in eos)
+
+
 def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
     rotary = PartSpec("rotary", {
         "rot_dim": cfg.head_dim,
@@ -69,6 +78,7 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
         tie_head=bool(cfg.tie_word_embeddings),
         # older checkpoints store each layer's rotary frequencies; they follow from the configuration
         ignored_tensors=("*.rotary_emb.inv_freq",),
+        stop_token_ids=_as_ids(cfg.eos_token_id),
     )
 
 

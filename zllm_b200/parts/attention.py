@@ -69,6 +69,10 @@ class PagedAttention(Mixer):
 
     accepts_input_norm = True
 
+    def step_planner(self):
+        # the tiled attention kernels want each portion cut into query tiles of their own size
+        return getattr(self.rt.ops, "plan_query_tiles", None)
+
     def forward(self, h, residual, ctx, cache, write_cache: bool = True, input_norm=None):
         """``input_norm`` None: h is the normed input.  Otherwise h is the float32 residual and
         ``input_norm`` = (weight, eps) of the RMS norm to apply to it inside the QKV product."""

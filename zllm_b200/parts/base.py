@@ -117,6 +117,8 @@ class ModelSpec:
     tie_head: bool = False
     # fnmatch patterns of tensors a folder may hold and the model does not read
     ignored_tensors: Tuple[str, ...] = ()
+    # token ids that end a generation unless the caller says otherwise (a model's end-of-text ids)
+    stop_token_ids: Tuple[int, ...] = ()
 
 
 # --------------------------------------------------------------------------
@@ -161,6 +163,14 @@ class Part:
         """Receive own tensors (local names), already on device in the dtype their role asks."""
         for k, v in tensors.items():
             setattr(self, k, v)
+
+    def step_planner(self):
+        """None, or a callable ``(entries, starts, aux) -> {name: (offset, shape)}`` that is run on
+        the host once per step outside captured graphs: it writes integer tables its kernels want
+        (cut from ``aux.take(n)``, a piece of the step's one upload) and names them; the forward
+        finds them as ``ctx.aux[name]`` on the device.  Parts that return equal callables share one
+        run.  Steps replayed from a graph (single decoded tokens only) run no planner."""
+        return None
 
 
 class Norm(Part):
