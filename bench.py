@@ -3,6 +3,9 @@
 bfloat16) on one B200, with prefill throughput, roofline fractions and end-to-end numbers.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --config 8b          # Llama-3.1-8B shape: decode to context 8192, prefill 2,048
+    python bench.py --config 3b-mixed    # Llama-3.2-3B shape: 32 requests, 512-token portions beside decoding
+    python bench.py --config cpu-baseline  # the plain CPU implementation of the test-suite, timed (no GPU)
 
 One JSON line on stdout.  ``value``: decode tokens/s at batch 8 near context 4096, K decode
 steps timed on the device with CUDA events (the steps replay a captured graph back to back,
@@ -176,6 +179,133 @@ def profile_case(args):
     return 0
 
 
+def mixed_workload(args, K, W):
+    """BASELINE.json's fourth configuration: Llama-3.2-3B layer sizes (28 layers), 32 requests with
+    prompt lengths drawn uniformly from 128..2048 (seeded), a token budget of 512 per step (prompt
+    portions beside decoded tokens in one forward), 256 new tokens each, through ``Engine``.
+    One JSON line: generated tokens/s as ``value`` (wall clock around ``Engine.step()``), tokens/s
+    with the prompts, the median time of decode-only and of mixed steps, and the decode-only
+    steps against the copy bandwidth."""
+    import random
+    import statistics
+
+    import torch
+    from zllm_b200 import Engine, EngineConfig, LlamaConfig, SamplingParams
+
+    pk, pk_src = peaks()
+    cfg = LlamaConfig.from_dict(dict(MODEL, **SHAPES["3b"]))
+    weight_bytes, kv_per_token, prefill_flops = model_numbers(cfg)
+    n_req, new_tokens, budget = 32, 256, 512
+    rng = random.Random(3)
+    lengths = [rng.randint(128, 2048) for _ in range(n_req)]
+    gen = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in lengths]
+    max_len = 2048 + new_tokens + 8
+    t0 = time.time()
+    eng = Engine(config=cfg, seed=3, random_on_device=True, engine_config=EngineConfig(
+        dtype="bfloat16", block_size=BLOCK, num_blocks=n_req * (-(-max_len // BLOCK)) + 8, max_num_seqs=n_req,
+        max_num_batched_tokens=budget, max_model_len=max_len, prefix_sharing=False))
+    print(f"[bench] model built in {time.time() - t0:.1f} s; weights {weight_bytes / 1e9:.3f} GB", file=sys.stderr, flush=True)
+    eng.warm_up(max_batch=n_req, max_context=max_len)
+
+    def run():
+        for p in prompts:
+            eng.add_request(p, SamplingParams.greedy(max_tokens=new_tokens))
+        steps = []                                # (wall ms, decoded rows, prompt tokens, cached positions of the decoded rows)
+        torch.cuda.synchronize()
+        t_start = last = time.perf_counter()
+        n_out = 0
+        while eng.has_unfinished():
+            cached = sum(len(r.tokens) for r in eng.scheduler.running)
+            n_out += len(eng.step())
+            now = time.perf_counter()
+            ls = eng.last_step
+            steps.append(((now - last) * 1e3, ls["decodes"], ls["prompt_tokens"], cached))
+            last = now
+        torch.cuda.synchronize()
+        return time.perf_counter() - t_start, n_out, steps
+
+    clocks = ClockSampler()
+    run()                                          # warm-up: every graph bucket and workspace size has been seen
+    clocks.start()
+    total_s, n_out, steps = run()
+    clk = clocks.stop()
+    dec = [s for s in steps if s[2] == 0 and s[1] == n_req]          # all 32 requests decoding, nothing else
+    mixed = [s for s in steps if s[2] > 0]
+    dec_ms = statistics.median(s[0] for s in dec) if dec else None
+    dec_ctx = statistics.median(s[3] for s in dec) if dec else 0
+    dec_bytes = weight_bytes + dec_ctx * kv_per_token
+    achieved = dec_bytes / (dec_ms / 1e3) / 1e9 if dec_ms else None
+    mixed_flops = [2 * (weight_bytes / 2) * (s[1] + s[2]) for s in mixed]     # products only
+    line = {
+        "metric": "generated tok/s, Llama-3.2-3B shape, bf16, 32 requests, prompts 128-2048 in 512-token portions beside "
+                  "decode, 256 new tokens each (random weights)",
+        "value": round(n_out / total_s, 1), "unit": "tokens/s", "n_gpus": 1, "steps": len(steps), "warmup": len(steps),
+        "ms_per_step": round(total_s * 1e3 / len(steps), 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights N(0,0.02) seed 3)", "impl": "ours",
+        "config": {"model": "Llama-3.2-3B-shaped", "layers": cfg.num_hidden_layers, "layers_full": 28,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "tied": True,
+                   "global_batch": n_req, "seq_len": max_len - 8, "prompt_len": "128-2048", "token_budget": budget,
+                   "new_tokens": new_tokens, "kv_block": BLOCK, "parallelism": "single GPU",
+                   "l2": f"inputs larger than L2 ({weight_bytes / 1e9:.2f} GB of weights per step)", "peaks": pk_src},
+        "e2e": {"value": round(n_out / total_s, 1), "unit": "tokens/s", "with_prompts": round((n_out + sum(lengths)) / total_s, 1),
+                "total_s": round(total_s, 3)},
+        "mixed_steps": {"n": len(mixed), "median_ms": round(statistics.median(s[0] for s in mixed), 3) if mixed else None,
+                        "median_tflops": round(statistics.median(f / (s[0] / 1e3) / 1e12 for f, s in zip(mixed_flops, mixed)), 1)
+                        if mixed else None},
+        "decode_steps": {"n": len(dec), "median_ms": round(dec_ms, 3) if dec_ms else None, "rows": n_req},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1) if achieved else None, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4) if achieved else None,
+                     "of": "decode-only steps of all 32 requests (median wall time between returns of Engine.step)"},
+        "clocks": clk,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def cpu_baseline():
+    """The plain float32 implementation of the test-suite (tests/plain_llama.py: torch on the CPU,
+    the whole sequence recomputed for every token, no cache) timed as the CPU baseline: greedy
+    tokens per second on tiny A, tiny B and the two-layer model of Llama-3.2-1B's layer sizes.
+    The reference's own CPU path (candle, Q4_K weights, with a cache) cannot be built here."""
+    import platform
+    import tempfile
+    from pathlib import Path
+
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_llama as P
+    from configs import TINY, make_model_dir, random_prompt
+    from zllm_b200 import LlamaConfig
+    from zllm_b200.weights import write_random_model
+
+    cpu = platform.processor() or platform.machine()
+    try:
+        with open("/proc/cpuinfo") as f:
+            cpu = next((l.split(":", 1)[1].strip() for l in f if l.startswith("model name")), cpu)
+    except OSError:
+        pass
+    out = {"impl": "plain CPU implementation (tests/plain_llama.py)", "cpu": cpu, "threads": torch.get_num_threads(),
+           "unit": "tokens/s", "results": {}}
+    with tempfile.TemporaryDirectory() as tmp:
+        cases = [("tiny A", make_model_dir(Path(tmp), "A"), 33, 16), ("tiny B", make_model_dir(Path(tmp), "B"), 33, 16)]
+        big = Path(tmp) / "1b2"
+        write_random_model(big, LlamaConfig.from_dict(dict(MODEL, num_hidden_layers=2, max_position_embeddings=4096)), 2,
+                           "float32", std=0.02)
+        cases.append(("Llama-3.2-1B layer sizes, 2 of 16 layers", big, 32, 8))
+        for name, d, n_prompt, n_new in cases:
+            cfg, w = P.read_model_dir(d)
+            prompt = random_prompt(cfg["vocab_size"], n_prompt, 1)
+            P.greedy_generate(cfg, w, prompt, 1)
+            t = time.perf_counter()
+            P.greedy_generate(cfg, w, prompt, n_new)
+            dt = time.perf_counter() - t
+            out["results"][name] = {"prompt": n_prompt, "new_tokens": n_new, "tokens_per_s": round(n_new / dt, 2)}
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -183,6 +313,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--config", default="1b", choices=("1b", "8b", "3b-mixed", "cpu-baseline"),
+                    help="which of the configurations the numbers are quoted on (default: the 1B headline)")
     ap.add_argument("--case", default=None, choices=("decode", "prefill"),
                     help="run only a small case for a profiler: a few decode steps without graphs, or one prefill")
     ap.add_argument("--context", type=int, default=1024, help="--case decode: cached positions per request")
@@ -191,6 +323,8 @@ def main():
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="--case: layer sizes of another Llama shape")
     args = ap.parse_args()
 
+    if args.config == "cpu-baseline":
+        return cpu_baseline()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "fankh/zllm is a Rust crate (candle, wgpu, ash): no Rust "
                           "toolchain and no crates offline, so it cannot be installed; its GPU paths need Vulkan or "
@@ -207,15 +341,21 @@ def main():
 
     if args.case:
         return profile_case(args)
+    if args.config == "3b-mixed":
+        return mixed_workload(args, K, W)
 
     pk, pk_src = peaks()
-    cfg = LlamaConfig.from_dict(MODEL)
+    big = args.config == "8b"
+    CONTEXT = 8192 if big else 4096
+    shape_name = "Llama-3.1-8B-shaped" if big else "Llama-3.2-1B-shaped"
+    seed = 4 if big else 2
+    cfg = LlamaConfig.from_dict(dict(MODEL, **SHAPES[args.config]))
     weight_bytes, kv_per_token, prefill_flops = model_numbers(cfg)
     dev = torch.device("cuda:0")
     max_b = max(64, args.batch)
     n_blocks = max_b * (CONTEXT // BLOCK) + 64
     t0 = time.time()
-    eng = Engine(config=cfg, seed=2, random_on_device=True, engine_config=EngineConfig(
+    eng = Engine(config=cfg, seed=seed, random_on_device=True, engine_config=EngineConfig(
         dtype="bfloat16", block_size=BLOCK, num_blocks=n_blocks, max_num_seqs=max_b, max_num_batched_tokens=PROMPT,
         max_model_len=CONTEXT + 8))
     runner = eng.runner
@@ -275,19 +415,35 @@ def main():
         eng.add_request(prompt(CONTEXT - K - W - slack - 2), SamplingParams.greedy(max_tokens=K + W + slack))
     while eng.scheduler.prefilling or eng.scheduler.waiting:
         eng.step()
-    for _ in range(W):
+    def timed_engine_steps():
+        """K steps of ``Engine.step()`` by the wall clock; (tokens/s, host-to-device bytes per step).
+        The bytes are counted where they are copied (step buffers and block-table rows)."""
+        from zllm_b200.engine.batch import StepBuffers
+        for _ in range(W):
+            eng.step()
+        torch.cuda.synchronize()
+        up0 = StepBuffers.bytes_uploaded + runner.cache.table_bytes_uploaded
+        t1 = time.perf_counter()
+        n = 0
+        for _ in range(K):
+            n += len(eng.step())
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t1
+        up = StepBuffers.bytes_uploaded + runner.cache.table_bytes_uploaded - up0
+        while eng.has_unfinished():
+            eng.step()
+        return n / dt, up / K
+
+    e2e_tps, h2d = timed_engine_steps()
+    # the same with every step scheduled by the host (no decode step launched ahead): each step
+    # then uploads its tokens, positions and slots from pinned memory before it runs
+    for i in range(B):
+        eng.add_request(prompt(CONTEXT - K - W - slack - 2), SamplingParams.greedy(max_tokens=K + W + slack))
+    while eng.scheduler.prefilling or eng.scheduler.waiting:
         eng.step()
-    torch.cuda.synchronize()
-    t1 = time.perf_counter()
-    n_tok = 0
-    for _ in range(K):
-        n_tok += len(eng.step())
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t1
-    g8 = next(g for k, g in runner._graphs.items() if k[0] == 8) if B == 8 else None
-    h2d = (g8["buf"].total * 4) if g8 else None
-    while eng.has_unfinished():
-        eng.step()
+    eng.overlap = False
+    strict_tps, strict_h2d = timed_engine_steps()
+    eng.overlap = True
 
     # ---- the same with top-k / top-p sampling (the draw among the candidates runs on the device) -------
     for i in range(B):
@@ -295,17 +451,7 @@ def main():
                         SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=i, max_tokens=K + W + slack))
     while eng.scheduler.prefilling or eng.scheduler.waiting:
         eng.step()
-    for _ in range(W):
-        eng.step()
-    torch.cuda.synchronize()
-    t1 = time.perf_counter()
-    n_tok_p = 0
-    for _ in range(K):
-        n_tok_p += len(eng.step())
-    torch.cuda.synchronize()
-    topp_s = time.perf_counter() - t1
-    while eng.has_unfinished():
-        eng.step()
+    topp_tps, _ = timed_engine_steps()
 
     # ---- prefill of 2,048 tokens ------------------------------------------------------------
     s = runner.admit()
@@ -326,26 +472,31 @@ def main():
     clk = clocks.stop()
 
     line = {
-        "metric": "decode tok/s, Llama-3.2-1B shape, bf16, batch 8, context 4096 (random weights)",
+        "metric": f"decode tok/s, {shape_name.replace('-shaped', '')} shape, bf16, batch {B}, context {CONTEXT} (random weights)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights N(0,0.02) seed 2)",
+        "dtype": "bf16", "data": f"synthetic (uniform random token ids, random weights N(0,0.02) seed {seed})",
         "impl": "ours",
-        "config": {"model": "Llama-3.2-1B-shaped", "layers": cfg.num_hidden_layers, "layers_full": 16,
+        "config": {"model": shape_name, "layers": cfg.num_hidden_layers, "layers_full": cfg.num_hidden_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "tied": True, "global_batch": B, "seq_len": CONTEXT, "prompt_len": PROMPT, "kv_block": BLOCK,
-                   "parallelism": "single GPU", "l2": "inputs larger than L2 (2.47 GB of weights per step)",
-                   "peaks": pk_src},
-        "e2e": {"value": round(n_tok / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": 4 * B},
+                   "tied": bool(cfg.tie_word_embeddings), "global_batch": B, "seq_len": CONTEXT, "prompt_len": PROMPT,
+                   "kv_block": BLOCK, "parallelism": "single GPU",
+                   "l2": f"inputs larger than L2 ({weight_bytes / 1e9:.2f} GB of weights per step)", "peaks": pk_src},
+        # through Engine.step(): while only decoding, the step after the one being read is launched
+        # ahead with inputs advanced on the device (an autoregressive step's input IS the last
+        # step's output), so a steady-state step copies nothing up; "scheduled" is the same with
+        # every step's tokens, positions and slots uploaded from pinned memory before it runs
+        "e2e": {"value": round(e2e_tps, 1), "unit": "tokens/s", "h2d_bytes_per_step": round(h2d, 1),
+                "d2h_bytes_per_step": 4 * B, "scheduled": {"value": round(strict_tps, 1),
+                                                           "h2d_bytes_per_step": round(strict_h2d, 1)}},
         "gpu_launches": launches,
         "prefill": {"value": round(PROMPT / (pf_ms / 1e3), 1), "tokens": PROMPT, "ms": round(pf_ms, 3),
                     "frac": round(flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": {"decode_b1": round(b1, 1), "decode_b64": round(b64, 1),
-                   "decode_b8_top_p_e2e": round(n_tok_p / topp_s, 1),
+                   f"decode_b{B}_top_p_e2e": round(topp_tps, 1),
                    "decode_b64_hbm_frac": round((weight_bytes + 64 * ctx64 * kv_per_token) / (ms64 / 1e3) / 1e9 / pk["hbm_gbs"], 4)},
         "clocks": clk,
     }

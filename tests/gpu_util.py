@@ -16,7 +16,13 @@ DEV = "cuda:0"
 # fault that doubles the error of a single position shows.  BF16_MAX_OF_SCALE is the ceiling
 # that no configuration may exceed and the bound of configurations without an entry.
 BF16_MAX_OF_SCALE = 0.04
-BF16_OF_SCALE = {}
+# observed over the suite at the configurations' own weight scales: A 0.0017, B 0.0067, C 0.0071,
+# D 0.0075, E 0.0064, the 1B layer sizes 0.0096
+BF16_OF_SCALE = {"A": 0.0035, "B": 0.0135, "C": 0.0145, "D": 0.015, "E": 0.013, "1B layers": 0.02}
+# Token streams at the sharper weights of ``configs.GEN_STD``: a greedy choice may flip when the
+# two best plain logits are closer than the sum of their errors.  The largest gap of a flipped
+# choice observed over the suite is 0.9 % of the largest logit; twice that counts as a near-tie.
+BF16_GAP_OF_SCALE = 0.02
 F32_ATOL = 1e-4
 
 OBSERVED = {}            # what -> (worst error / scale, bound / scale)
@@ -56,7 +62,7 @@ def check_greedy_stream(forward, prompt, got, dtype, max_tokens, stop=(), gap_of
         assert dtype != "float32", f"{what}: token {i} is {t}, plain says {best}"
         gap = float(row[best] - row[t])
         scale = float(row.abs().max())
-        lim = (gap_of_scale if gap_of_scale is not None else bf16_bound()) * scale
+        lim = (gap_of_scale if gap_of_scale is not None else BF16_GAP_OF_SCALE) * scale
         observe(f"near-tie gap {what}", gap, scale, lim / scale)
         assert gap <= lim, f"{what}: token {i} is {t} (plain {best}), gap {gap:.3e} > {lim:.3e}"
 

@@ -10,8 +10,8 @@ pytestmark = pytest.mark.gpu
 
 import plain_llama as P
 import traces as TR
-from configs import TINY, make_model_dir, random_prompt
-from gpu_util import bf16_bound, check_greedy_stream, observe
+from configs import GEN_STD, TINY, make_model_dir, random_prompt
+from gpu_util import BF16_GAP_OF_SCALE, bf16_bound, check_greedy_stream, observe
 from zllm_b200 import Engine, EngineConfig, ModelRunner, SamplingParams, Session, StepEntry
 
 
@@ -49,15 +49,15 @@ def check_gumbel_stream(cfg, w, prompt, got, temperature, seed, dtype, name, wha
         assert dtype != "float32", f"{what}: token {n} is {t}, plain samples {best}"
         gap = float(sc[best] - sc[t]) * temperature
         scale = float(lg[n].abs().max())
-        observe(f"near-tie gap {what}", gap, scale, bf16_bound(name))
-        assert gap <= bf16_bound(name) * scale, f"{what}: token {n}: gap {gap:.3e}"
+        observe(f"near-tie gap {what}", gap, scale, BF16_GAP_OF_SCALE)
+        assert gap <= BF16_GAP_OF_SCALE * scale, f"{what}: token {n}: gap {gap:.3e}"
 
 
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_matches_plain(tmp_path, name, dtype):
     """Sharper logits (larger weights) so that greedy choices are not rounding ties."""
-    d = make_model_dir(tmp_path, name, dtype, std={"C": 0.12, "D": 0.15, "E": 0.15}.get(name, 0.3))
+    d = make_model_dir(tmp_path, name, dtype, std=GEN_STD[name])
     cfg, w = P.read_model_dir(d)
     V = cfg["vocab_size"]
     prompts = [random_prompt(V, n, 50 + n) for n in (5, 17, 33)]
@@ -70,14 +70,13 @@ def test_greedy_generation_matches_plain(tmp_path, name, dtype):
             assert out == want
         for o, p in zip(out, prompts):
             # every token is the plain argmax given the stream so far; bfloat16 may take a near-tie
-            check_greedy_stream(plain_forward(cfg, w), p, o, dtype, 16, gap_of_scale=bf16_bound(name),
-                                what=f"tiny {name} greedy")
+            check_greedy_stream(plain_forward(cfg, w), p, o, dtype, 16, what=f"tiny {name} greedy")
         assert eng.stats()["free_pages"] == [nb * 16 // TINY[name][1]]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_temperature_and_topk_sampling(tmp_path, dtype):
-    d = make_model_dir(tmp_path, "B", dtype, std=0.2)
+    d = make_model_dir(tmp_path, "B", dtype, std=GEN_STD["B"])
     prompts = [random_prompt(1000, n, 70 + n) for n in (3, 30, 12, 40)]
     params = [SamplingParams.with_temperature(0.8, seed=100 + i, max_tokens=24) for i in range(3)]
     params.append(SamplingParams(temperature=0.9, top_k=5, top_p=0.9, seed=7, max_tokens=24))
@@ -184,7 +183,7 @@ def test_many_requests_through_few_slots_and_few_pages(tmp_path, dtype):
     run in turn between mixed steps.  float32: every stream must be the plain implementation's;
     bfloat16: every token the plain argmax given its own stream, or a near-tie."""
     import random
-    d = make_model_dir(tmp_path, "B", dtype, std=0.3)
+    d = make_model_dir(tmp_path, "B", dtype, std=GEN_STD["B"])
     cfg, w = P.read_model_dir(d)
     V = cfg["vocab_size"]
     rng = random.Random(5)
@@ -206,8 +205,7 @@ def test_many_requests_through_few_slots_and_few_pages(tmp_path, dtype):
     if dtype == "float32":
         assert [got[i] for i in ids] == want
     for i, p, n in zip(ids, prompts, lens):
-        check_greedy_stream(plain_forward(cfg, w), p, got[i], dtype, n, gap_of_scale=bf16_bound("B"),
-                            what="tiny B many requests")
+        check_greedy_stream(plain_forward(cfg, w), p, got[i], dtype, n, what="tiny B many requests")
     st = eng.stats()
     assert st["preemptions"] > 0 and st["free_slots"] == 5 and st["free_pages"] == [-(-150 // bs)]
     eng.runner.ops.check_async_errors()
@@ -219,7 +217,7 @@ def test_prefix_sharing_gives_the_same_tokens_with_fewer_positions_computed(tmp_
     (several at once, one after another, and after the pages' first owner is gone); so few pages
     that registered pages are reclaimed in between.  The tokens are the plain implementation's."""
     name = "B"
-    d = make_model_dir(tmp_path, name, dtype, std=0.3)
+    d = make_model_dir(tmp_path, name, dtype, std=GEN_STD[name])
     cfg, w = P.read_model_dir(d)
     V = cfg["vocab_size"]
     bs = TINY[name][1]
@@ -250,8 +248,7 @@ def test_prefix_sharing_gives_the_same_tokens_with_fewer_positions_computed(tmp_
         if dtype == "float32":
             return got == want
         for g, p, n in zip(got, prompts, lens):
-            check_greedy_stream(plain_forward(cfg, w), p, g, dtype, n, gap_of_scale=bf16_bound(name),
-                                what="tiny B prefix sharing")
+            check_greedy_stream(plain_forward(cfg, w), p, g, dtype, n, what="tiny B prefix sharing")
         return True
 
     out, st = run(True, 40)

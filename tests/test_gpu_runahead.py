@@ -9,15 +9,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 import plain_llama as P
-from configs import TINY, make_model_dir, random_prompt
-from gpu_util import bf16_bound, check_greedy_stream
+from configs import GEN_STD, TINY, make_model_dir, random_prompt
+from gpu_util import check_greedy_stream
 from zllm_b200 import Engine, SamplingParams
 
-STD = {"C": 0.12, "D": 0.15}
-
-
 def setup(tmp_path, name, dtype, slots=4):
-    d = make_model_dir(tmp_path, name, dtype, std=STD[name])
+    d = make_model_dir(tmp_path, name, dtype, std=GEN_STD[name])
     cfg, w = P.read_model_dir(d)
     bs = TINY[name][1]
     eng = Engine(str(d), dtype=dtype, block_size=bs, num_blocks=slots * (256 // bs), max_num_seqs=slots,
@@ -55,7 +52,7 @@ def test_a_stop_token_ends_one_of_four_requests_while_a_step_is_in_flight(tmp_pa
     # the engine's own streams without a stop token (checked against plain), to pick the stop from
     free_run = eng.generate(prompts, SamplingParams.greedy(max_tokens=N))
     for p, o in zip(prompts, free_run):
-        check_greedy_stream(fwd, p, o, dtype, N, gap_of_scale=bf16_bound(name), what=f"tiny {name} run-ahead")
+        check_greedy_stream(fwd, p, o, dtype, N, what=f"tiny {name} run-ahead")
     if dtype == "float32":
         assert free_run == [P.greedy_generate(cfg, w, p, N) for p in prompts]
     # a token of request 1's stream that appears first at a step in the middle, not the last
@@ -69,8 +66,7 @@ def test_a_stop_token_ends_one_of_four_requests_while_a_step_is_in_flight(tmp_pa
     assert ahead, "the engine never ran ahead: the test did not exercise what it is for"
     assert got[ids[1]] == free_run[1][:k + 1]            # the stop token is emitted, nothing after it
     for i in (0, 2, 3):                                   # the others do not notice
-        check_greedy_stream(fwd, prompts[i], got[ids[i]], dtype, N, gap_of_scale=bf16_bound(name),
-                            what=f"tiny {name} run-ahead")
+        check_greedy_stream(fwd, prompts[i], got[ids[i]], dtype, N, what=f"tiny {name} run-ahead")
         if dtype == "float32":
             assert got[ids[i]] == free_run[i]
     assert eng.scheduler.requests[ids[1]].finish_reason == "stop"
@@ -101,10 +97,9 @@ def test_cancel_between_steps_then_a_new_request_in_the_freed_slot(tmp_path, nam
     assert len(got[victim]) == produced                    # nothing was reported for it after the cancel
     for i, p in zip(ids, prompts):
         if i != victim:
-            check_greedy_stream(fwd, p, got[i], dtype, N, gap_of_scale=bf16_bound(name), what=f"tiny {name} cancel")
-    check_greedy_stream(fwd, prompts[2], got[victim], dtype, produced, gap_of_scale=bf16_bound(name),
-                        what=f"tiny {name} cancel")
-    check_greedy_stream(fwd, newcomer, got[nid], dtype, N, gap_of_scale=bf16_bound(name), what=f"tiny {name} cancel")
+            check_greedy_stream(fwd, p, got[i], dtype, N, what=f"tiny {name} cancel")
+    check_greedy_stream(fwd, prompts[2], got[victim], dtype, produced, what=f"tiny {name} cancel")
+    check_greedy_stream(fwd, newcomer, got[nid], dtype, N, what=f"tiny {name} cancel")
     if dtype == "float32":
         assert got[nid] == P.greedy_generate(cfg, w, newcomer, N)
     assert slot is not None and all_free(eng)
@@ -128,8 +123,7 @@ def test_a_request_stops_while_another_is_admitted(tmp_path, dtype):
     drain(eng, got)
     assert got[ids[0]] == free_run[0][:k + 1]
     for i in (1, 2):
-        check_greedy_stream(fwd, prompts[i], got[ids[i]], dtype, N, gap_of_scale=bf16_bound(name),
-                            what=f"tiny {name} stop and admit")
+        check_greedy_stream(fwd, prompts[i], got[ids[i]], dtype, N, what=f"tiny {name} stop and admit")
     if dtype == "float32":
         assert got[ids[2]] == P.greedy_generate(cfg, w, prompts[2], N)
     assert all_free(eng, slots=2)

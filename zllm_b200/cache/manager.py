@@ -432,6 +432,8 @@ class CacheManager:
         if nb > done:
             self._hashed[slot] = (nb, h)
 
+    table_bytes_uploaded = 0        # host-to-device bytes of block-table rows so far (for measurement)
+
     def sync_tables(self) -> None:
         """Copy the table rows that changed since the last call to the device."""
         for g in self.groups:
@@ -440,6 +442,7 @@ class CacheManager:
                 continue
             for slot in sorted(g.dirty):
                 g.table_dev[slot].copy_(g.table_pinned[slot], non_blocking=True)
+                self.table_bytes_uploaded += g.table_pinned[slot].numel() * 4
             g.dirty.clear()
 
     # ---- integrity ------------------------------------------------------

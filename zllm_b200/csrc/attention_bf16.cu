@@ -274,10 +274,10 @@ __device__ __forceinline__ void attend_block(const unsigned (&qf)[MT][HD / 16][4
 // ------------------------------------------------------------------------------------ decode
 template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32) decode_split_kernel(
-    const bf16* __restrict__ qkv, const int* __restrict__ rows, const int* __restrict__ positions,
-    const int* __restrict__ row_slot, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+    const bf16* qkv, const int* rows, const int* positions,
+    const int* row_slot, const bf16* k_pages, const bf16* v_pages,
     const int* __restrict__ table, int max_blocks, int bs, int bs_shift, int nq, int nkv, float scale, int window,
-    float* __restrict__ part_o, float* __restrict__ part_ml, int max_splits) {
+    float* part_o, float* part_ml, int max_splits) {
     constexpr int STR = HD + 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // What this block needs that the kernel before it (the QKV product of this step) does not
@@ -484,8 +484,8 @@ ZLLM_API int zllm_attention_decode_bf16(const void* qkv, void* out, const int* r
 // (the accumulators of two tiles would not fit the registers).
 template <int HD, int MT, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32, MT == 2 ? 2 : 1) prefill_kernel(
-    const bf16* __restrict__ qkv, bf16* __restrict__ out, const int* __restrict__ tiles,
-    const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages, const int* __restrict__ table,
+    const bf16* qkv, bf16* out, const int* __restrict__ tiles,
+    const bf16* k_pages, const bf16* v_pages, const int* __restrict__ table,
     int max_blocks, int bs, int bs_shift, int nq, int nkv, float scale, int window) {
     static_assert(MT * NWARPS * 16 == PF_QROWS, "the warps' tiles must cover the query tile");
     constexpr int STR = HD + 8;

@@ -48,8 +48,8 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 #define COMBINE_THREADS 256
 template <int HD, int NTHR>
 __global__ void __launch_bounds__(NTHR) decode_combine_kernel(
-    const int* __restrict__ rows, const int* __restrict__ positions, const int* __restrict__ row_slot,
-    const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int window,
+    const int* rows, const int* positions, const int* row_slot,
+    const float* part_o, const float* part_ml, bf16* out, int nq, int window,
     int max_splits, int n_splits) {
     constexpr int nthr = NTHR, G = NTHR / HD;                // groups of HD threads (at least one)
     __shared__ float s_red[NTHR / 32];

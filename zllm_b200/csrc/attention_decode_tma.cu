@@ -69,11 +69,11 @@ __device__ __forceinline__ unsigned movmatrix_trans(unsigned a) {
 template <int HD, bool BIG, bool DIRECT>
 __global__ void __launch_bounds__(DEC_WARPS * 32) decode_tma_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-    const bf16* __restrict__ qkv, const int* __restrict__ rows, const int* __restrict__ positions,
-    const int* __restrict__ row_slot, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+    const bf16* qkv, const int* rows, const int* positions,
+    const int* row_slot, const bf16* k_pages, const bf16* v_pages,
     const int* __restrict__ table, int max_blocks, int bs, int bs_shift,
-    int box_rows, int nq, int nkv, float scale, float* __restrict__ part_o, float* __restrict__ part_ml,
-    int max_splits, bf16* __restrict__ out) {
+    int box_rows, int nq, int nkv, float scale, float* part_o, float* part_ml,
+    int max_splits, bf16* out) {
     constexpr int NB = HD <= 64 ? 64 : 32;                   // keys per warp iteration
     constexpr int NIT = (SPLIT_KEYS / DEC_WARPS) / NB;       // iterations per warp
     constexpr int HALVES = HD / 64;                          // 128-byte column boxes per row

@@ -19,8 +19,8 @@
 
 template <typename AT>
 __global__ void __launch_bounds__(128) attention_plain_kernel(
-    const AT* __restrict__ qkv, AT* __restrict__ out, const int* __restrict__ positions,
-    const int* __restrict__ row_slot, const AT* __restrict__ k_pages, const AT* __restrict__ v_pages,
+    const AT* qkv, AT* out, const int* positions,
+    const int* row_slot, const AT* k_pages, const AT* v_pages,
     const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, int hd, float scale, int window) {
     __shared__ float qs[4][MAX_HD];
     const int t = blockIdx.x;

@@ -137,7 +137,7 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 template <int HD, int NSB, int NPB, int NS, int CTAS>
 __global__ void __launch_bounds__(PT_THREADS, CTAS) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-    const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ tiles,
+    const __grid_constant__ CUtensorMap map_v, bf16* out, const int* __restrict__ tiles,
     const int* __restrict__ table, int max_blocks, int bs, int bs_shift, int box_rows, int nq, int nkv, float scale) {
     constexpr int HALVES = HD / 64;                          // 64-element column boxes of a row
     constexpr int QHALF = PT_ROWS * 128;                     // [128 rows][64 elements], swizzled (Q, P)

@@ -56,14 +56,39 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 // predecessor (fetching weights), and only then waits for the predecessor's results
 // (pdl_wait).  EVERY kernel launched through launch_pdl must call pdl_wait() before it reads
 // or writes anything another kernel of the step touches.
+// A pointer to such data must not be declared ``const T* __restrict__``: that promises the
+// compiler that nobody writes the data while the kernel runs, so it may read it through the
+// read-only path and move the loads to wherever it likes -- also above the wait, where the
+// kernel before has not written them yet (seen with head size 80: the decode attention read
+// the previous layer's q).  Only what no kernel of a step writes (weights, rotary tables,
+// block tables, tile lists) keeps the qualifier.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <stdlib.h>
-// ZLLM_NO_PDL=1 launches every kernel fully serialized (for measuring what the overlap buys)
+#include <string.h>
+// ZLLM_NO_PDL=1 launches every kernel fully serialized (for measuring what the overlap buys);
+// ZLLM_NO_PDL=gemm_decode,attention_bf16 only the kernels of the source files named.
 static inline bool pdl_enabled() {
     static int v = -1;
-    if (v < 0) { const char* e = getenv("ZLLM_NO_PDL"); v = (e && e[0] == '1') ? 0 : 1; }
+    if (v < 0) {
+        const char* e = getenv("ZLLM_NO_PDL");
+        v = 1;
+        if (e && e[0] == '1') v = 0;
+        else if (e && e[0]) {
+            const char* base = strrchr(__BASE_FILE__, '/');
+            base = base ? base + 1 : __BASE_FILE__;
+            char name[128];
+            size_t n = strcspn(base, ".");
+            if (n >= sizeof(name)) n = sizeof(name) - 1;
+            memcpy(name, base, n);
+            name[n] = 0;
+            for (const char* q = e; (q = strstr(q, name)) != nullptr; q += n) {
+                const char after = q[n];
+                if ((q == e || q[-1] == ',') && (after == 0 || after == ',')) { v = 0; break; }
+            }
+        }
+    }
     return v == 1;
 }
 

@@ -10,7 +10,7 @@
 
 // ---------------------------------------------------------------- embedding
 template <typename WT>
-__global__ void embedding_kernel(const int* __restrict__ tok, const WT* __restrict__ table, float* __restrict__ out,
+__global__ void embedding_kernel(const int* tok, const WT* __restrict__ table, float* out,
                                  int H, int V) {
     pdl_trigger();
     pdl_wait();
@@ -36,7 +36,7 @@ ZLLM_API int zllm_embedding(const int* tok, const void* table, float* out, int T
 // ---------------------------------------------------------------- rmsnorm
 // y = x * rsqrt(mean(x^2) + eps) * w ; x float32 [T,H]; w float32 or bf16; y AT.
 template <typename WT, typename OT>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict__ w, OT* __restrict__ y, int H,
+__global__ void rmsnorm_kernel(const float* x, const WT* __restrict__ w, OT* y, int H,
                                float eps) {
     __shared__ float red[33];
     pdl_trigger();
@@ -52,8 +52,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const WT* __restrict
 
 // The same with 16-byte loads and the row kept in registers (H % 4 == 0, H <= 256 * 4 * RV).
 template <typename WT, typename OT, int RV>
-__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const WT* __restrict__ w,
-                                                          OT* __restrict__ y, int H, float eps) {
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* x, const WT* __restrict__ w,
+                                                          OT* y, int H, float eps) {
     __shared__ float red[33];
     pdl_trigger();
     pdl_wait();
@@ -112,7 +112,7 @@ ZLLM_API int zllm_rmsnorm(const float* x, const void* w, void* y, int T, int H, 
 
 // ---------------------------------------------------------------- silu * up
 template <typename AT>
-__global__ void silu_mul_kernel(const AT* __restrict__ g, const AT* __restrict__ u, AT* __restrict__ o, size_t n) {
+__global__ void silu_mul_kernel(const AT* g, const AT* u, AT* o, size_t n) {
     pdl_trigger();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -131,7 +131,7 @@ ZLLM_API int zllm_silu_mul(const void* g, const void* u, void* o, long long n, i
 }
 
 // ---------------------------------------------------------------- gather rows (float32)
-__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, float* __restrict__ out,
+__global__ void gather_rows_kernel(const float* x, const int* rows, float* out,
                                    int H) {
     pdl_trigger();
     pdl_wait();
@@ -152,10 +152,10 @@ ZLLM_API int zllm_gather_rows(const float* x, const int* rows, float* out, int R
 //   page = table[slot * max_blocks + pos / bs];  element [page][kv head][pos % bs][d].
 // cos/sin: [max_pos, rot_dim/2] float32 tables of pos * theta_j (null: no rotation).
 template <typename AT>
-__global__ void rope_kv_store_kernel(AT* __restrict__ qkv, const int* __restrict__ positions,
-                                     const int* __restrict__ row_slot, const float* __restrict__ cos_t,
+__global__ void rope_kv_store_kernel(AT* qkv, const int* positions,
+                                     const int* row_slot, const float* __restrict__ cos_t,
                                      const float* __restrict__ sin_t, int rot_dim, int interleaved,
-                                     AT* __restrict__ k_pages, AT* __restrict__ v_pages,
+                                     AT* k_pages, AT* v_pages,
                                      const int* __restrict__ table, int max_blocks, int bs, int nq, int nkv, int hd,
                                      int store) {
     pdl_trigger();
@@ -198,11 +198,11 @@ __global__ void rope_kv_store_kernel(AT* __restrict__ qkv, const int* __restrict
 
 // bfloat16, half-split pairing over the whole head, head_dim % 16 == 0: 16-byte accesses.
 // One thread rotates 8 pairs (j..j+7, j+half..j+half+7) of one head, or copies 8 values of v.
-__global__ void __launch_bounds__(256) rope_kv_store_vec_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions,
-                                                                const int* __restrict__ row_slot,
+__global__ void __launch_bounds__(256) rope_kv_store_vec_kernel(bf16* qkv, const int* positions,
+                                                                const int* row_slot,
                                                                 const float* __restrict__ cos_t,
                                                                 const float* __restrict__ sin_t,
-                                                                bf16* __restrict__ k_pages, bf16* __restrict__ v_pages,
+                                                                bf16* k_pages, bf16* v_pages,
                                                                 const int* __restrict__ table, int max_blocks, int bs,
                                                                 int nq, int nkv, int hd, int store) {
     pdl_trigger();

@@ -24,8 +24,8 @@
 #define BK 16
 
 template <typename AT, typename OT, int MODE>
-__global__ void __launch_bounds__(256) gemm_plain_kernel(const AT* __restrict__ x, const AT* __restrict__ w,
-                                                         OT* __restrict__ out, int M, int N, int K) {
+__global__ void __launch_bounds__(256) gemm_plain_kernel(const AT* x, const AT* __restrict__ w,
+                                                         OT* out, int M, int N, int K) {
     // N counts output columns (for SWIGLU: the intermediate size I, W has 2I rows)
     __shared__ float xs[BK][BM + 1];
     __shared__ float ws[BK][BN + 1];

@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
 
 // Second pass of a product whose K was split: out = epilogue(sum over the slices, in slice order).
 // part [splits][M][w_rows] float32; a thread takes 4 consecutive outputs.
-__global__ void gemm_tc_reduce_kernel(const float* __restrict__ part, int splits, int M, int w_rows, void* __restrict__ out,
+__global__ void gemm_tc_reduce_kernel(const float* part, int splits, int M, int w_rows, void* out,
                                       int N, int mode, int out_bf16) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int n4 = N / 4;

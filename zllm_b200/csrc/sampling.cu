@@ -27,10 +27,10 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 #define SAMPLE_THREADS 1024
 
 // one block per row; out[row] = sampled token
-__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __restrict__ logits,
-                                                                const float* __restrict__ temps,
-                                                                const unsigned* __restrict__ seeds,
-                                                                int* __restrict__ out, int V) {
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* logits,
+                                                                const float* temps,
+                                                                const unsigned* seeds,
+                                                                int* out, int V) {
     __shared__ float sv[32];
     __shared__ int si[32];
     pdl_trigger();
@@ -76,11 +76,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const float* __r
 // memory) picks the best of the chunks and resets the counter.  "Best" is the largest value,
 // the lowest index among equals, which does not depend on the order of arrival.
 #define SAMPLE_CHUNKS 64
-__global__ void __launch_bounds__(256) sample_chunks_kernel(const float* __restrict__ logits,
-                                                            const float* __restrict__ temps,
-                                                            const unsigned* __restrict__ seeds, int* __restrict__ out,
-                                                            int V, float* __restrict__ part_v, int* __restrict__ part_i,
-                                                            unsigned* __restrict__ counters) {
+__global__ void __launch_bounds__(256) sample_chunks_kernel(const float* logits,
+                                                            const float* temps,
+                                                            const unsigned* seeds, int* out,
+                                                            int V, float* part_v, int* part_i,
+                                                            unsigned* counters) {
     __shared__ float sv[8];
     __shared__ int si[8];
     __shared__ bool last;
@@ -212,8 +212,8 @@ __device__ __forceinline__ void topk_select(const float* __restrict__ cv, const 
 }
 
 // the whole row in one block (any number of rows)
-__global__ void __launch_bounds__(SAMPLE_THREADS) topk_kernel(const float* __restrict__ logits, float* __restrict__ vals,
-                                                              int* __restrict__ idxs, int V, int k) {
+__global__ void __launch_bounds__(SAMPLE_THREADS) topk_kernel(const float* logits, float* vals,
+                                                              int* idxs, int V, int k) {
     pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x;
@@ -281,7 +281,7 @@ __device__ __forceinline__ void warp_topk(const float (&cv)[TOPK_E], const int (
 }
 
 // (1) grid (R, TOPK_GROUPS): the maximum of each group of the row
-__global__ void __launch_bounds__(256) topk_groupmax_kernel(const float* __restrict__ logits, float* __restrict__ gmax, int V) {
+__global__ void __launch_bounds__(256) topk_groupmax_kernel(const float* logits, float* gmax, int V) {
     __shared__ float sm[8];
     pdl_trigger();
     pdl_wait();
@@ -301,8 +301,8 @@ __global__ void __launch_bounds__(256) topk_groupmax_kernel(const float* __restr
     }
 }
 // (2) grid (R, TOPK_STRETCHES / 8), 8 warps per block, a stretch per warp
-__global__ void __launch_bounds__(256) topk_stretch_kernel(const float* __restrict__ logits, const float* __restrict__ gmax,
-                                                           float* __restrict__ cand_v, int* __restrict__ cand_i, int V, int k) {
+__global__ void __launch_bounds__(256) topk_stretch_kernel(const float* logits, const float* gmax,
+                                                           float* cand_v, int* cand_i, int V, int k) {
     pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -324,8 +324,8 @@ __global__ void __launch_bounds__(256) topk_stretch_kernel(const float* __restri
     warp_topk(cv, ci, cand_v + o, cand_i + o, k, topk_mono(fl));
 }
 // (3a) grid (R, 4), 8 warps per block: 256 lists -> 32 lists, a warp takes 8 lists (8 k <= 512 slots)
-__global__ void __launch_bounds__(256) topk_merge1_kernel(const float* __restrict__ cand_v, const int* __restrict__ cand_i,
-                                                          float* __restrict__ m1_v, int* __restrict__ m1_i, int k) {
+__global__ void __launch_bounds__(256) topk_merge1_kernel(const float* cand_v, const int* cand_i,
+                                                          float* m1_v, int* m1_i, int k) {
     pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x, warp = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -343,8 +343,8 @@ __global__ void __launch_bounds__(256) topk_merge1_kernel(const float* __restric
     warp_topk(cv, ci, m1_v + dst, m1_i + dst, k, 0u);
 }
 // (3b) grid (R), 4 warps: 32 lists -> 4 lists -> the row's k best
-__global__ void __launch_bounds__(128) topk_merge2_kernel(const float* __restrict__ m1_v, const int* __restrict__ m1_i,
-                                                          float* __restrict__ vals, int* __restrict__ idxs, int k) {
+__global__ void __launch_bounds__(128) topk_merge2_kernel(const float* m1_v, const int* m1_i,
+                                                          float* vals, int* idxs, int k) {
     __shared__ float tv[4 * 64];
     __shared__ int ti[4 * 64];
     pdl_trigger();
@@ -410,9 +410,9 @@ __device__ __forceinline__ double splitmix01(unsigned seed) {
     z ^= z >> 31;
     return ((double)(z >> 40) + 0.5) / 16777216.0;
 }
-__global__ void pool_draw_kernel(const float* __restrict__ vals, const int* __restrict__ idxs, const double* __restrict__ ptemp,
-                                 const int* __restrict__ topk, const double* __restrict__ topp,
-                                 const unsigned* __restrict__ seeds, int* __restrict__ out, int k) {
+__global__ void pool_draw_kernel(const float* vals, const int* idxs, const double* ptemp,
+                                 const int* topk, const double* topp,
+                                 const unsigned* seeds, int* out, int k) {
     __shared__ double probs[64];
     pdl_trigger();
     pdl_wait();
@@ -467,9 +467,9 @@ ZLLM_API int zllm_pool_draw(const float* vals, const int* idxs, const double* pt
 // tok <- out, pos += 1, seed += 0x9E3779B1 (the per-token seed rule of
 // zllm src/backend/gpu/sampling.rs:9); the sampled tokens are also appended to a history ring
 // [hist_cap, B] that the host reads once at the end.  One block; B <= 1024.
-__global__ void advance_decode_kernel(int* __restrict__ tok, int* __restrict__ pos, const int* __restrict__ row_slot,
-                                      unsigned* __restrict__ seeds, const int* __restrict__ out,
-                                      int* __restrict__ hist, int* __restrict__ counter, int hist_cap, int B) {
+__global__ void advance_decode_kernel(int* tok, int* pos, const int* row_slot,
+                                      unsigned* seeds, const int* out,
+                                      int* hist, int* counter, int hist_cap, int B) {
     pdl_trigger();
     pdl_wait();
     const int r = threadIdx.x;

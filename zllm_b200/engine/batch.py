@@ -75,7 +75,10 @@ class StepBuffers:
             self.copied.synchronize()   # the previous copy must have read the pinned buffer
             self._pending = False
 
+    bytes_uploaded = 0          # host-to-device bytes of all step buffers so far (for measurement)
+
     def upload(self):
+        StepBuffers.bytes_uploaded += self.total * 4
         self.dev.copy_(self.host, non_blocking=True)
         if self.copied is not None:
             self.copied.record()

@@ -25,6 +25,20 @@ from .runner import ModelRunner
 from .scheduler import Plan, Scheduler
 
 
+def _step_log():
+    """ZLLM_STEP_LOG=path (or "-" for stderr): one JSON line per engine step -- what it ran, the
+    wall time since the step before, queue lengths, free pages, and with ZLLM_PROFILE=1 the device
+    time per kernel class.  The reference prints per-section timers from its ``profile`` feature
+    (zllm src/main.rs:643-658); this is the same aid for a batched engine."""
+    import os
+    import sys
+    import time
+    path = os.environ.get("ZLLM_STEP_LOG")
+    if not path:
+        return None
+    return {"f": sys.stderr if path == "-" else open(path, "a"), "t": time.perf_counter()}
+
+
 class Engine:
     """Continuous batching over one model on one GPU.
 
@@ -43,10 +57,14 @@ class Engine:
         self.sampler = Sampler(self.runner.ops, self.runner.device, max(ecfg.max_num_seqs, 1))
         self.steps = 0
         self.generated = 0
+        # what the last ``step()`` ran: decoded rows, prompt tokens, and whether it was a decode
+        # graph launched ahead of the host (for measurement and the per-step log)
+        self.last_step = {"decodes": 0, "prompt_tokens": 0, "ahead": False}
+        self._log = _step_log()
         self.overlap = True            # launch the next decode step before reading this one's tokens
         self._ahead = None             # (requests, handle) of a decode step launched ahead
         # top-k / top-p draws inside the decode graph (no host between steps); off: the host draws
-        self._device_pool = bool(ecfg.cuda_graphs and self.runner.device.type == "cuda" and hasattr(self.runner.ops, "pool_draw"))
+        self._device_pool = bool(self.runner.ecfg.cuda_graphs and self.runner.device.type == "cuda" and hasattr(self.runner.ops, "pool_draw"))
 
     # ---- requests ------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -104,6 +122,7 @@ class Engine:
             out = self._commit_ahead(reqs, self.runner.decode_collect(handle))
             if nxt is not None:
                 self._ahead = (reqs, nxt)
+            self._note(len(reqs), 0, True, out)
             return out
         plan = self.scheduler.schedule()
         if plan.empty:
@@ -146,7 +165,26 @@ class Engine:
         out = self.scheduler.commit(plan, dtoks, first)
         self.steps += 1
         self.generated += len(out)
+        self._note(len(dec), sum(p.n for p in plan.portions), False, out)
         return out
+
+    def _note(self, decodes, prompt_tokens, ahead, out):
+        self.last_step = {"decodes": decodes, "prompt_tokens": prompt_tokens, "ahead": ahead}
+        if self._log is not None:
+            import json
+            import time
+            now = time.perf_counter()
+            rec = dict(self.last_step, step=self.steps, produced=len(out), ms=round((now - self._log["t"]) * 1e3, 3),
+                       running=len(self.scheduler.running), waiting=len(self.scheduler.waiting),
+                       free_pages=self.runner.cache.free_pages())
+            prof = getattr(self.runner.ops, "take_profile", None)
+            if prof is not None:
+                kernels = prof()
+                if kernels:
+                    rec["kernel_ms"] = kernels
+            self._log["t"] = now
+            self._log["f"].write(json.dumps(rec) + "\n")
+            self._log["f"].flush()
 
     # ---- whole generation ------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[List[int]]:

@@ -52,6 +52,10 @@ class ModelRunner:
             ops = _default_ops(self.device)
         self.ops = ops
         ops.configure(self.dtype)
+        if getattr(ops, "profiling", False) and self.ecfg.cuda_graphs:
+            # per-operation timers bracket every launch with events, which a captured graph cannot hold
+            import dataclasses
+            self.ecfg = dataclasses.replace(self.ecfg, cuda_graphs=False)
         if model_dir is not None:
             raw = read_config_json(model_dir)
             arch = architecture_of(raw)

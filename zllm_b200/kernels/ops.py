@@ -17,6 +17,7 @@ float32 in both.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -52,6 +53,54 @@ class CudaOps:
         self._tc_scratch = None
         self._kv_maps = {}
         self.launches = 0
+        self.profiling = os.environ.get("ZLLM_PROFILE", "") not in ("", "0")
+        if self.profiling:
+            self._profile_setup()
+
+    # ---- device time per kind of operation, behind ZLLM_PROFILE=1 ---------------------------
+    # The reference has per-section timers behind its ``profile`` feature (zllm
+    # src/backend/candle/quantized_llama_fork.rs:1042-1128, printed by src/main.rs:643-658).  Here
+    # every outermost operation of the kernel table is bracketed by two CUDA events on the
+    # launching stream; ``take_profile()`` waits for them and returns the milliseconds per kind
+    # since the last call.  Steps then run without CUDA graphs (events cannot be timed inside a
+    # capture), so the shares are those of serialised launches, as a profiler would show them.
+    PROFILED = ("embedding", "rmsnorm", "linear", "linear_normed", "qkv_rope_store", "rope_kv_store", "paged_attention",
+                "silu_mul", "gather_rows", "sample", "topk", "pool_draw", "advance_decode")
+
+    def _profile_setup(self):
+        self._prof_depth = 0
+        self._prof_events = []
+        for name in self.PROFILED:
+            inner = getattr(self, name)
+
+            def timed(*a, _inner=inner, _name=name, **kw):
+                if self._prof_depth > 0 or torch.cuda.is_current_stream_capturing():
+                    return _inner(*a, **kw)
+                kind = _name
+                if _name in ("linear", "linear_normed"):
+                    mode = kw.get("mode", a[3] if _name == "linear" else a[5])
+                    kind = f"{_name}[{mode}]"
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                self._prof_depth += 1
+                e0.record()
+                try:
+                    return _inner(*a, **kw)
+                finally:
+                    e1.record()
+                    self._prof_depth -= 1
+                    self._prof_events.append((kind, e0, e1))
+            setattr(self, name, timed)
+
+    def take_profile(self):
+        """{kind of operation: device milliseconds} since the last call; {} unless ZLLM_PROFILE is set."""
+        if not self.profiling or not self._prof_events:
+            return {}
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for kind, e0, e1 in self._prof_events:
+            out[kind] = out.get(kind, 0.0) + e0.elapsed_time(e1)
+        self._prof_events = []
+        return {k: round(v, 4) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
 
     # ------------------------------------------------------------------
     def configure(self, dtype):
