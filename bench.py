@@ -141,23 +141,25 @@ def profile_case(args):
     runner = ModelRunner(config=cfg, seed=2, random_on_device=True, engine_config=EngineConfig(
         dtype="bfloat16", block_size=BLOCK, num_blocks=B * (-(-(ctx_len + 64) // BLOCK)) + args.tokens // BLOCK + 8,
         max_num_seqs=max(B, 1), max_num_batched_tokens=max(args.tokens, PROMPT), max_model_len=max(ctx_len + 64, args.tokens + 8),
-        cuda_graphs=False))
+        cuda_graphs=bool(args.graphs)))
     gen = torch.Generator().manual_seed(0)
     rand = lambda n: torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if args.case == "prefill":
         toks = rand(args.tokens)
-        times = []
+        times, wall = [], []
         for _ in range(max(2, args.steps)):
             s = runner.admit()
-            torch.cuda.synchronize(); a.record()
+            torch.cuda.synchronize(); t0 = time.perf_counter(); a.record()
             runner.step([StepEntry(s, toks, (len(toks) - 1,))])
-            b.record(); torch.cuda.synchronize()
-            times.append(a.elapsed_time(b))
+            b.record(); t1 = time.perf_counter(); torch.cuda.synchronize()
+            times.append(round(a.elapsed_time(b), 4))
+            wall.append(round((t1 - t0) * 1e3, 4))          # the host's share: until the last launch is issued
             runner.release(s)
         best = min(times)
         print(json.dumps({"case": "prefill", "shape": args.shape, "tokens": args.tokens, "layers": cfg.num_hidden_layers,
-                          "ms": times, "tflops": round(prefill_flops(args.tokens) / best / 1e9, 1),
+                          "graphs": bool(args.graphs), "ms": times, "host_ms": wall,
+                          "tflops": round(prefill_flops(args.tokens) / best / 1e9, 1),
                           "frac_of_peak": round(prefill_flops(args.tokens) / best / 1e9 / pk["bf16_tflops"], 3)}))
         return 0
     slots = [runner.admit() for _ in range(B)]
@@ -174,7 +176,7 @@ def profile_case(args):
         times.append(a.elapsed_time(b))
     gbs = (weight_bytes + B * ctx_len * kv_per_token) / min(times) / 1e6
     print(json.dumps({"case": "decode", "shape": args.shape, "batch": B, "context": ctx_len, "layers": cfg.num_hidden_layers,
-                      "ms": times, "graphs": False, "gb_per_s": round(gbs, 1), "frac_of_peak": round(gbs / pk["hbm_gbs"], 3),
+                      "ms": times, "graphs": bool(args.graphs), "gb_per_s": round(gbs, 1), "frac_of_peak": round(gbs / pk["hbm_gbs"], 3),
                       "launches_per_step": (runner.ops.launches - launches0) // max(2, args.steps)}))
     return 0
 
@@ -320,6 +322,8 @@ def main():
     ap.add_argument("--context", type=int, default=1024, help="--case decode: cached positions per request")
     ap.add_argument("--tokens", type=int, default=PROMPT, help="--case prefill: tokens of the prompt")
     ap.add_argument("--layers", type=int, default=None, help="--case: fewer layers (profiling only)")
+    ap.add_argument("--graphs", action="store_true", help="--case: with CUDA graphs (default off, so that a profiler sees "
+                    "every kernel as its own launch)")
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="--case: layer sizes of another Llama shape")
     args = ap.parse_args()
 

@@ -229,6 +229,40 @@ def test_llama_1b_layer_sizes(tmp_path, dtype):
     r.ops.check_async_errors()
 
 
+@pytest.mark.parametrize("name", ["B", "C", "D"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_with_portions_replay_captured_graphs(tmp_path, name, dtype):
+    """A step with prompt portions whose shape bucket (rows, decoded rows, wanted rows, tiles,
+    splits) has been seen before replays a captured graph with padding rows and empty tiles.  The
+    portions and the mixed family, three times over on one runner: from the second time on most
+    steps are replays; every logit against the plain implementation, and in 32-bit the replayed
+    steps bit for bit what the launched ones gave."""
+    d = make_model_dir(tmp_path, name, dtype)
+    cfg, w = P.read_model_dir(d)
+    V = cfg["vocab_size"]
+    reqs = requests_for(name, V)[:6]
+    ref = {rid: P.forward_all_positions(cfg, w, toks) for rid, toks in reqs}
+    max_tokens = 448
+    steps = TR.family_portions(reqs, prefix="p.") + TR.family_mixed(reqs, max_tokens, 4, 2, "m.")
+    r = gpu_runner(d, name, dtype, num_blocks=max_tokens // TINY[name][1], max_rows=max_tokens)
+    assert r.step_graphs_on
+    atol, rel = tolerances(dtype, name)
+    rounds = []
+    for i in range(3):
+        before = r.step_graph_replays
+        got = TR.replay_inprocess(r, steps)
+        rounds.append((got, r.step_graph_replays - before))
+        for prefix in ("p.", "m."):
+            TR.compare(got, ref, reqs, prefix, atol, rel, f"tiny {name} {dtype} step graphs {prefix}")
+    assert rounds[0][1] < rounds[2][1] and rounds[2][1] > len(steps) // 3, [n for _, n in rounds]
+    if dtype == "float32":
+        for k, v in rounds[0][0].items():
+            assert torch.equal(v, rounds[2][0][k]), k
+    r.cache.check_integrity()
+    r.ops.check_async_errors()
+    assert r.cache.free_pages() == [max_tokens // TINY[name][1]]
+
+
 @pytest.mark.parametrize("name", ["C", "D"])
 def test_large_mixed_step_with_decoded_rows(tmp_path, name):
     """A step of more than 512 rows that holds two decoded rows around a prompt portion: the

@@ -28,6 +28,7 @@ class EngineConfig:
     seed: int = 0
     device: str = "cuda:0"
     cuda_graphs: bool = True           # replay captured graphs for decode-only steps
+    step_graphs: bool = True           # with cuda_graphs: also capture steps with prompt portions, per shape bucket
     prefix_sharing: bool = True        # requests take over the full cache pages of a prompt prefix seen before
 
     def validate(self) -> "EngineConfig":

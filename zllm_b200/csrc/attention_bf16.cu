@@ -497,6 +497,7 @@ __global__ void __launch_bounds__(NWARPS * 32, MT == 2 ? 2 : 1) prefill_kernel(
     // with the most work start first for ALL heads and the short ones fill the tail
     const int* tl = tiles + 4 * (gridDim.y - 1 - blockIdx.y);
     const int row0 = tl[0], n_rows = tl[1], slot = tl[2], pos0 = tl[3];
+    if (n_rows <= 0 || slot < 0) return;                     // an empty tile (padding of a tile list of fixed size)
     const int h = blockIdx.x;
     const int kvh = h / (nq / nkv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;

@@ -175,6 +175,8 @@ __global__ void __launch_bounds__(PT_THREADS, CTAS) prefill_tc_kernel(
     // CTAs with the most work start first for ALL heads and the short ones fill the tail.
     const int* tl = tiles + 4 * (gridDim.y - 1 - blockIdx.y);
     const int row0 = tl[0], n_rows = tl[1], slot = tl[2], pos0 = tl[3];
+    if (n_rows <= 0 || slot < 0) return;                     // an empty tile (padding of a tile list of fixed
+                                                             // size): the whole CTA leaves before it owns anything
     const int h = blockIdx.x;
     const int kvh = h / (nq / nkv);
     const int* trow = table + (size_t)slot * max_blocks;

@@ -62,6 +62,18 @@ class StepBuffers:
         self.copied = torch.cuda.Event() if dev.type == "cuda" else None
         self._pending = False
 
+    @staticmethod
+    def table_shapes(entries, starts, planners):
+        """The names and (bucketed) shapes of the tables the planners would make for this step,
+        without a buffer: what a step graph's key needs."""
+        if not planners:
+            return ()
+        scratch = AuxRegion(np.zeros(4 * sum(len(e.tokens) for e in entries) + 64, dtype=np.int32))
+        out = []
+        for plan in planners:
+            out.extend((name, tuple(shape)) for name, (_, shape) in plan(entries, starts, scratch, bucketed=True).items())
+        return tuple(sorted(out))
+
     def host_section(self, name):
         o, n = self.offsets[name]
         return self.np[o:o + n]
@@ -122,7 +134,8 @@ class StepContext:
     fixed_splits: int = 0        # > 0: the split count a captured graph was recorded with
 
 
-def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[int], pad_rows: int = 0, planners=()):
+def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[int], pad_rows: int = 0, planners=(),
+              pad_decode: Optional[int] = None, pad_want: int = 0, bucketed: bool = False):
     """Write the step's arrays into ``buf`` (host side) and return the counts
     (rows, wanted rows, decoded rows, the planners' tables, largest context).
 
@@ -130,6 +143,10 @@ def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[i
     pads the row arrays to that many rows with slot -1 (for graph buckets).
     ``planners``: callables ``(entries, starts, aux: AuxRegion) -> {name: (offset, shape)}`` of
     the model's parts; each writes what its kernels want to know about this step.
+    For steps replayed from a captured graph every count must be that of the graph: ``pad_decode``
+    pads the list of decoded rows to that many with padding rows (default: every padding row is
+    one), ``pad_want`` the wanted rows with row 0, and ``bucketed`` asks the planners to round
+    their tables up to sizes of their own choosing (``bucketed=True`` in their call).
     """
     buf.begin_fill()
     tok = buf.host_section("token_ids")
@@ -161,15 +178,21 @@ def fill_step(buf: StepBuffers, entries: Sequence[StepEntry], starts: Sequence[i
         tok[T:pad_rows] = 0
         pos[T:pad_rows] = 0
         rs[T:pad_rows] = -1
-        for i in range(T, pad_rows):
+        more = pad_rows - T if pad_decode is None else max(0, pad_decode - nd)
+        if more > pad_rows - T:
+            raise ValueError("not enough padding rows for the decoded rows of the bucket")
+        for i in range(T, T + more):
             dec[nd] = i
             nd += 1
         T = pad_rows
+    if pad_want > nw:
+        want[nw:pad_want] = 0
+        nw = pad_want
     plans = {}
     if planners:
         aux = AuxRegion(buf.host_section("aux"))
         for plan in planners:
-            plans.update(plan(entries, starts, aux))
+            plans.update(plan(entries, starts, aux, bucketed=True) if bucketed else plan(entries, starts, aux))
     return T, nw, nd, plans, max_ctx
 
 

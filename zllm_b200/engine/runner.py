@@ -10,7 +10,12 @@ cache.  Pool exhaustion is an error return (MemoryError_) raised before
 anything is launched, where the reference panics (mod.rs:2508-2509).
 
 Decode-only steps replay a captured CUDA graph per (rows, split-count) bucket,
-since at small batch the step is bound by launches, not by memory.
+since at small batch the step is bound by launches, not by memory.  Steps with
+prompt portions are captured too, per shape bucket (rows, decoded rows, wanted
+rows, splits, the parts' own table sizes), once a shape has been seen twice: a
+forward is more than a hundred launches, which the driver then issues in one
+call where the host would need a millisecond.  The reference records a whole
+step into one command buffer and submits it once (mod.rs:2193-2208).
 """
 from __future__ import annotations
 
@@ -96,6 +101,13 @@ class ModelRunner:
         self.buffers = StepBuffers(self.max_rows, self.max_rows, self.device)
         self._planners = self.model.step_planners()
         self._graphs: Dict[tuple, dict] = {}
+        # graphs of steps with prompt portions, by shape bucket; a shape is captured when it comes
+        # a second time.  Only for models all of whose parts say they can be captured.
+        self._step_graphs: Dict[tuple, dict] = {}
+        self._step_seen: Dict[tuple, int] = {}
+        self.step_graphs_on = bool(self.ecfg.cuda_graphs and self.ecfg.step_graphs and self.device.type == "cuda"
+                                   and self.model.capturable())
+        self.step_graph_replays = 0
         self._token_ring = None
         self._last_key = None
         self.steps = 0
@@ -166,6 +178,10 @@ class ModelRunner:
         device, in the order of the entries and of their ``want`` (None if nothing is wanted).
         The tensor is a view of a reused buffer: read it before the next step."""
         starts = self._prepare(entries)
+        if self.step_graphs_on:
+            logits = self._step_through_graph(entries, starts)
+            if logits is not NotImplemented:
+                return logits
         buf = self.buffers
         T, R, nd, plans, max_ctx = fill_step(buf, entries, starts, planners=self._planners)
         buf.upload()
@@ -177,6 +193,97 @@ class ModelRunner:
         self.steps += 1
         self.tokens_run += T
         return logits
+
+    # ---- steps with prompt portions through captured graphs -----------------------------------
+    STEP_GRAPH_CAP = 64                     # graphs kept; beyond that new shapes run launch by launch
+
+    @staticmethod
+    def _row_bucket(n: int) -> int:
+        """Rows of a captured step: 16, 32, 64, 128, then multiples of 128 up to 1024, then of 256."""
+        if n <= 128:
+            return max(16, _bucket(n))
+        if n <= 1024:
+            return -(-n // 128) * 128
+        return -(-n // 256) * 256
+
+    def _step_through_graph(self, entries, starts):
+        """Run the step by replaying the graph of its shape bucket; NotImplemented when the shape
+        has no graph (yet) and the caller should launch the kernels one by one."""
+        T = sum(len(e.tokens) for e in entries)
+        nd = sum(1 for e in entries if len(e.tokens) == 1)
+        if nd == len(entries):
+            return NotImplemented                           # decode-only steps have their own graphs
+        R = sum(len(e.want) for e in entries)
+        nd_b = _bucket(nd) if nd else 0
+        T_b = self._row_bucket(T + (nd_b - nd))             # padding rows stand in for the missing decoded rows
+        if T_b > self.max_rows:
+            return NotImplemented
+        R_b = _bucket(R) if R else 0
+        max_ctx = max(s + len(e.tokens) for e, s in zip(entries, starts))
+        sp_b = _bucket(self.ops.decode_splits(max_ctx)) if nd else 0
+        # the parts' tables: their sizes are part of the shape
+        probe = StepBuffers.table_shapes(entries, starts, self._planners)
+        key = (T_b, nd_b, R_b, sp_b, probe)
+        g = self._step_graphs.get(key)
+        if g is None:
+            seen = self._step_seen.get(key, 0) + 1
+            self._step_seen[key] = seen
+            if seen < 2 or len(self._step_graphs) >= self.STEP_GRAPH_CAP:
+                return NotImplemented
+            g = self._step_graphs[key] = self._capture_step(key, entries, starts)
+        buf = g["buf"]
+        fill_step(buf, entries, starts, pad_rows=T_b, planners=self._planners, pad_decode=nd_b, pad_want=R_b,
+                  bucketed=True)
+        buf.upload()
+        self.cache.sync_tables()
+        g["graph"].replay()
+        for e, s in zip(entries, starts):
+            self.cache.advance(e.slot, s + len(e.tokens))
+        self.steps += 1
+        self.tokens_run += T
+        self.step_graph_replays += 1
+        return g["logits"][:R] if R else None
+
+    def _capture_step(self, key, entries, starts):
+        T_b, nd_b, R_b, sp_b, _ = key
+        buf = StepBuffers(T_b, max(R_b, 1), self.device)
+        _, R, nd, plans, _ = fill_step(buf, entries, starts, pad_rows=T_b, planners=self._planners, pad_decode=nd_b,
+                                       pad_want=R_b, bucketed=True)
+        ctx = make_context(buf, T_b, R, nd, plans, 0, self.ws)          # no host-side description: a replay has other entries
+        ctx.max_context = sp_b * self.ops.decode_split_keys
+        ctx.fixed_splits = sp_b
+        # warm-up and capture run on neutral contents: every row padding, every tile empty, so that
+        # nothing is written to the cache; the real contents are uploaded before each replay
+        buf.host_section("row_slot")[:] = -1
+        buf.host_section("token_ids")[:] = 0
+        buf.host_section("positions")[:] = 0
+        for name, (off, shape) in plans.items():
+            n = 1
+            for d in shape:
+                n *= d
+            self._neutral_table(buf.host_section("aux")[off:off + n], name)
+        buf.upload()
+        self.cache.sync_tables()
+        torch.cuda.synchronize(self.device)
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._forward(ctx)                      # sizes every workspace buffer
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self._forward(ctx)
+        return {"buf": buf, "graph": graph, "logits": logits, "ctx": ctx}
+
+    @staticmethod
+    def _neutral_table(host, name):
+        # a part's table made harmless for the warm-up and capture runs: the attention path's tiles
+        # become empty tiles; any other table is zeroed
+        if name == "query_tiles":
+            host.reshape(-1, 4)[:] = (0, 0, -1, 0)
+        else:
+            host[:] = 0
 
     def _forward(self, ctx):
         bind = getattr(self.ops, "bind_stream", None)

@@ -430,12 +430,21 @@ class CudaOps:
     QUERY_TILE = 128        # query rows of one tile of the prefill attention kernels (PF_QROWS in csrc)
 
     @classmethod
-    def plan_query_tiles(cls, entries, starts, aux):
+    def plan_query_tiles(cls, entries, starts, aux, bucketed=False):
         """The step planner of the attention path: every portion (an entry of two tokens or more)
-        cut into tiles of QUERY_TILE rows, as [first row, rows, slot, position of the first row]."""
+        cut into tiles of QUERY_TILE rows, as [first row, rows, slot, position of the first row].
+        ``bucketed``: the list is rounded up to a power of two with empty tiles (0 rows, slot -1),
+        which the kernels skip, so that steps of like shape can replay one captured graph."""
         q = cls.QUERY_TILE
-        n = sum(-(-len(e.tokens) // q) for e in entries if len(e.tokens) > 1)
+        n_real = sum(-(-len(e.tokens) // q) for e in entries if len(e.tokens) > 1)
+        n = n_real
+        if bucketed and n_real:
+            n = 1
+            while n < n_real:
+                n *= 2
         host, off = aux.take(4 * n)
+        if n > n_real:
+            host[4 * n_real:4 * n] = (0, 0, -1, 0) * (n - n_real)
         r = i = 0
         for e, start in zip(entries, starts):
             m = len(e.tokens)

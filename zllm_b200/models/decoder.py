@@ -160,6 +160,17 @@ class DecoderModel:
         """Per run entry: (cache spec of its mixer or None, cache_of)."""
         return [(self.layers[e.layer].mixer.cache_spec(), e.cache_of) for e in self.spec.run_order]
 
+    def capturable(self) -> bool:
+        """True when every part says that a step with prompt portions may be captured as a graph."""
+        parts = [p for layer in self.layers for p in layer.parts().values()] + [self.final_norm]
+        if self.position is not None:
+            parts.append(self.position)
+        for p in list(parts):
+            pe = getattr(p, "position_encoding", None)
+            if pe is not None:
+                parts.append(pe)
+        return all(getattr(p, "capturable", False) for p in parts)
+
     def step_planners(self):
         """The planners of the model's parts, each once: callables that write a part's own tables
         for a step into the step buffer (``parts.base.Part.step_planner``)."""

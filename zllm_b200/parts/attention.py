@@ -68,6 +68,7 @@ class PagedAttention(Mixer):
         self.w_o = tensors["o_proj"].contiguous()
 
     accepts_input_norm = True
+    capturable = True
 
     def step_planner(self):
         # the tiled attention kernels want each portion cut into query tiles of their own size

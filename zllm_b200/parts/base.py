@@ -153,6 +153,13 @@ class Part:
 
     rt = None
 
+    # True: ``forward`` only launches work on the current stream and learns about the step from
+    # ``ctx``'s device arrays and shapes alone (never from ``ctx.entries`` or other host data), so
+    # a step with prompt portions may be captured as a CUDA graph and replayed for other steps of
+    # the same shape.  Decode-only steps are captured whatever this says (there ``ctx.entries`` is
+    # None and a part must already manage with the device arrays).
+    capturable = False
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {}
 

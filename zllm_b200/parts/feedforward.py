@@ -58,6 +58,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj"].contiguous()
 
     accepts_input_norm = True
+    capturable = True
 
     def forward(self, h, residual, ctx, input_norm=None):
         """``input_norm`` as for the attention mixer: (weight, eps) when h is the float32 residual."""

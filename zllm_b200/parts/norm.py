@@ -13,6 +13,8 @@ from .base import Norm, WeightSpec, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    capturable = True
+
     def __init__(self, size: int, eps: float):
         self.size = int(size)
         self.eps = float(eps)

@@ -80,6 +80,8 @@ def inverse_frequencies(rot_dim: int, theta: float, scaling: Optional[dict], fre
 
 @register_position_encoding("rotary")
 class Rotary(PositionEncoding):
+    capturable = True
+
     def __init__(self, rot_dim: int, theta: float, max_position: int, scaling: Optional[dict] = None,
                  interleaved: bool = False, freq_factors=None):
         if rot_dim <= 0 or rot_dim % 2:
