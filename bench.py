@@ -157,6 +157,12 @@ def profile_case(args):
             wall.append(round((t1 - t0) * 1e3, 4))          # the host's share: until the last launch is issued
             runner.release(s)
         best = min(times)
+        if runner.ops.profiling:                              # ZLLM_PROFILE=1: device time per kind of operation
+            runner.ops.take_profile()
+            s = runner.admit()
+            runner.step([StepEntry(s, toks, (len(toks) - 1,))])
+            print(json.dumps({"case": "prefill", "tokens": args.tokens, "kernel_ms": runner.ops.take_profile()}))
+            runner.release(s)
         print(json.dumps({"case": "prefill", "shape": args.shape, "tokens": args.tokens, "layers": cfg.num_hidden_layers,
                           "graphs": bool(args.graphs), "ms": times, "host_ms": wall,
                           "tflops": round(prefill_flops(args.tokens) / best / 1e9, 1),
@@ -174,6 +180,10 @@ def profile_case(args):
         runner.decode_step(slots, rand(B), [0.0] * B, [0] * B)
         b.record(); torch.cuda.synchronize()
         times.append(a.elapsed_time(b))
+    if runner.ops.profiling:
+        runner.ops.take_profile()
+        runner.decode_step(slots, rand(B), [0.0] * B, [0] * B)
+        print(json.dumps({"case": "decode", "batch": B, "context": ctx_len, "kernel_ms": runner.ops.take_profile()}))
     gbs = (weight_bytes + B * ctx_len * kv_per_token) / min(times) / 1e6
     print(json.dumps({"case": "decode", "shape": args.shape, "batch": B, "context": ctx_len, "layers": cfg.num_hidden_layers,
                       "ms": times, "graphs": bool(args.graphs), "gb_per_s": round(gbs, 1), "frac_of_peak": round(gbs / pk["hbm_gbs"], 3),
@@ -228,7 +238,8 @@ def mixed_workload(args, K, W):
         return time.perf_counter() - t_start, n_out, steps
 
     clocks = ClockSampler()
-    run()                                          # warm-up: every graph bucket and workspace size has been seen
+    run()                                          # warm-up, twice: a step shape is captured as a graph when it comes a
+    run()                                          # second time, so only then has every graph of the workload been made
     clocks.start()
     total_s, n_out, steps = run()
     clk = clocks.stop()

@@ -105,6 +105,9 @@ class ModelRunner:
         # a second time.  Only for models all of whose parts say they can be captured.
         self._step_graphs: Dict[tuple, dict] = {}
         self._step_seen: Dict[tuple, int] = {}
+        self._side_stream = None
+        self._graph_pool = None
+        self._last_captured = None
         self.step_graphs_on = bool(self.ecfg.cuda_graphs and self.ecfg.step_graphs and self.device.type == "cuda"
                                    and self.model.capturable())
         self.step_graph_replays = 0
@@ -264,17 +267,33 @@ class ModelRunner:
             self._neutral_table(buf.host_section("aux")[off:off + n], name)
         buf.upload()
         self.cache.sync_tables()
-        torch.cuda.synchronize(self.device)
-        side = torch.cuda.Stream(self.device)
-        side.wait_stream(torch.cuda.current_stream(self.device))
+        logits = self._capture(lambda: self._forward(ctx))
+        return {"buf": buf, "graph": self._last_captured, "logits": logits, "ctx": ctx}
+
+    def _capture(self, body):
+        """Run ``body`` once on a side stream (it sizes every workspace buffer), then capture it
+        into a graph (``self._last_captured``) and return what it returned.  The graphs share one
+        memory pool; ``capture_begin`` is used directly because the ``torch.cuda.graph`` context
+        collects garbage and empties the allocator's cache on entry, which costs tens of
+        milliseconds per capture."""
+        cur = torch.cuda.current_stream(self.device)
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(self.device)
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        side = self._side_stream
+        side.wait_stream(cur)
         with torch.cuda.stream(side):
-            self._forward(ctx)                      # sizes every workspace buffer
-        torch.cuda.current_stream(self.device).wait_stream(side)
-        torch.cuda.synchronize(self.device)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = self._forward(ctx)
-        return {"buf": buf, "graph": graph, "logits": logits, "ctx": ctx}
+            body()
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            graph.capture_begin(pool=self._graph_pool)
+            try:
+                out = body()
+            finally:
+                graph.capture_end()
+        cur.wait_stream(side)
+        self._last_captured = graph
+        return out
 
     @staticmethod
     def _neutral_table(host, name):
@@ -504,18 +523,10 @@ class ModelRunner:
         buf.host_section("decode_rows")[:bucket] = range(bucket)
         buf.host_section("want_rows")[:bucket] = range(bucket)
         buf.upload()
-        torch.cuda.synchronize(self.device)
-        side = torch.cuda.Stream(self.device)
-        side.wait_stream(torch.cuda.current_stream(self.device))
-        with torch.cuda.stream(side):
-            self._decode_body(g)          # warm-up: sizes every workspace buffer
-        torch.cuda.current_stream(self.device).wait_stream(side)
-        torch.cuda.synchronize(self.device)
-        graph = torch.cuda.CUDAGraph()
         before = getattr(self.ops, "launches", 0)
-        with torch.cuda.graph(graph):
-            self._decode_body(g)
-        g["launches"] = getattr(self.ops, "launches", 0) - before     # kernels in one replay
+        self._capture(lambda: self._decode_body(g))
+        g["launches"] = (getattr(self.ops, "launches", 0) - before) // 2     # kernels in one replay (warm-up + capture)
+        graph = self._last_captured
         g["graph"] = graph
         return g
 
