@@ -130,10 +130,18 @@ SPLIT_K_SHAPES = [  # rows, N, K, epilogue: few tiles, so the many-row kernel ta
 ]
 
 
-@pytest.mark.parametrize("tile", [0, 128, 256])
-@pytest.mark.parametrize("M,N,K,mode", SPLIT_K_SHAPES + [(700, 1288, 520, "store"), (1100, 640, 264, "swiglu"), (640, 904, 1032, "add")])
+STREAM_K_SHAPES = [  # more tiles than SMs, so that the tile width is chosen by the waves it makes (192, 195, 320 tiles of
+    # 256 weight rows, the last ones ragged; 128 tiles of a long K)
+    (2048, 3072, 2048, "store"), (1900, 3080, 1032, "store"), (1280, 4096, 1024, "swiglu"), (2048, 2048, 8192, "add"),
+    (2047, 3072, 2048, "add"),
+]
+
+
+@pytest.mark.parametrize("tile", [0, 128, 192, 256])
+@pytest.mark.parametrize("M,N,K,mode", SPLIT_K_SHAPES + STREAM_K_SHAPES +
+                         [(700, 1288, 520, "store"), (1100, 640, 264, "swiglu"), (640, 904, 1032, "add")])
 def test_many_row_product_with_split_k(ops, M, N, K, mode, tile):
-    """``tile``: the kernel's tile width forced to 128 or 256 weight rows (0: chosen by the sizes),
+    """``tile``: the kernel's tile width forced to 128, 192 or 256 weight rows (0: chosen by the sizes),
     so that both shapes run at every size."""
     assert ops.lib("gemm_tc").zllm_gemm_tc_force_tile(tile) == 0
     try:

@@ -2,7 +2,7 @@
 // out[m][n] = sum_k x[m][k] w[n][k], float32 accumulation in tensor memory.
 //
 // One CTA computes a 128 x 256 tile (128 x 128 for products with few tiles and a short K: twice
-// the CTAs without splitting K).  Operands come by TMA (cp.async.bulk.tensor, 128-byte
+// the CTAs without splitting K; 128 x 192 when that fills the waves of tiles better).  Operands come by TMA (cp.async.bulk.tensor, 128-byte
 // swizzle) into a ring of shared-memory tiles [128][64] and [256][64] (4 stages; 6 of the narrow
 // tile); one elected thread issues tcgen05.mma (M = 128, N = tile width, K = 16, four per stage)
 // with the accumulator in TMEM; tcgen05.commit hands stages back to the TMA warp and finally the accumulator to
@@ -27,11 +27,13 @@
 #define TC_BM 128
 #define TC_BN 256                       // weight rows per tile; TC_BN_HALF for products with few tiles
 #define TC_BN_HALF 128
+#define TC_BN_MID 192                   // for products whose tiles of 256 would leave the last wave nearly empty
 #define TC_BK 64
 #define TC_STAGES 4
 #define TC_A_BYTES (TC_BM * TC_BK * 2)
 #define TC_STAGE_BYTES_OF(BN) (TC_A_BYTES + (BN) * TC_BK * 2)
-#define TC_STAGES_OF(BN) ((BN) == TC_BN ? TC_STAGES : 6)      // the same shared memory either way
+#define TC_STAGES_OF(BN) ((BN) == TC_BN_HALF ? 6 : TC_STAGES)  // about the same shared memory either way
+#define TC_TMEM_COLS(BN) (2 * (BN) <= 256 ? 256 : 512)         // two accumulators; the allocation is a power of two
 #define TC_SMEM_OF(BN) (TC_STAGES_OF(BN) * TC_STAGE_BYTES_OF(BN) + 1024 /* alignment */ + 256 /* barriers */ + 4 * 2 * 4096 /* output staging */)
 #define TC_WAIT_LIMIT (1u << 24)
 
@@ -203,7 +205,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     }
     if (warp == 1) {                                                     // this warp owns the tensor memory
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(2 * BN) : "memory");
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(TC_TMEM_COLS(BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -329,7 +331,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TC_TMEM_COLS(BN)) : "memory");
     }
 }
 
@@ -496,6 +498,13 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
     // depends on the sizes only.
     const int k_all = (K + TC_BK - 1) / TC_BK;
     int bn = tiles_m * ((w_rows + TC_BN - 1) / TC_BN) * 2 <= n_sm && (k_all <= 64 || tiles_m <= 2) ? TC_BN_HALF : TC_BN;
+    if (bn == TC_BN) {
+        // More tiles than SMs: the time is the number of waves times the tile's width.  Tiles of 192
+        // weight rows when that product is smaller (192 tiles of 256 rows on 148 SMs are two waves
+        // with the second a third full; 256 tiles of 192 rows are two waves of three quarters the work).
+        auto cost = [&](int w) { const long long t = (long long)tiles_m * ((w_rows + w - 1) / w); return ((t + n_sm - 1) / n_sm) * w; };
+        if (cost(TC_BN_MID) < cost(TC_BN)) bn = TC_BN_MID;
+    }
     if (g_force_bn) bn = g_force_bn;
     e = make_map(&map_w, w, w_rows, K, bn);
     if (e) return e;
@@ -518,12 +527,17 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
         cudaError_t ce = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_OF(TC_BN));
         if (ce == cudaSuccess)
             ce = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN_HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_OF(TC_BN_HALF));
+        if (ce == cudaSuccess)
+            ce = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN_MID>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_OF(TC_BN_MID));
         if (ce != cudaSuccess) return (int)ce;
         attr_set = true;
     }
     if (bn == TC_BN)
         gemm_tc_kernel<TC_BN><<<grid, 192, TC_SMEM_OF(TC_BN), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode, out_bf16,
                                                                                        tiles_m, tiles_n, splits);
+    else if (bn == TC_BN_MID)
+        gemm_tc_kernel<TC_BN_MID><<<grid, 192, TC_SMEM_OF(TC_BN_MID), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode,
+                                                                                               out_bf16, tiles_m, tiles_n, splits);
     else
         gemm_tc_kernel<TC_BN_HALF><<<grid, 192, TC_SMEM_OF(TC_BN_HALF), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode,
                                                                                                  out_bf16, tiles_m, tiles_n, splits);
@@ -537,7 +551,7 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
 
 // Tests: force the tile width (128 or 256 weight rows; 0: by the sizes).
 ZLLM_API int zllm_gemm_tc_force_tile(int bn) {
-    if (bn != 0 && bn != TC_BN && bn != TC_BN_HALF) return ZLLM_ERR_UNSUPPORTED;
+    if (bn != 0 && bn != TC_BN && bn != TC_BN_HALF && bn != TC_BN_MID) return ZLLM_ERR_UNSUPPORTED;
     g_force_bn = bn;
     return 0;
 }

@@ -214,6 +214,7 @@ class CudaOps:
     STREAM_MAX_ROWS = 64
     STREAM_MIN_WEIGHTS = 12 * 1024 * 1024
     STREAM_MAX_WEIGHT_ROWS = 32768
+    UNFUSE_NORM_WEIGHT_ROWS = 32768
     SAMPLE_SCRATCH_ROWS = 1024
     TC_SCRATCH_BYTES = 64 * 1024 * 1024
     DECODE_MAX_ROWS = 16
@@ -264,7 +265,12 @@ class CudaOps:
         if x.dtype != torch.float32 or norm_w.numel() != K or w.shape[1] != K or out.shape[0] != M \
                 or w.shape[0] != (2 * N if mode == "swiglu" else N):
             raise BackendError("linear_normed: bad operand types or shapes")
-        if self._can_fuse_decode(x, norm_w, w, M, K) and not (mode == "swiglu" and N % 8) \
+        # The fused form has every CTA read the float32 rows of x again (4 M K bytes beside its own
+        # 32 K bytes of weights per 16 rows): from a few rows on and for matrices of many rows the
+        # norm as a kernel of its own and bfloat16 rows are faster (8 rows: the head 90 against 130 us,
+        # gate/up 16.7 against 18.9 us; one row: 88 against 100 and 16.3 against 15.1)
+        unfuse = w.shape[0] >= self.UNFUSE_NORM_WEIGHT_ROWS and M >= (1 if w.shape[0] >= self.STREAM_MAX_WEIGHT_ROWS else 4)
+        if self._can_fuse_decode(x, norm_w, w, M, K) and not unfuse and not (mode == "swiglu" and N % 8) \
                 and not (mode == "add" and out.dtype != torch.float32):
             self._gemm_decode(x, norm_w, eps, w, out, mode, M, N, K)
             return
