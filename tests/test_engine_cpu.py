@@ -151,3 +151,27 @@ def test_prefix_sharing_and_truncation_leave_the_tokens_unchanged(tmp_path):
         assert float((lg - ref[39]).abs().max()) < 1e-4
     ses.close()
     eng.runner.cache.check_integrity()
+
+
+def test_a_kernels_error_flag_stops_the_engine(tmp_path):
+    """The engine asks the kernel table for flagged bounded waits where it has just synchronised
+    (after the sampler's copy, after collecting a decode step); a table that reports one makes the
+    step raise instead of handing out tokens computed from an abandoned launch."""
+    from zllm_b200.errors import BackendError
+
+    class FlaggingOps(RefOps):
+        flagged = False
+
+        def raise_if_a_wait_gave_up(self):
+            if self.flagged:
+                raise BackendError("gemm_tc: a bounded wait ran out (code 3); results of that launch are invalid")
+
+    d = make_model_dir(tmp_path, "A")
+    ops = FlaggingOps()
+    eng = Engine(str(d), ops=ops, dtype="float32", device="cpu", cuda_graphs=False, block_size=16, num_blocks=16,
+                 max_num_seqs=2, max_num_batched_tokens=32)
+    eng.add_request(random_prompt(512, 9, 1), SamplingParams.greedy(max_tokens=4))
+    assert len(eng.step()) == 1                       # the prompt's step: one token
+    ops.flagged = True
+    with pytest.raises(BackendError, match="bounded wait ran out"):
+        eng.step()

@@ -576,3 +576,58 @@ def test_qkv_product_with_rope_and_cache_write(ops, M, nq, nkv, hd, inter, with_
     assert float((view.k_pages.float().cpu() - cview.k_pages).abs().max()) <= 2 ** -7 * sc
     assert float((view.v_pages.float().cpu() - cview.v_pages).abs().max()) <= 2 ** -7 * sc
     assert float(cview.k_pages.abs().sum()) > 0 and float(cview.v_pages.abs().sum()) > 0
+
+
+# ---- bounded waits: the give-up path of each kernel family -----------------------------------
+def _run_family(ops, family):
+    """One ordinary launch of the family's kernel; returns (got, want, tolerance)."""
+    g = torch.Generator().manual_seed(21)
+    if family in ("gemm_tc", "gemm_stream"):
+        M = 300 if family == "gemm_tc" else 40
+        N, K = 512, 1024
+        x, w = rnd((M, K), torch.bfloat16, 31), rnd((N, K), torch.bfloat16, 32, K ** -0.5)
+        out = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+        ops.linear(x.to(DEV), w.to(DEV), out, "store")
+        want = torch.zeros(M, N)
+        REF.linear(x, w, want, "store")
+        return out, want, 2 ** -8 * 1.5 * max(1.0, float(want.abs().max()))
+    nq, nkv, hd, bs = 8, 2, 64, 16
+    cm = make_cache(nkv, hd, bs, 64, 2, 700, torch.bfloat16)
+    s = cm.admit()
+    view = cm.view(0)
+    view.k_pages.copy_(torch.randn(view.k_pages.shape, generator=g).to(torch.bfloat16))
+    view.v_pages.copy_(torch.randn(view.v_pages.shape, generator=g).to(torch.bfloat16))
+    make_ctx(cm, [(s, 300)])
+    ctx = make_ctx(cm, [(s, 1)] if family == "attention_decode_tma" else [(s, 150)])
+    T = ctx.T
+    qkv = rnd((T, (nq + 2 * nkv) * hd), torch.bfloat16, 33)
+    out = torch.zeros(T, nq * hd, dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(qkv.to(DEV), out, ctx, view, nq, nkv, hd, 0.125, None)
+    want = torch.zeros(T, nq * hd)
+    REF.paged_attention(qkv.float(), want, cpu_ctx(ctx), CpuCacheView(view), nq, nkv, hd, 0.125, None)
+    return out, want, 0.02
+
+
+@pytest.mark.parametrize("family", ["gemm_tc", "gemm_stream", "attention_decode_tma", "attention_prefill_tc"])
+def test_a_wait_that_runs_out_is_reported_and_the_kernel_recovers(ops, family):
+    """The kernels with mbarrier waits bound every wait.  Here the family's producer is told to
+    issue no copy at all and the limit is a few hundred polls, so every wait for data runs out
+    with nothing in flight: the kernel must return by itself, the error must reach the host (the
+    device flag and its pinned mirror), and the next ordinary launch must be right again."""
+    from zllm_b200.errors import BackendError
+    got, want, tol = _run_family(ops, family)                     # an ordinary launch first
+    assert float((got.float().cpu() - want).abs().max()) <= tol
+    ops.check_async_errors()
+    ops.set_wait_test_hook(family, limit=300, skip_loads=True)
+    try:
+        _run_family(ops, family)                                  # returns although nothing ever arrives
+        torch.cuda.synchronize()
+        with pytest.raises(BackendError, match="bounded wait ran out"):
+            ops.raise_if_a_wait_gave_up()                         # seen through the pinned mirror, no copy
+    finally:
+        ops.set_wait_test_hook(family, limit=0, skip_loads=False)
+    ops.check_async_errors()                                      # reading cleared the flags
+    assert not bool(ops._error_words.any())
+    got, want, tol = _run_family(ops, family)                     # the same kernel, right again
+    assert float((got.float().cpu() - want).abs().max()) <= tol
+    ops.check_async_errors()

@@ -26,12 +26,13 @@
 //
 // Waits on mbarriers are bounded; a wait that runs out sets a flag the host reads.
 #include "attention_common.cuh"
+#include "wait_hooks.cuh"
 #include <cuda.h>
 #include <string.h>
 
 #define DT_WAIT_LIMIT (1u << 22)
 
-__device__ int g_dt_error = 0;
+ZLLM_WAIT_STATE(dt, DT_WAIT_LIMIT)
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
@@ -41,7 +42,8 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int where) {
-    for (unsigned i = 0; i < DT_WAIT_LIMIT; ++i) {
+    const unsigned limit = c_dt_limit;
+    for (unsigned i = 0; i < limit; ++i) {
         unsigned done;
         asm volatile("{\n\t.reg .pred p;\n\t"
                      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -49,7 +51,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int whe
                      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
     }
-    atomicCAS(&g_dt_error, 0, 1 + where);
+    dt_give_up(where);
     return false;
 }
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
@@ -129,6 +131,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) decode_tma_kernel(
     // requested like the others although the kernel before may still be writing that one row:
     // the row is put in place from registers after the wait (see own_row below)
     auto issue = [&](int it) {
+        if (c_dt_skip) return;                               // (tests: no copy is ever in flight)
         const int key0 = w_first + it * NB;
         const int key_b0 = key0 + pb * box_rows;
         bool valid = bidx < n_box && key_b0 <= pos;
@@ -446,10 +449,4 @@ ZLLM_API int zllm_attention_decode_tma(const void* qkv, void* out, const int* ro
     return ZLLM_ERR_UNSUPPORTED;
 }
 
-// The device flag that a bounded wait sets when it gives up (0: none); reading clears it.
-ZLLM_API int zllm_attention_decode_tma_error(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_dt_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_dt_error, &zero, sizeof(int));
-    return v;
-}
+ZLLM_WAIT_EXPORTS(dt, attention_decode_tma)

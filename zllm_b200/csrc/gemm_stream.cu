@@ -27,6 +27,7 @@
 // Every wait on an mbarrier is bounded; a CTA whose wait ran out records where, still walks
 // through every barrier its cluster expects, frees its tensor memory and returns.
 #include "common.cuh"
+#include "wait_hooks.cuh"
 #include <cuda.h>
 #include <cooperative_groups.h>
 namespace cg = cooperative_groups;
@@ -43,7 +44,7 @@ namespace cg = cooperative_groups;
 #define GS_WAIT_LIMIT (1u << 24)
 #define GS_THREADS 192
 
-__device__ int g_gs_error = 0;          // 0 ok; else 1 + index of the wait that gave up
+ZLLM_WAIT_STATE(gs, GS_WAIT_LIMIT)
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
@@ -53,7 +54,8 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int where) {
-    for (unsigned i = 0; i < GS_WAIT_LIMIT; ++i) {
+    const unsigned limit = c_gs_limit;
+    for (unsigned i = 0; i < limit; ++i) {
         unsigned done;
         asm volatile("{\n\t.reg .pred p;\n\t"
                      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -61,7 +63,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int whe
                      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
     }
-    atomicCAS(&g_gs_error, 0, 1 + where);
+    gs_give_up(where);
     return false;
 }
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
@@ -163,7 +165,7 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_stream_kernel(const __grid_co
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             bool ok = true;
-            const int pre = min(stages, n_it);
+            const int pre = c_gs_skip ? 0 : min(stages, n_it);            // (tests: no copy is issued at all)
             // the weights do not depend on the kernel before: request the first stages, then wait
             for (int i = 0; i < pre; ++i) {
                 mbar_expect_tx(bars + 8 * i, STAGE_BYTES);
@@ -178,11 +180,12 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_stream_kernel(const __grid_co
                 ok = mbar_wait(bars + 8 * (GS_MAX_STAGES + s), ((g / stages) & 1) ^ 1, 0);   // stage is free
                 if (!ok) break;
                 const unsigned full = bars + 8 * s;
+                if (c_gs_skip) continue;
                 mbar_expect_tx(full, STAGE_BYTES);
                 tma_load_2d(base + s * STAGE_BYTES, &map_w, (it0 + g) * GS_BK, n0, full);
                 tma_load_2d(base + s * STAGE_BYTES + GS_W_BYTES, &map_x, (it0 + g) * GS_BK, 0, full);
             }
-            if (!ok)                                                     // the copies already issued must land
+            if (!ok && !c_gs_skip)                                       // the copies already issued must land
                 for (int q = max(0, g - stages); q < g; ++q) mbar_wait(bars + 8 * (q % stages), (q / stages) & 1, 1);
         }
     } else if (warp == 1) {
@@ -412,10 +415,4 @@ ZLLM_API int zllm_gemm_stream_bf16(const void* x, const void* w, void* out, int 
     return launch_stream<64>(map_w, map_x, p, s);
 }
 
-// The device flag that a bounded wait sets when it gives up (0: none); reading clears it.
-ZLLM_API int zllm_gemm_stream_error(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_gs_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_gs_error, &zero, sizeof(int));
-    return v;
-}
+ZLLM_WAIT_EXPORTS(gs, gemm_stream)

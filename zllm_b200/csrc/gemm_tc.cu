@@ -18,6 +18,7 @@
 // Every wait on an mbarrier is bounded: when a limit runs out the kernel records where in
 // a device flag, drains what it started, frees its tensor memory and returns.
 #include "common.cuh"
+#include "wait_hooks.cuh"
 #include <cuda.h>
 
 #define MODE_STORE 0
@@ -37,7 +38,7 @@
 #define TC_SMEM_OF(BN) (TC_STAGES_OF(BN) * TC_STAGE_BYTES_OF(BN) + 1024 /* alignment */ + 256 /* barriers */ + 4 * 2 * 4096 /* output staging */)
 #define TC_WAIT_LIMIT (1u << 24)
 
-__device__ int g_tc_error = 0;       // 0 ok; else 1 + index of the wait that gave up
+ZLLM_WAIT_STATE(tc, TC_WAIT_LIMIT)
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -49,7 +50,8 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
 }
 // Bounded wait: false if the phase did not complete within the limit.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int where) {
-    for (unsigned i = 0; i < TC_WAIT_LIMIT; ++i) {
+    const unsigned limit = c_tc_limit;
+    for (unsigned i = 0; i < limit; ++i) {
         unsigned done;
         asm volatile("{\n\t.reg .pred p;\n\t"
                      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -57,7 +59,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, int whe
                      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
     }
-    atomicCAS(&g_tc_error, 0, 1 + where);
+    tc_give_up(where);
     return false;
 }
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
@@ -227,13 +229,14 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                     ok = mbar_wait(bars + 8 * (NSTAGE + s), ((g / NSTAGE) & 1) ^ 1, 0);   // stage is free
                     if (!ok) break;
                     const unsigned full = bars + 8 * s;
+                    if (c_tc_skip) continue;                             // (tests: nothing is ever in flight)
                     mbar_expect_tx(full, STAGE_BYTES);
                     const unsigned a_dst = base + s * STAGE_BYTES;
                     tma_load_2d(a_dst, &map_x, (k_lo + it) * TC_BK, m0, full);
                     tma_load_2d(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full);
                 }
             }
-            if (!ok) {
+            if (!ok && !c_tc_skip) {
                 // drain: the copies already issued must land before the CTA may exit
                 for (int q = max(0, g - NSTAGE); q < g; ++q) mbar_wait(bars + 8 * (q % NSTAGE), (q / NSTAGE) & 1, 1);
             }
@@ -556,10 +559,4 @@ ZLLM_API int zllm_gemm_tc_force_tile(int bn) {
     return 0;
 }
 
-// The device flag that a bounded wait sets when it gives up (0: none); reading clears it.
-ZLLM_API int zllm_gemm_tc_error(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
-    return v;
-}
+ZLLM_WAIT_EXPORTS(tc, gemm_tc)

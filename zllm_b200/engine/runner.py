@@ -427,10 +427,12 @@ class ModelRunner:
             ev.record()
         return {"host": host, "event": ev, "n": n, "key": key, "slots": slots}
 
-    @staticmethod
-    def decode_collect(handle) -> List[int]:
+    def decode_collect(self, handle) -> List[int]:
         if handle["event"] is not None:
             handle["event"].synchronize()
+        check = getattr(self.ops, "raise_if_a_wait_gave_up", None)
+        if check is not None:
+            check()                 # a kernel whose bounded wait ran out has flagged it by now
         return handle["host"][:handle["n"]].tolist()
 
     def _decode_body(self, g):

@@ -52,6 +52,7 @@ class CudaOps:
         self._bound_stream = None
         self._tc_scratch = None
         self._kv_maps = {}
+        self._error_words = None
         self.launches = 0
         self.profiling = os.environ.get("ZLLM_PROFILE", "") not in ("", "0")
         if self.profiling:
@@ -113,6 +114,16 @@ class CudaOps:
         build.build(names)
         for n in names:
             self._libs[n] = build.load(n)
+        # a word of pinned host memory per kernel family with bounded waits: a wait that gives up
+        # writes its code there too, so the engine sees it where it synchronises anyway, without a copy
+        if self._error_words is None:
+            self._error_words = torch.zeros(len(self.WAIT_FAMILIES), dtype=torch.int32).pin_memory()
+        for i, (name, prefix) in enumerate(self.WAIT_FAMILIES):
+            lib = self._libs.get(name)
+            if lib is not None:
+                code = getattr(lib, prefix + "_set_error_mirror")(c_void_p(self._error_words.data_ptr() + 4 * i))
+                if code != 0:
+                    raise BackendError(f"{name}: cannot set the error mirror (CUDA error {code})")
 
     def lib(self, name):
         lib = self._libs.get(name)
@@ -329,16 +340,40 @@ class CudaOps:
             return True
         return False
 
+    WAIT_FAMILIES = (("gemm_tc", "zllm_gemm_tc"), ("gemm_stream", "zllm_gemm_stream"),
+                     ("attention_decode_tma", "zllm_attention_decode_tma"),
+                     ("attention_prefill_tc", "zllm_attention_prefill_tc"))
+
     def check_async_errors(self):
         """Raise if a kernel's bounded wait gave up since the last call (synchronises the device)."""
-        for name, fn in (("gemm_tc", "zllm_gemm_tc_error"), ("gemm_stream", "zllm_gemm_stream_error"),
-                         ("attention_decode_tma", "zllm_attention_decode_tma_error"),
-                         ("attention_prefill_tc", "zllm_attention_prefill_tc_error")):
+        found = None
+        for i, (name, prefix) in enumerate(self.WAIT_FAMILIES):
             lib = self._libs.get(name)
             if lib is not None:
-                v = getattr(lib, fn)()
-                if v != 0:
-                    raise BackendError(f"{name}: a bounded wait ran out (code {v}); results of that launch are invalid")
+                v = getattr(lib, prefix + "_error")()
+                if v != 0 and found is None:
+                    found = (name, v)
+        if self._error_words is not None:
+            self._error_words.zero_()
+        if found is not None:
+            raise BackendError(f"{found[0]}: a bounded wait ran out (code {found[1]}); results of that launch are invalid")
+
+    def raise_if_a_wait_gave_up(self):
+        """The same check without touching the device: reads the pinned words the kernels mirror
+        their error codes into.  For the places where the engine has just synchronised."""
+        w = self._error_words
+        if w is not None and bool(w.any()):
+            self.check_async_errors()                    # names the kernel, clears the flags, raises
+            raise BackendError("a bounded wait ran out; results of that launch are invalid")
+
+    def set_wait_test_hook(self, family: str, limit: int = 0, skip_loads: bool = False):
+        """Tests: lower a kernel family's wait limit to ``limit`` polls (0: the default) and, with
+        ``skip_loads``, make its producer issue no copy, so that its waits for data run out with
+        nothing in flight and the kernel's give-up path runs."""
+        prefix = dict(self.WAIT_FAMILIES)[family]
+        code = getattr(self.lib(family), prefix + "_test_hook")(ctypes.c_uint(limit), c_int(1 if skip_loads else 0))
+        if code != 0:
+            raise BackendError(f"{family}: test hook failed (CUDA error {code})")
 
     # ---- silu * up -----------------------------------------------------
     def silu_mul(self, a, b, out):

@@ -151,4 +151,7 @@ class Sampler:
         self.seeds[:R].copy_(s)
         self.ops.sample(logits[:R], self.temps[:R], self.seeds[:R], self.out[:R])
         toks = self.out[:R].cpu().tolist()
+        check = getattr(self.ops, "raise_if_a_wait_gave_up", None)
+        if check is not None:
+            check()                 # the copy above waited for the step: a wait that ran out has flagged it
         return self.host_finish(logits, toks, params, seeds)
