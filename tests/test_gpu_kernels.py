@@ -528,9 +528,9 @@ def test_linear_with_norm_prologue(ops, M, N, K, mode, wdtype):
     assert err <= 2 ** -7 * max(1.0, float(want.abs().max())), err
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 13, 16, 20])
+@pytest.mark.parametrize("M", [1, 3, 8, 13, 16, 20, 70, 200, 333])      # from 65 rows: the epilogue of the tensor-core product
 @pytest.mark.parametrize("nq,nkv,hd,inter", [(4, 2, 16, False), (3, 1, 32, True), (8, 2, 64, False), (2, 1, 128, False),
-                                             (5, 5, 48, True)])
+                                             (5, 5, 48, True), (5, 1, 64, False), (3, 3, 128, False)])
 @pytest.mark.parametrize("with_norm", [False, True])
 def test_qkv_product_with_rope_and_cache_write(ops, M, nq, nkv, hd, inter, with_norm):
     """The fused QKV product (norm prologue, rotation and cache write in the epilogue) against
@@ -544,11 +544,21 @@ def test_qkv_product_with_rope_and_cache_write(ops, M, nq, nkv, hd, inter, with_
     rot = Rotary(hd, 10000.0, 300, interleaved=inter)
     rot.bind(Runtime(dtype, torch.device(DEV), ops))
     bs = 6
-    cm = make_cache(nkv, hd, bs, 500, M + 1, 200, dtype)
-    slots = [cm.admit() for _ in range(M)]
-    for i, s in enumerate(slots):
-        make_ctx(cm, [(s, 3 + 5 * i)])                   # every request at another position
-    ctx = make_ctx(cm, [(s, 1) for s in slots])
+    if M <= 20:
+        cm = make_cache(nkv, hd, bs, 500, M + 1, 200, dtype)
+        slots = [cm.admit() for _ in range(M)]
+        for i, s in enumerate(slots):
+            make_ctx(cm, [(s, 3 + 5 * i)])               # every request at another position
+        ctx = make_ctx(cm, [(s, 1) for s in slots])
+    else:
+        # many rows: three portions that start anywhere (a page's edge, mid-page) beside two decoded rows
+        cm = make_cache(nkv, hd, bs, 500, 6, 280, dtype)
+        slots = [cm.admit() for _ in range(5)]
+        for s, n in zip(slots, (12, 5, 30, 7, 1)):
+            make_ctx(cm, [(s, n)])
+        a = (M - 2) // 3
+        ctx = make_ctx(cm, [(slots[0], a), (slots[1], 1), (slots[2], a), (slots[3], 1), (slots[4], M - 2 - 2 * a)])
+        assert ctx.T == M
     N = (nq + 2 * nkv) * hd
     w = rnd((N, H), dtype, 31, H ** -0.5)
     x32 = rnd((M, H), torch.float32, 32, 2.0)

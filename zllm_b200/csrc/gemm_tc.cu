@@ -24,6 +24,7 @@
 #define MODE_STORE 0
 #define MODE_ADD 1
 #define MODE_SWIGLU 2
+#define MODE_ROPE 3                     // QKV: q and k heads rotated (half-split pairs), k and v also written to cache pages
 
 #define TC_BM 128
 #define TC_BN 256                       // weight rows per tile; TC_BN_HALF for products with few tiles
@@ -168,6 +169,46 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x,
                  ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
 }
 
+// What the rope epilogue needs (mode MODE_ROPE; N = (nq + 2 nkv) * hd, hd 64 or 128, tile width a
+// multiple of hd so that no head straddles a tile).
+struct TcRope {
+    const int* positions;   // [M]
+    const int* row_slot;    // [M]; < 0: padding row (nothing goes to the cache)
+    const float* cos_t;     // [max_pos][hd / 2] or null (no rotation)
+    const float* sin_t;
+    bf16* k_pages;          // [pages][nkv][bs][hd] or null when store == 0
+    bf16* v_pages;
+    const int* table;       // [slots][max_blocks]
+    int max_blocks, bs, nq, nkv, hd, store;
+};
+
+// Rotate 32 pairs (a[j], b[j]) = (dims d0 + j, d0 + j + hd / 2) of one head of one row.
+__device__ __forceinline__ void tc_rotate32(unsigned (&a)[32], unsigned (&b)[32], const float* cs, const float* sn) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        const float4 c = *reinterpret_cast<const float4*>(cs + j), s = *reinterpret_cast<const float4*>(sn + j);
+        const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float x = __uint_as_float(a[j + e]), y = __uint_as_float(b[j + e]);
+            a[j + e] = __float_as_uint(x * cc[e] - y * ss[e]);
+            b[j + e] = __float_as_uint(x * ss[e] + y * cc[e]);
+        }
+    }
+}
+// 32 float32 values of one row as bfloat16 to 64 bytes of global memory (a piece of a cache row).
+__device__ __forceinline__ void tc_store32_bf16(bf16* dst, const unsigned (&r)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        uint4 pk;
+        pk.x = pack2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+        pk.y = pack2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        pk.z = pack2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+        pk.w = pack2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+        *reinterpret_cast<uint4*>(dst + j) = pk;
+    }
+}
+
 // Persistent: a CTA walks the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles
 // fastest, so the CTAs running at the same time share weight panels in L2).  Two accumulators
 // of 256 columns live in TMEM: while the epilogue warps drain one, the MMA warp fills the other.
@@ -175,7 +216,8 @@ template <int BN>
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                          const __grid_constant__ CUtensorMap map_w,
                                                          const __grid_constant__ CUtensorMap map_o, int M, int N, int K,
-                                                         int mode, int out_bf16, int tiles_m, int tiles_n, int splits) {
+                                                         int mode, int out_bf16, int tiles_m, int tiles_n, int splits,
+                                                         const TcRope rope) {
     constexpr int NSTAGE = TC_STAGES_OF(BN);
     constexpr int STAGE_BYTES = TC_STAGE_BYTES_OF(BN);
     extern __shared__ unsigned char smem_raw[];
@@ -297,8 +339,62 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
             if (!ok) break;
             const unsigned t_row = tmem_acc + buf * BN + ((unsigned)(q * 32) << 16);
             const int n_limit = mode == MODE_SWIGLU ? 2 * N : N;
+            if (mode == MODE_ROPE) {
+                // ---- QKV with rotation and cache write: per head of the tile, the 32-column pieces
+                // j and j + hd/2 together (a rotation pair sits in the same thread = row) ----
+                const int row = y + lane;
+                const bool row_ok = row < M;
+                const int pos = row_ok ? rope.positions[row] : 0;
+                const int slot = row_ok ? rope.row_slot[row] : -1;
+                const int half = rope.hd >> 1;
+                size_t kv_row = 0;                                       // + kvh * bs * hd: this row's place in a page
+                bool to_cache = false;
+                if (rope.store && slot >= 0) {
+                    const int page = rope.table[(size_t)slot * rope.max_blocks + pos / rope.bs];
+                    if (page >= 0) {
+                        to_cache = true;
+                        kv_row = ((size_t)page * rope.nkv * rope.bs + (size_t)(pos % rope.bs)) * rope.hd;
+                    }
+                }
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
+                for (int h0 = 0; h0 < BN; h0 += rope.hd) {
+                    if (n0 + h0 >= N) break;                             // warp-uniform
+                    const int head = (n0 + h0) / rope.hd;
+                    const bool rotated = head < rope.nq + rope.nkv && rope.cos_t != nullptr;
+#pragma unroll 1
+                    for (int j = 0; j < half; j += 32) {
+                        unsigned ra[32], rb[32];
+                        tmem_ld32(t_row + h0 + j, ra);
+                        tmem_ld32(t_row + h0 + half + j, rb);
+                        if (y >= M) continue;                            // warp-uniform: no row of this warp exists
+                        if (rotated && row_ok)
+                            tc_rotate32(ra, rb, rope.cos_t + (size_t)pos * half + j, rope.sin_t + (size_t)pos * half + j);
+                        if (to_cache && head >= rope.nq) {
+                            const bool is_k = head < rope.nq + rope.nkv;
+                            const int kvh = is_k ? head - rope.nq : head - rope.nq - rope.nkv;
+                            bf16* dst = (is_k ? rope.k_pages : rope.v_pages) + kv_row + (size_t)kvh * rope.bs * rope.hd;
+                            tc_store32_bf16(dst + j, ra);
+                            tc_store32_bf16(dst + half + j, rb);
+                        }
+#pragma unroll
+                        for (int part = 0; part < 2; ++part) {           // both pieces also go to the qkv buffer
+                            unsigned char* stage = stage0 + (n_staged & 1) * 4096;
+                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                            __syncwarp();
+                            tc_stage32(part ? rb : ra, stage, lane, MODE_STORE, 1);
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            __syncwarp();
+                            if (lane == 0) {
+                                tma_store_2d(&map_o, n0 + h0 + j + part * half, y, smem_u32(stage));
+                                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            }
+                            ++n_staged;
+                        }
+                    }
+                }
+            }
+#pragma unroll 1
+            for (int c = 0; c < BN && mode != MODE_ROPE; c += 32) {
                 if (n0 + c >= n_limit) break;                            // warp-uniform
                 unsigned r[32];
                 tmem_ld32(t_row + c, r);
@@ -475,10 +571,10 @@ static int make_part_map(CUtensorMap* map, void* ptr, int splits, int M, int w_r
 // then split over more CTAs and summed in a second pass, in a fixed order.
 static int g_force_bn = 0;
 
-ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_bf16,
-                               void* scratch, long long scratch_bytes, void* stream) {
+static int tc_launch(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_bf16, void* scratch,
+                     long long scratch_bytes, void* stream, const TcRope& rope) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K % 8) || (N % 8) || mode < 0 || mode > 2) return ZLLM_ERR_UNSUPPORTED;
+    if (K <= 0 || (K % 8) || (N % 8) || mode < 0 || mode > 3) return ZLLM_ERR_UNSUPPORTED;
     if (mode == MODE_ADD && out_bf16) return ZLLM_ERR_UNSUPPORTED;
     if ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15)) return ZLLM_ERR_UNSUPPORTED;
     const int w_rows = mode == MODE_SWIGLU ? 2 * N : N;
@@ -501,21 +597,22 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
     // depends on the sizes only.
     const int k_all = (K + TC_BK - 1) / TC_BK;
     int bn = tiles_m * ((w_rows + TC_BN - 1) / TC_BN) * 2 <= n_sm && (k_all <= 64 || tiles_m <= 2) ? TC_BN_HALF : TC_BN;
+    if (mode == MODE_ROPE && bn % rope.hd) bn = TC_BN;             // no head may straddle a tile
     if (bn == TC_BN) {
         // More tiles than SMs: the time is the number of waves times the tile's width.  Tiles of 192
         // weight rows when that product is smaller (192 tiles of 256 rows on 148 SMs are two waves
         // with the second a third full; 256 tiles of 192 rows are two waves of three quarters the work).
         auto cost = [&](int w) { const long long t = (long long)tiles_m * ((w_rows + w - 1) / w); return ((t + n_sm - 1) / n_sm) * w; };
-        if (cost(TC_BN_MID) < cost(TC_BN)) bn = TC_BN_MID;
+        if (cost(TC_BN_MID) < cost(TC_BN) && !(mode == MODE_ROPE && TC_BN_MID % rope.hd)) bn = TC_BN_MID;
     }
-    if (g_force_bn) bn = g_force_bn;
+    if (g_force_bn && !(mode == MODE_ROPE && g_force_bn % rope.hd)) bn = g_force_bn;
     e = make_map(&map_w, w, w_rows, K, bn);
     if (e) return e;
     const int tiles_n = (w_rows + bn - 1) / bn;
     // still few tiles: split K until about every SM has a unit of work, each with at least 4 k
     // steps, and sum the slices in a second pass, in a fixed order
     int splits = 1;
-    while (tiles_n * tiles_m * splits * 2 <= n_sm && k_all / (splits * 2) >= 4 && splits < 32) splits *= 2;
+    while (mode != MODE_ROPE && tiles_n * tiles_m * splits * 2 <= n_sm && k_all / (splits * 2) >= 4 && splits < 32) splits *= 2;
     if (splits > 1 && (scratch == nullptr || (long long)splits * M * w_rows * 4 > scratch_bytes || (w_rows % 4) ||
                        ((uintptr_t)scratch & 15)))
         splits = 1;
@@ -537,19 +634,44 @@ ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, i
     }
     if (bn == TC_BN)
         gemm_tc_kernel<TC_BN><<<grid, 192, TC_SMEM_OF(TC_BN), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode, out_bf16,
-                                                                                       tiles_m, tiles_n, splits);
+                                                                                       tiles_m, tiles_n, splits, rope);
     else if (bn == TC_BN_MID)
         gemm_tc_kernel<TC_BN_MID><<<grid, 192, TC_SMEM_OF(TC_BN_MID), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode,
-                                                                                               out_bf16, tiles_m, tiles_n, splits);
+                                                                                               out_bf16, tiles_m, tiles_n, splits, rope);
     else
         gemm_tc_kernel<TC_BN_HALF><<<grid, 192, TC_SMEM_OF(TC_BN_HALF), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode,
-                                                                                                 out_bf16, tiles_m, tiles_n, splits);
+                                                                                                 out_bf16, tiles_m, tiles_n, splits, rope);
     int rc = launch_status();
     if (rc || splits == 1) return rc;
     const long long n_thr = (long long)M * (N / 4);
     gemm_tc_reduce_kernel<<<(unsigned)((n_thr + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
         (const float*)scratch, splits, M, w_rows, out, N, mode, out_bf16);
     return launch_status();
+}
+
+ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_bf16,
+                               void* scratch, long long scratch_bytes, void* stream) {
+    if (mode < 0 || mode > 2) return ZLLM_ERR_UNSUPPORTED;
+    TcRope none = {};
+    return tc_launch(x, w, out, M, N, K, mode, out_bf16, scratch, scratch_bytes, stream, none);
+}
+
+// qkv [M, (nq + 2 nkv) * hd] = x w^T with q and k heads rotated (half-split pairs over the whole
+// head; cos / sin [max_pos][hd / 2] float32, null: no rotation) and, when ``store``, k and v of
+// every row with a slot >= 0 written to the page of its position: the QKV product of a prompt
+// portion with what used to be a pass of its own over qkv.  hd 64 or 128.
+ZLLM_API int zllm_gemm_tc_qkv_rope(const void* x, const void* w, void* qkv, int M, int K, const int* positions,
+                                   const int* row_slot, const float* cos_t, const float* sin_t, int nq, int nkv, int hd,
+                                   void* k_pages, void* v_pages, const int* table, int max_blocks, int bs, int store,
+                                   void* stream) {
+    if ((hd != 64 && hd != 128) || nq <= 0 || nkv <= 0 || (store && (bs <= 0 || max_blocks <= 0 || !k_pages || !v_pages || !table)))
+        return ZLLM_ERR_UNSUPPORTED;
+    if (((uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)cos_t | (uintptr_t)sin_t) & 15) return ZLLM_ERR_UNSUPPORTED;
+    TcRope r;
+    r.positions = positions; r.row_slot = row_slot; r.cos_t = cos_t; r.sin_t = sin_t;
+    r.k_pages = (bf16*)k_pages; r.v_pages = (bf16*)v_pages; r.table = table;
+    r.max_blocks = max_blocks; r.bs = bs; r.nq = nq; r.nkv = nkv; r.hd = hd; r.store = store;
+    return tc_launch(x, w, qkv, M, (nq + 2 * nkv) * hd, K, MODE_ROPE, 1, nullptr, 0, stream, r);
 }
 
 // Tests: force the tile width (128 or 256 weight rows; 0: by the sizes).

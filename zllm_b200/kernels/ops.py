@@ -311,6 +311,27 @@ class CudaOps:
             h = ws.get("normed", (M, K), self.dtype)
             self.rmsnorm(x, norm_w, eps, h)
             x = h
+        # many rows: rotation and cache write in the epilogue of the tensor-core product (head sizes
+        # 64 and 128, half-split pairs over the whole head); otherwise a pass of their own over qkv
+        if M > self.STREAM_MAX_ROWS and "gemm_tc" in self._libs and x.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16 \
+                and w_qkv.dtype == torch.bfloat16 and hd in (64, 128) and K % 8 == 0 \
+                and (rot is None or (rot.rot_dim == hd and not rot.interleaved)) \
+                and (x.data_ptr() | w_qkv.data_ptr() | qkv.data_ptr()) & 15 == 0:
+            self._dev(ctx.positions, ctx.row_slot)
+            if ctx.positions.numel() != M or ctx.row_slot.numel() != M:
+                raise BackendError("qkv_rope_store: the step's rows do not match qkv")
+            if write_cache:
+                self._check_cache(cache, nkv, hd, qkv.dtype, "qkv_rope_store")
+                kp, vp, tb, mb, bs = cache.k_pages, cache.v_pages, cache.block_table, cache.block_table.shape[1], cache.block_size
+            else:
+                kp = vp = tb = None
+                mb = bs = 1
+            code = self.lib("gemm_tc").zllm_gemm_tc_qkv_rope(
+                _ptr(x), _ptr(w_qkv), _ptr(qkv), c_int(M), c_int(K), _ptr(ctx.positions), _ptr(ctx.row_slot),
+                _ptr(rot.cos if rot is not None else None), _ptr(rot.sin if rot is not None else None), c_int(nq), c_int(nkv),
+                c_int(hd), _ptr(kp), _ptr(vp), _ptr(tb), c_int(mb), c_int(bs), c_int(1 if write_cache else 0), self._stream())
+            self._check(code, "gemm_tc_qkv_rope")
+            return
         self.linear(x, w_qkv, qkv, "store")
         self.rope_kv_store(qkv, ctx, rot, cache, nq, nkv, hd, write_cache)
 
