@@ -137,17 +137,22 @@ STREAM_K_SHAPES = [  # more tiles than SMs, so that the tile width is chosen by 
 ]
 
 
+@pytest.mark.parametrize("pair", [-1, 0])
 @pytest.mark.parametrize("tile", [0, 128, 192, 256])
 @pytest.mark.parametrize("M,N,K,mode", SPLIT_K_SHAPES + STREAM_K_SHAPES +
                          [(700, 1288, 520, "store"), (1100, 640, 264, "swiglu"), (640, 904, 1032, "add")])
-def test_many_row_product_with_split_k(ops, M, N, K, mode, tile):
+def test_many_row_product_with_split_k(ops, M, N, K, mode, tile, pair):
     """``tile``: the kernel's tile width forced to 128, 192 or 256 weight rows (0: chosen by the sizes),
-    so that both shapes run at every size."""
-    assert ops.lib("gemm_tc").zllm_gemm_tc_force_tile(tile) == 0
+    so that both shapes run at every size.  ``pair``: -1, pairs of CTAs on tiles of 256 rows wherever
+    there is more than one row tile (a last row tile without a partner included: 300, 640, 700,
+    1100, 1900 rows); 0, single CTAs on tiles of 128 rows everywhere."""
+    lib = ops.lib("gemm_tc")
+    assert lib.zllm_gemm_tc_force_tile(tile) == 0 and lib.zllm_gemm_tc_force_pair(pair) == 0
     try:
         _many_row_product(ops, M, N, K, mode)
     finally:
-        ops.lib("gemm_tc").zllm_gemm_tc_force_tile(0)
+        lib.zllm_gemm_tc_force_tile(0)
+        lib.zllm_gemm_tc_force_pair(-1)
 
 
 def _many_row_product(ops, M, N, K, mode):

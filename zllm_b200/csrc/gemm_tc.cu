@@ -37,6 +37,11 @@
 #define TC_STAGES_OF(BN) ((BN) == TC_BN_HALF ? 6 : TC_STAGES)  // about the same shared memory either way
 #define TC_TMEM_COLS(BN) (2 * (BN) <= 256 ? 256 : 512)         // two accumulators; the allocation is a power of two
 #define TC_SMEM_OF(BN) (TC_STAGES_OF(BN) * TC_STAGE_BYTES_OF(BN) + 1024 /* alignment */ + 256 /* barriers */ + 4 * 2 * 4096 /* output staging */)
+// A pair of CTAs (a cluster of two, tcgen05 cta_group::2) on one 256 x BN tile: each CTA loads its
+// 128 rows of x and HALF of the tile's weight rows, so a k step costs it a third less traffic.
+#define TC_PAIR_STAGES 6
+#define TC_PAIR_STAGE_BYTES_OF(BN) (TC_A_BYTES + ((BN) / 2) * TC_BK * 2)
+#define TC_PAIR_SMEM_OF(BN) (TC_PAIR_STAGES * TC_PAIR_STAGE_BYTES_OF(BN) + 1024 + 256 + 4 * 2 * 4096)
 #define TC_WAIT_LIMIT (1u << 24)
 
 ZLLM_WAIT_STATE(tc, TC_WAIT_LIMIT)
@@ -76,6 +81,36 @@ __device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long adesc
                  "setp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The forms for a pair of CTAs: the copy signals a barrier that may live in the other CTA, the MMA
+// reads both CTAs' shared memory and writes both CTAs' tensor memory, the commit arrives in both.
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar_cluster) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc,
+                                            unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ unsigned map_to_cta(unsigned addr, unsigned rank) {   // the same shared address in another CTA of the cluster
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -212,14 +247,23 @@ __device__ __forceinline__ void tc_store32_bf16(bf16* dst, const unsigned (&r)[3
 // Persistent: a CTA walks the tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles
 // fastest, so the CTAs running at the same time share weight panels in L2).  Two accumulators
 // of 256 columns live in TMEM: while the epilogue warps drain one, the MMA warp fills the other.
-template <int BN>
+//
+// PAIR: two CTAs of a cluster share a tile of 256 rows (this CTA: rows m0 + 128 * rank) and BN
+// weight rows, of which each loads half.  Only the first CTA issues MMAs (M = 256 over both);
+// its "full" barriers count the bytes of both CTAs' copies, its commits arrive in both, and
+// both CTAs' epilogue warps arrive on its "accumulator drained" barriers.
+template <int BN, int PAIR>
 __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                                                          const __grid_constant__ CUtensorMap map_w,
                                                          const __grid_constant__ CUtensorMap map_o, int M, int N, int K,
                                                          int mode, int out_bf16, int tiles_m, int tiles_n, int splits,
                                                          const TcRope rope) {
-    constexpr int NSTAGE = TC_STAGES_OF(BN);
-    constexpr int STAGE_BYTES = TC_STAGE_BYTES_OF(BN);
+    constexpr int NSTAGE = PAIR ? TC_PAIR_STAGES : TC_STAGES_OF(BN);
+    constexpr int STAGE_BYTES = PAIR ? TC_PAIR_STAGE_BYTES_OF(BN) : TC_STAGE_BYTES_OF(BN);
+    constexpr int ROWS_PER_TILE = PAIR ? 2 * TC_BM : TC_BM;
+    const int rank = PAIR ? (int)cluster_cta_rank() : 0;
+    const int walker = PAIR ? blockIdx.x >> 1 : blockIdx.x;                // which tile walker this CTA (pair) is
+    const int n_walkers = PAIR ? gridDim.x >> 1 : gridDim.x;
     extern __shared__ unsigned char smem_raw[];
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;         // swizzled tiles need 1024-byte alignment
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -243,17 +287,24 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full + 8 * b, 1);                          // accumulator complete: one tcgen05.commit
-            mbar_init(bar_acc_empty + 8 * b, 4);                         // accumulator drained: one arrive per epilogue warp
+            mbar_init(bar_acc_empty + 8 * b, PAIR ? 8 : 4);              // accumulator drained: one arrive per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {                                                     // this warp owns the tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(TC_TMEM_COLS(BN)) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {                                                      // (of a pair: the same warp of both CTAs, the same slot)
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_slot)), "r"(TC_TMEM_COLS(BN)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_slot)), "r"(TC_TMEM_COLS(BN)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();                                        // the other CTA's barriers exist before anything signals them
     tc_fence_after();
     const unsigned tmem_acc = *tmem_slot;
 
@@ -262,9 +313,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         if (lane == 0) {
             bool ok = true;
             int g = 0;                                                   // k steps issued over all tiles
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = walker; tile < total_tiles && ok; tile += n_walkers) {
                 const int ks = tile % splits, t2 = tile / splits;
-                const int m0 = (t2 % tiles_m) * TC_BM, n0 = (t2 / tiles_m) * BN;
+                const int m0 = (t2 % tiles_m) * ROWS_PER_TILE + rank * TC_BM;
+                const int n0 = (t2 / tiles_m) * BN + (PAIR ? rank * (BN / 2) : 0);   // of a pair: this CTA's half of the weight rows
                 const int k_lo = ks * k_per, k_iters = max(0, min(k_all, k_lo + k_per) - k_lo);
                 for (int it = 0; it < k_iters; ++it, ++g) {
                     const int s = g % NSTAGE;
@@ -272,27 +324,36 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                     if (!ok) break;
                     const unsigned full = bars + 8 * s;
                     if (c_tc_skip) continue;                             // (tests: nothing is ever in flight)
-                    mbar_expect_tx(full, STAGE_BYTES);
                     const unsigned a_dst = base + s * STAGE_BYTES;
-                    tma_load_2d(a_dst, &map_x, (k_lo + it) * TC_BK, m0, full);
-                    tma_load_2d(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full);
+                    if (PAIR) {
+                        // the first CTA's barrier counts both CTAs' bytes; a copy may complete on it
+                        // before the expectation is posted: the phase still waits for that arrival
+                        if (rank == 0) mbar_expect_tx(full, 2 * STAGE_BYTES);
+                        const unsigned full0 = map_to_cta(full, 0);
+                        tma_load_2d_pair(a_dst, &map_x, (k_lo + it) * TC_BK, m0, full0);
+                        tma_load_2d_pair(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full0);
+                    } else {
+                        mbar_expect_tx(full, STAGE_BYTES);
+                        tma_load_2d(a_dst, &map_x, (k_lo + it) * TC_BK, m0, full);
+                        tma_load_2d(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full);
+                    }
                 }
             }
-            if (!ok && !c_tc_skip) {
+            if (!ok && !c_tc_skip && rank == 0) {
                 // drain: the copies already issued must land before the CTA may exit
                 for (int q = max(0, g - NSTAGE); q < g; ++q) mbar_wait(bars + 8 * (q % NSTAGE), (q / NSTAGE) & 1, 1);
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             // instruction descriptor: D float32 [4,6) = 1, A and B bfloat16 [7,10) = [10,13) = 1, both
-            // K-major, N >> 3 at [17,23), M >> 4 at [24,29)
+            // K-major, N >> 3 at [17,23), M >> 4 at [24,29) (of a pair: M = 256 over both CTAs)
             const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
-                                   ((unsigned)(TC_BM >> 4) << 24);
+                                   ((unsigned)(ROWS_PER_TILE >> 4) << 24);
             bool ok = true;
             int g = 0, j = 0;                                            // k steps consumed; tiles done by this CTA
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+            for (int tile = walker; tile < total_tiles && ok; tile += n_walkers, ++j) {
                 const int buf = j & 1;
                 ok = mbar_wait(bar_acc_empty + 8 * buf, ((j >> 1) & 1) ^ 1, 4);   // the epilogue has drained this accumulator
                 if (!ok) break;
@@ -308,11 +369,15 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                     const unsigned long long adesc = umma_desc(a_addr);
                     const unsigned long long bdesc = umma_desc(a_addr + TC_A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; ++k)                 // 32 bytes along K per step: +2 in the address field
-                        tc_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(bars + 8 * (NSTAGE + s));               // stage free when these MMAs have read it
+                    for (int k = 0; k < TC_BK / 16; ++k) {               // 32 bytes along K per step: +2 in the address field
+                        if (PAIR) tc_mma_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                        else tc_mma(acc, adesc + 2 * k, bdesc + 2 * k, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                    }
+                    if (PAIR) tc_commit_pair(bars + 8 * (NSTAGE + s));   // stage free (in both CTAs) when these MMAs have read it
+                    else tc_commit(bars + 8 * (NSTAGE + s));
                 }
-                tc_commit(bar_acc_full + 8 * buf);                       // accumulator complete (or abandoned)
+                if (PAIR) tc_commit_pair(bar_acc_full + 8 * buf);        // accumulator complete (or abandoned)
+                else tc_commit(bar_acc_full + 8 * buf);
             }
         }
     } else {
@@ -328,9 +393,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         bool ok = true;
         int j = 0;
         unsigned n_staged = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++j) {
+        const unsigned acc_empty0 = PAIR ? map_to_cta(bar_acc_empty, 0) : bar_acc_empty;
+        for (int tile = walker; tile < total_tiles && ok; tile += n_walkers, ++j) {
             const int ks = tile % splits, t2 = tile / splits;
-            const int m0 = (t2 % tiles_m) * TC_BM, n0 = (t2 / tiles_m) * BN;
+            const int m0 = (t2 % tiles_m) * ROWS_PER_TILE + rank * TC_BM, n0 = (t2 / tiles_m) * BN;
             const int buf = j & 1;
             const int y = m0 + q * 32;                                       // first output row of this warp
             const bool empty_slice = ks * k_per >= k_all;                    // no k step: the accumulator holds nothing
@@ -421,16 +487,21 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+            if (lane == 0) {
+                if (PAIR) asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
+                else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+            }
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // all tiles are in global memory
         (void)box_cols;
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();                                        // neither CTA leaves or frees while the other still works
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TC_TMEM_COLS(BN)) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TC_TMEM_COLS(BN)) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TC_TMEM_COLS(BN)) : "memory");
     }
 }
 
@@ -570,6 +641,51 @@ static int make_part_map(CUtensorMap* map, void* ptr, int splits, int M, int w_r
 // scratch (may be null): float32 workspace of scratch_bytes for products with few tiles, whose K is
 // then split over more CTAs and summed in a second pass, in a fixed order.
 static int g_force_bn = 0;
+static int g_force_pair = -1;           // -1: by the sizes; 0: never pairs of CTAs; 1: pairs whenever there are two row tiles
+
+template <int BN, int PAIR>
+static cudaError_t tc_prepare(int* max_walkers, int n_sm) {
+    constexpr int smem = PAIR ? TC_PAIR_SMEM_OF(BN) : TC_SMEM_OF(BN);
+    cudaError_t ce = cudaFuncSetAttribute(gemm_tc_kernel<BN, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (ce != cudaSuccess) return ce;
+    *max_walkers = n_sm;
+    if (PAIR) {
+        // how many pairs the device can hold at once (a GPC with an odd number of SMs leaves one out)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (n_sm / 2));
+        cfg.blockDim = dim3(192);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        int n = 0;
+        ce = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, PAIR>, &cfg);
+        if (ce != cudaSuccess) return ce;
+        *max_walkers = n;
+    }
+    return cudaSuccess;
+}
+
+template <int BN, int PAIR>
+static void tc_start(int walkers, void* stream, const CUtensorMap& map_x, const CUtensorMap& map_w, const CUtensorMap& map_o,
+                     int M, int N, int K, int mode, int out_bf16, int tiles_m, int tiles_n, int splits, const TcRope& rope) {
+    if (!PAIR) {
+        gemm_tc_kernel<BN, 0><<<walkers, 192, TC_SMEM_OF(BN), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode, out_bf16,
+                                                                                      tiles_m, tiles_n, splits, rope);
+        return;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * walkers);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = TC_PAIR_SMEM_OF(BN);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, 1>, map_x, map_w, map_o, M, N, K, mode, out_bf16, tiles_m, tiles_n, splits, rope);
+}
 
 static int tc_launch(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_bf16, void* scratch,
                      long long scratch_bytes, void* stream, const TcRope& rope) {
@@ -583,36 +699,51 @@ static int tc_launch(const void* x, const void* w, void* out, int M, int N, int 
     if (e) return e;
     e = make_out_map(&map_o, out, M, N, out_bf16, mode == MODE_SWIGLU ? 16 : 32);
     if (e) return e;
+    // once: shared-memory limits, and how many CTAs (pairs) the device runs at a time
     static int n_sm = 0;
+    static int cap[3][2];                                          // [width 256, 192, 128][pair]
     if (n_sm == 0) {
-        int dev = 0;
+        int dev = 0, n = 0;
         cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cudaError_t ce = tc_prepare<TC_BN, 0>(&cap[0][0], n);
+        if (ce == cudaSuccess) ce = tc_prepare<TC_BN_MID, 0>(&cap[1][0], n);
+        if (ce == cudaSuccess) ce = tc_prepare<TC_BN_HALF, 0>(&cap[2][0], n);
+        if (ce == cudaSuccess) ce = tc_prepare<TC_BN, 1>(&cap[0][1], n);
+        if (ce == cudaSuccess) ce = tc_prepare<TC_BN_MID, 1>(&cap[1][1], n);
+        if (ce == cudaSuccess) ce = tc_prepare<TC_BN_HALF, 1>(&cap[2][1], n);
+        if (ce != cudaSuccess) return (int)ce;
+        n_sm = n;
     }
-    const int tiles_m = (M + TC_BM - 1) / TC_BM;
+    // Pairs of CTAs on tiles of 256 rows when there are at least two row tiles (and the device holds pairs).
+    int pair = M > TC_BM && cap[0][1] > 0 && cap[1][1] > 0 && cap[2][1] > 0;
+    if (g_force_pair == 0) pair = 0;
+    const int walkers_all = pair ? cap[0][1] : n_sm;               // tile walkers: CTAs, or pairs
+    const int tiles_m = pair ? (M + 2 * TC_BM - 1) / (2 * TC_BM) : (M + TC_BM - 1) / TC_BM;
     // Tiles of 256 weight rows; of 128 when those would leave half of the SMs without a tile.  A
     // narrow tile loads as many bytes of x per k step for half the arithmetic, so with a long K and
     // more than two row tiles the wide tile with K split over more CTAs is the faster one
     // (measured: 512 rows, K 8192: 26.7 us wide, 30.5 us narrow; K 2048: 16.4 and 15.1).  The choice
     // depends on the sizes only.
     const int k_all = (K + TC_BK - 1) / TC_BK;
-    int bn = tiles_m * ((w_rows + TC_BN - 1) / TC_BN) * 2 <= n_sm && (k_all <= 64 || tiles_m <= 2) ? TC_BN_HALF : TC_BN;
+    const int row_tiles = (M + TC_BM - 1) / TC_BM;
+    int bn = tiles_m * ((w_rows + TC_BN - 1) / TC_BN) * 2 <= walkers_all && (k_all <= 64 || row_tiles <= 2) ? TC_BN_HALF : TC_BN;
     if (mode == MODE_ROPE && bn % rope.hd) bn = TC_BN;             // no head may straddle a tile
     if (bn == TC_BN) {
         // More tiles than SMs: the time is the number of waves times the tile's width.  Tiles of 192
         // weight rows when that product is smaller (192 tiles of 256 rows on 148 SMs are two waves
         // with the second a third full; 256 tiles of 192 rows are two waves of three quarters the work).
-        auto cost = [&](int w) { const long long t = (long long)tiles_m * ((w_rows + w - 1) / w); return ((t + n_sm - 1) / n_sm) * w; };
+        auto cost = [&](int w) { const long long t = (long long)tiles_m * ((w_rows + w - 1) / w); return ((t + walkers_all - 1) / walkers_all) * w; };
         if (cost(TC_BN_MID) < cost(TC_BN) && !(mode == MODE_ROPE && TC_BN_MID % rope.hd)) bn = TC_BN_MID;
     }
     if (g_force_bn && !(mode == MODE_ROPE && g_force_bn % rope.hd)) bn = g_force_bn;
-    e = make_map(&map_w, w, w_rows, K, bn);
+    e = make_map(&map_w, w, w_rows, K, pair ? bn / 2 : bn);
     if (e) return e;
     const int tiles_n = (w_rows + bn - 1) / bn;
     // still few tiles: split K until about every SM has a unit of work, each with at least 4 k
     // steps, and sum the slices in a second pass, in a fixed order
     int splits = 1;
-    while (mode != MODE_ROPE && tiles_n * tiles_m * splits * 2 <= n_sm && k_all / (splits * 2) >= 4 && splits < 32) splits *= 2;
+    while (mode != MODE_ROPE && tiles_n * tiles_m * splits * 2 <= walkers_all && k_all / (splits * 2) >= 4 && splits < 32) splits *= 2;
     if (splits > 1 && (scratch == nullptr || (long long)splits * M * w_rows * 4 > scratch_bytes || (w_rows % 4) ||
                        ((uintptr_t)scratch & 15)))
         splits = 1;
@@ -621,26 +752,15 @@ static int tc_launch(const void* x, const void* w, void* out, int M, int N, int 
         if (e) return e;
     }
     const int total = tiles_n * tiles_m * splits;
-    const int grid = total < n_sm ? total : n_sm;                  // one CTA per SM walks the units
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t ce = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_OF(TC_BN));
-        if (ce == cudaSuccess)
-            ce = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN_HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_OF(TC_BN_HALF));
-        if (ce == cudaSuccess)
-            ce = cudaFuncSetAttribute(gemm_tc_kernel<TC_BN_MID>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_OF(TC_BN_MID));
-        if (ce != cudaSuccess) return (int)ce;
-        attr_set = true;
-    }
-    if (bn == TC_BN)
-        gemm_tc_kernel<TC_BN><<<grid, 192, TC_SMEM_OF(TC_BN), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode, out_bf16,
-                                                                                       tiles_m, tiles_n, splits, rope);
-    else if (bn == TC_BN_MID)
-        gemm_tc_kernel<TC_BN_MID><<<grid, 192, TC_SMEM_OF(TC_BN_MID), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode,
-                                                                                               out_bf16, tiles_m, tiles_n, splits, rope);
-    else
-        gemm_tc_kernel<TC_BN_HALF><<<grid, 192, TC_SMEM_OF(TC_BN_HALF), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode,
-                                                                                                 out_bf16, tiles_m, tiles_n, splits, rope);
+    const int bi = bn == TC_BN ? 0 : bn == TC_BN_MID ? 1 : 2;
+    const int walkers = total < cap[bi][pair] ? total : cap[bi][pair];   // one CTA (pair) per SM (two SMs) walks the units
+#define TC_START(BNV) \
+    (pair ? tc_start<BNV, 1>(walkers, stream, map_x, map_w, map_o, M, N, K, mode, out_bf16, tiles_m, tiles_n, splits, rope) \
+          : tc_start<BNV, 0>(walkers, stream, map_x, map_w, map_o, M, N, K, mode, out_bf16, tiles_m, tiles_n, splits, rope))
+    if (bn == TC_BN) TC_START(TC_BN);
+    else if (bn == TC_BN_MID) TC_START(TC_BN_MID);
+    else TC_START(TC_BN_HALF);
+#undef TC_START
     int rc = launch_status();
     if (rc || splits == 1) return rc;
     const long long n_thr = (long long)M * (N / 4);
@@ -678,6 +798,13 @@ ZLLM_API int zllm_gemm_tc_qkv_rope(const void* x, const void* w, void* qkv, int 
 ZLLM_API int zllm_gemm_tc_force_tile(int bn) {
     if (bn != 0 && bn != TC_BN && bn != TC_BN_HALF && bn != TC_BN_MID) return ZLLM_ERR_UNSUPPORTED;
     g_force_bn = bn;
+    return 0;
+}
+
+// Tests and measurements: pairs of CTAs never (0), or by the sizes (-1, the default).
+ZLLM_API int zllm_gemm_tc_force_pair(int mode) {
+    if (mode < -1 || mode > 0) return ZLLM_ERR_UNSUPPORTED;
+    g_force_pair = mode;
     return 0;
 }
 
