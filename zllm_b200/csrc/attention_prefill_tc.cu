@@ -175,6 +175,7 @@ __global__ void __launch_bounds__(PT_THREADS, CTAS) prefill_tc_kernel(
 
     // Heads run fastest over the grid and later tiles (which see more keys) come first, so the
     // CTAs with the most work start first for ALL heads and the short ones fill the tail.
+    pdl_trigger();
     const int* tl = tiles + 4 * (gridDim.y - 1 - blockIdx.y);
     const int row0 = tl[0], n_rows = tl[1], slot = tl[2], pos0 = tl[3];
     if (n_rows <= 0 || slot < 0) return;                     // an empty tile (padding of a tile list of fixed
@@ -215,6 +216,9 @@ __global__ void __launch_bounds__(PT_THREADS, CTAS) prefill_tc_kernel(
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + NSB * PT_KEYS;
+    // barriers, tensor memory and descriptors are ready; q, the pages and the output belong to
+    // the step: nothing of them is touched before the kernel before this one has finished
+    pdl_wait();
 
     if ((warp == 0 || warp == 2) && c_pt_skip) {
         // (tests: the producers issue no copy, every wait for data runs out with nothing in flight)
@@ -510,10 +514,8 @@ static int launch_prefill_tc(const void* qkv, int T, void* out, const int* tiles
         if (ce != cudaSuccess) return (int)ce;
         attr_set = true;
     }
-    kern<<<dim3(nq, n_tiles), PT_THREADS, smem, s>>>(mq, mk, mv, (bf16*)out, tiles, table, max_blocks, bs,
-                                                       (int)__builtin_ctz(bs), box_rows, nq, nkv,
-                                                       scale * 1.4426950408889634f);
-    return launch_status();
+    return launch_pdl(kern, dim3(nq, n_tiles), dim3(PT_THREADS), smem, s, mq, mk, mv, (bf16*)out, tiles, table, max_blocks, bs,
+                      (int)__builtin_ctz(bs), box_rows, nq, nkv, scale * 1.4426950408889634f);
 }
 
 // qkv [T][(nq + 2 nkv) hd] bfloat16 (only q is read), out [T][nq hd]; the pools [num_pages][nkv][bs][hd].

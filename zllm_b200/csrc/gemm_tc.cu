@@ -280,6 +280,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
     const int k_per = (k_all + splits - 1) / splits;
     const int total_tiles = tiles_m * tiles_n * splits;
 
+    pdl_trigger();                                                       // the kernel after this one may set itself up
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(bars + 8 * s, 1);                                  // full: one arrive (expect_tx) + bytes
@@ -313,6 +314,23 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         if (lane == 0) {
             bool ok = true;
             int g = 0;                                                   // k steps issued over all tiles
+            // The weights of the first tile's first stages are requested before the wait on the
+            // kernel before this one (no kernel of a step writes weights); x comes after it.
+            int n_pre = 0;
+            if (walker < total_tiles && !c_tc_skip) {
+                const int ks = walker % splits, t2 = walker / splits;
+                const int n0 = (t2 / tiles_m) * BN + (PAIR ? rank * (BN / 2) : 0);
+                const int k_lo = ks * k_per;
+                n_pre = min(NSTAGE, max(0, min(k_all, k_lo + k_per) - k_lo));
+                for (int it = 0; it < n_pre; ++it) {
+                    const unsigned full = bars + 8 * it;
+                    if (!PAIR || rank == 0) mbar_expect_tx(full, (PAIR ? 2 : 1) * STAGE_BYTES);
+                    const unsigned w_dst = base + it * STAGE_BYTES + TC_A_BYTES;
+                    if (PAIR) tma_load_2d_pair(w_dst, &map_w, (k_lo + it) * TC_BK, n0, map_to_cta(full, 0));
+                    else tma_load_2d(w_dst, &map_w, (k_lo + it) * TC_BK, n0, full);
+                }
+            }
+            pdl_wait();
             for (int tile = walker; tile < total_tiles && ok; tile += n_walkers) {
                 const int ks = tile % splits, t2 = tile / splits;
                 const int m0 = (t2 % tiles_m) * ROWS_PER_TILE + rank * TC_BM;
@@ -325,17 +343,18 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                     const unsigned full = bars + 8 * s;
                     if (c_tc_skip) continue;                             // (tests: nothing is ever in flight)
                     const unsigned a_dst = base + s * STAGE_BYTES;
+                    const bool pre = g < n_pre;                          // expectation and weights: before the wait
                     if (PAIR) {
                         // the first CTA's barrier counts both CTAs' bytes; a copy may complete on it
                         // before the expectation is posted: the phase still waits for that arrival
-                        if (rank == 0) mbar_expect_tx(full, 2 * STAGE_BYTES);
+                        if (rank == 0 && !pre) mbar_expect_tx(full, 2 * STAGE_BYTES);
                         const unsigned full0 = map_to_cta(full, 0);
                         tma_load_2d_pair(a_dst, &map_x, (k_lo + it) * TC_BK, m0, full0);
-                        tma_load_2d_pair(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full0);
+                        if (!pre) tma_load_2d_pair(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full0);
                     } else {
-                        mbar_expect_tx(full, STAGE_BYTES);
+                        if (!pre) mbar_expect_tx(full, STAGE_BYTES);
                         tma_load_2d(a_dst, &map_x, (k_lo + it) * TC_BK, m0, full);
-                        tma_load_2d(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full);
+                        if (!pre) tma_load_2d(a_dst + TC_A_BYTES, &map_w, (k_lo + it) * TC_BK, n0, full);
                     }
                 }
             }
@@ -388,6 +407,7 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
         // not depend on any order).  The memory system sees whole rows of the box instead of 32
         // scattered 16-byte pieces per instruction, and nobody waits for the old residual.
         const int q = warp & 3;
+        pdl_wait();                                                      // before anything of the step is read or written
         unsigned char* stage0 = out_stage + (size_t)(warp - 2) * 2 * 4096;
         const int box_cols = mode == MODE_SWIGLU ? 16 : 32;                  // output columns per 32 accumulator columns
         bool ok = true;
@@ -509,6 +529,8 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
 // part [splits][M][w_rows] float32; a thread takes 4 consecutive outputs.
 __global__ void gemm_tc_reduce_kernel(const float* part, int splits, int M, int w_rows, void* out,
                                       int N, int mode, int out_bf16) {
+    pdl_trigger();
+    pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int n4 = N / 4;
     if (idx >= (long long)M * n4) return;
@@ -671,8 +693,8 @@ template <int BN, int PAIR>
 static void tc_start(int walkers, void* stream, const CUtensorMap& map_x, const CUtensorMap& map_w, const CUtensorMap& map_o,
                      int M, int N, int K, int mode, int out_bf16, int tiles_m, int tiles_n, int splits, const TcRope& rope) {
     if (!PAIR) {
-        gemm_tc_kernel<BN, 0><<<walkers, 192, TC_SMEM_OF(BN), (cudaStream_t)stream>>>(map_x, map_w, map_o, M, N, K, mode, out_bf16,
-                                                                                      tiles_m, tiles_n, splits, rope);
+        launch_pdl(gemm_tc_kernel<BN, 0>, dim3(walkers), dim3(192), TC_SMEM_OF(BN), (cudaStream_t)stream, map_x, map_w, map_o, M, N, K,
+                   mode, out_bf16, tiles_m, tiles_n, splits, rope);
         return;
     }
     cudaLaunchConfig_t cfg = {};
@@ -680,10 +702,12 @@ static void tc_start(int walkers, void* stream, const CUtensorMap& map_x, const 
     cfg.blockDim = dim3(192);
     cfg.dynamicSmemBytes = TC_PAIR_SMEM_OF(BN);
     cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl_enabled() ? 2 : 1;
     cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, 1>, map_x, map_w, map_o, M, N, K, mode, out_bf16, tiles_m, tiles_n, splits, rope);
 }
 
@@ -764,9 +788,8 @@ static int tc_launch(const void* x, const void* w, void* out, int M, int N, int 
     int rc = launch_status();
     if (rc || splits == 1) return rc;
     const long long n_thr = (long long)M * (N / 4);
-    gemm_tc_reduce_kernel<<<(unsigned)((n_thr + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-        (const float*)scratch, splits, M, w_rows, out, N, mode, out_bf16);
-    return launch_status();
+    return launch_pdl(gemm_tc_reduce_kernel, dim3((unsigned)((n_thr + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                      (const float*)scratch, splits, M, w_rows, out, N, mode, out_bf16);
 }
 
 ZLLM_API int zllm_gemm_tc_bf16(const void* x, const void* w, void* out, int M, int N, int K, int mode, int out_bf16,

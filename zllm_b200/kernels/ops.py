@@ -225,6 +225,11 @@ class CudaOps:
     STREAM_MAX_ROWS = 64
     STREAM_MIN_WEIGHTS = 12 * 1024 * 1024
     STREAM_MAX_WEIGHT_ROWS = 32768
+    # Rotation and cache write ride in the QKV product's epilogue only when the product has tiles for
+    # two waves, so that one tile's (slow, row-by-row) epilogue hides behind the next tile's MMAs:
+    # measured per 16-layer step, fused against a pass of its own over qkv: 2,048 rows 4.25 / 4.29 ms,
+    # 1,024 rows 3.02 / 2.93 ms, 128 rows 1.37 / 1.29 ms.
+    ROPE_IN_PRODUCT_MIN_ROWS = 2048
     UNFUSE_NORM_WEIGHT_ROWS = 32768
     SAMPLE_SCRATCH_ROWS = 1024
     TC_SCRATCH_BYTES = 64 * 1024 * 1024
@@ -313,7 +318,7 @@ class CudaOps:
             x = h
         # many rows: rotation and cache write in the epilogue of the tensor-core product (head sizes
         # 64 and 128, half-split pairs over the whole head); otherwise a pass of their own over qkv
-        if M > self.STREAM_MAX_ROWS and "gemm_tc" in self._libs and x.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16 \
+        if M >= self.ROPE_IN_PRODUCT_MIN_ROWS and "gemm_tc" in self._libs and x.dtype == torch.bfloat16 and qkv.dtype == torch.bfloat16 \
                 and w_qkv.dtype == torch.bfloat16 and hd in (64, 128) and K % 8 == 0 \
                 and (rot is None or (rot.rot_dim == hd and not rot.interleaved)) \
                 and (x.data_ptr() | w_qkv.data_ptr() | qkv.data_ptr()) & 15 == 0:
