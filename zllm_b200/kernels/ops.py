@@ -114,6 +114,9 @@ class CudaOps:
         build.build(names)
         for n in names:
             self._libs[n] = build.load(n)
+        if dtype == torch.bfloat16 and os.environ.get("ZLLM_GEMM_PAIR", "") == "0":
+            # measurement switch: the many-row products on single CTAs (tiles of 128 rows) only
+            self._libs["gemm_tc"].zllm_gemm_tc_force_pair(0)
         # a word of pinned host memory per kernel family with bounded waits: a wait that gives up
         # writes its code there too, so the engine sees it where it synchronises anyway, without a copy
         if self._error_words is None:
