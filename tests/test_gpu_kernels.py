@@ -155,6 +155,21 @@ def test_many_row_product_with_split_k(ops, M, N, K, mode, tile, pair):
         lib.zllm_gemm_tc_force_pair(-1)
 
 
+@pytest.mark.parametrize("slices", [1, 3, 5, 32])
+@pytest.mark.parametrize("M,N,K,mode", [(128, 2048, 2048, "add"), (300, 264, 4104, "store"), (512, 2048, 8192, "add"),
+                                        (96, 520, 1352, "swiglu"), (1024, 2048, 8192, "add")])
+def test_many_row_product_with_forced_slices(ops, M, N, K, mode, slices):
+    """The number of slices of K is chosen by a model of the kernel's time; here it is forced: one
+    slice, counts that do not divide the k steps (ragged and empty last slices), and more than
+    the product allows (clamped to one slice per four k steps and to the scratch)."""
+    lib = ops.lib("gemm_tc")
+    assert lib.zllm_gemm_tc_force_splits(slices) == 0
+    try:
+        _many_row_product(ops, M, N, K, mode)
+    finally:
+        lib.zllm_gemm_tc_force_splits(0)
+
+
 def _many_row_product(ops, M, N, K, mode):
     dtype = torch.bfloat16
     x = rnd((M, K), dtype, 5)

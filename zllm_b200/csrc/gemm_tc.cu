@@ -512,7 +512,9 @@ __global__ void __launch_bounds__(192, 1) gemm_tc_kernel(const __grid_constant__
                 else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
             }
         }
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // all tiles are in global memory
+        // the staging tiles have been read; the writes themselves complete with the grid, which is
+        // what the kernel after this one waits for
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         (void)box_cols;
     }
     tc_fence_before();
@@ -663,6 +665,7 @@ static int make_part_map(CUtensorMap* map, void* ptr, int splits, int M, int w_r
 // scratch (may be null): float32 workspace of scratch_bytes for products with few tiles, whose K is
 // then split over more CTAs and summed in a second pass, in a fixed order.
 static int g_force_bn = 0;
+static int g_force_splits = 0;          // 0: by the sizes
 static int g_force_pair = -1;           // -1: by the sizes; 0: never pairs of CTAs; 1: pairs whenever there are two row tiles
 
 template <int BN, int PAIR>
@@ -744,33 +747,42 @@ static int tc_launch(const void* x, const void* w, void* out, int M, int N, int 
     if (g_force_pair == 0) pair = 0;
     const int walkers_all = pair ? cap[0][1] : n_sm;               // tile walkers: CTAs, or pairs
     const int tiles_m = pair ? (M + 2 * TC_BM - 1) / (2 * TC_BM) : (M + TC_BM - 1) / TC_BM;
-    // Tiles of 256 weight rows; of 128 when those would leave half of the SMs without a tile.  A
-    // narrow tile loads as many bytes of x per k step for half the arithmetic, so with a long K and
-    // more than two row tiles the wide tile with K split over more CTAs is the faster one
-    // (measured: 512 rows, K 8192: 26.7 us wide, 30.5 us narrow; K 2048: 16.4 and 15.1).  The choice
-    // depends on the sizes only.
+    // Tile width (256, 192 or 128 weight rows) and slices of K by a small model of the kernel's time,
+    // calibrated on this kernel: a k step is bound by what a CTA loads (x 16 KB + its weight rows;
+    // measured 0.44 us for a pair's 32 KB, 0.49 us for a single CTA's 48 KB), a tile costs its k steps
+    // plus an epilogue, the tiles run in waves over the walkers, and slices of K cost a second pass
+    // that sums them in a fixed order.  Few tiles with a long K get wide tiles and slices (512 rows,
+    // K 8192, 2048 weight rows: 16 tiles of 256 in 4 slices instead of 22 of 192 in 2); many tiles get
+    // the width that fills the last wave.  The choice depends on the sizes only.
     const int k_all = (K + TC_BK - 1) / TC_BK;
-    const int row_tiles = (M + TC_BM - 1) / TC_BM;
-    int bn = tiles_m * ((w_rows + TC_BN - 1) / TC_BN) * 2 <= walkers_all && (k_all <= 64 || row_tiles <= 2) ? TC_BN_HALF : TC_BN;
-    if (mode == MODE_ROPE && bn % rope.hd) bn = TC_BN;             // no head may straddle a tile
-    if (bn == TC_BN) {
-        // More tiles than SMs: the time is the number of waves times the tile's width.  Tiles of 192
-        // weight rows when that product is smaller (192 tiles of 256 rows on 148 SMs are two waves
-        // with the second a third full; 256 tiles of 192 rows are two waves of three quarters the work).
-        auto cost = [&](int w) { const long long t = (long long)tiles_m * ((w_rows + w - 1) / w); return ((t + walkers_all - 1) / walkers_all) * w; };
-        if (cost(TC_BN_MID) < cost(TC_BN) && !(mode == MODE_ROPE && TC_BN_MID % rope.hd)) bn = TC_BN_MID;
+    const bool can_split = mode != MODE_ROPE && scratch != nullptr && (w_rows % 4) == 0 && (((uintptr_t)scratch & 15) == 0);
+    int bn = 0, splits = 1;
+    double best = 0.0;
+    const int widths[3] = {TC_BN, TC_BN_MID, TC_BN_HALF};
+    const int forced = g_force_bn && !(mode == MODE_ROPE && g_force_bn % rope.hd) ? g_force_bn : 0;
+    for (int wi = 0; wi < 3; ++wi) {
+        const int w = widths[wi];
+        if (forced && w != forced) continue;
+        if (mode == MODE_ROPE && w % rope.hd) continue;            // no head may straddle a tile
+        const long long tiles = (long long)tiles_m * ((w_rows + w - 1) / w);
+        const double kstep = pair ? 0.4375 * (16.0 + w / 16.0) / 32.0 : 0.488 * (16.0 + w / 8.0) / 48.0;
+        int s_max = can_split ? (k_all / 4 < 1 ? 1 : (k_all / 4 > 32 ? 32 : k_all / 4)) : 1;
+        const long long s_room = scratch_bytes / ((long long)M * w_rows * 4);      // slices the scratch holds
+        if (s_max > 1 && s_room < s_max) s_max = s_room < 1 ? 1 : (int)s_room;
+        for (int sp = 1; sp <= s_max; ++sp) {
+            if (g_force_splits && sp != (g_force_splits < s_max ? g_force_splits : s_max)) continue;
+            const long long units = tiles * sp;
+            const long long waves = (units + walkers_all - 1) / walkers_all;
+            const int k_per = (k_all + sp - 1) / sp;
+            double t = waves * (k_per * kstep + 0.5 + (sp > 1 ? 2.0 : 1.0) * w / 256.0) + 2.0;
+            if (sp > 1) t += 5.0 + (double)M * w_rows * sp * 4.0 / 3e6;
+            if (bn == 0 || t < best - 1e-9) { best = t; bn = w; splits = sp; }
+        }
     }
-    if (g_force_bn && !(mode == MODE_ROPE && g_force_bn % rope.hd)) bn = g_force_bn;
+    if (bn == 0) return ZLLM_ERR_UNSUPPORTED;
     e = make_map(&map_w, w, w_rows, K, pair ? bn / 2 : bn);
     if (e) return e;
     const int tiles_n = (w_rows + bn - 1) / bn;
-    // still few tiles: split K until about every SM has a unit of work, each with at least 4 k
-    // steps, and sum the slices in a second pass, in a fixed order
-    int splits = 1;
-    while (mode != MODE_ROPE && tiles_n * tiles_m * splits * 2 <= walkers_all && k_all / (splits * 2) >= 4 && splits < 32) splits *= 2;
-    if (splits > 1 && (scratch == nullptr || (long long)splits * M * w_rows * 4 > scratch_bytes || (w_rows % 4) ||
-                       ((uintptr_t)scratch & 15)))
-        splits = 1;
     if (splits > 1) {
         e = make_part_map(&map_o, scratch, splits, M, w_rows);
         if (e) return e;
@@ -821,6 +833,13 @@ ZLLM_API int zllm_gemm_tc_qkv_rope(const void* x, const void* w, void* qkv, int 
 ZLLM_API int zllm_gemm_tc_force_tile(int bn) {
     if (bn != 0 && bn != TC_BN && bn != TC_BN_HALF && bn != TC_BN_MID) return ZLLM_ERR_UNSUPPORTED;
     g_force_bn = bn;
+    return 0;
+}
+
+// Tests and measurements: the number of slices of K (0: by the sizes; more than a product allows: as many as it allows).
+ZLLM_API int zllm_gemm_tc_force_splits(int n) {
+    if (n < 0 || n > 32) return ZLLM_ERR_UNSUPPORTED;
+    g_force_splits = n;
     return 0;
 }
 
