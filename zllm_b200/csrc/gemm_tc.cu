@@ -686,7 +686,10 @@ static cudaError_t tc_prepare(int* max_walkers, int n_sm) {
         cfg.attrs = at; cfg.numAttrs = 1;
         int n = 0;
         ce = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, PAIR>, &cfg);
-        if (ce != cudaSuccess) return ce;
+        if (ce != cudaSuccess) {                                   // no pairs on this device: single CTAs do all the work
+            cudaGetLastError();
+            n = 0;
+        }
         *max_walkers = n;
     }
     return cudaSuccess;
