@@ -181,6 +181,33 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
     }
     pdl_wait();
 
+    // What the epilogue of the CTA's first tile will need from global memory is requested now, so
+    // that it is there when the products are done instead of costing the kernel's tail up to three
+    // round trips one after the other (slot -> position -> page and rotation): the old residual
+    // (add), or the row's slot, position, page and rotation pair (rope).  blockDim covers every
+    // (row, weight row) of a tile, so a thread's place in the epilogue is known: i = threadIdx.x.
+    float e_cur = 0.f, e_cos = 1.f, e_sin = 0.f;
+    int e_slot = -1, e_pos = 0, e_page = -1;
+    if (crank == 0 && p.mode == MODE_ADD && (int)threadIdx.x < 16 * M) {
+        const int n = tile0 * 16 + (threadIdx.x & 15);
+        if (n < p.N) e_cur = reinterpret_cast<const float*>(p.out)[(size_t)(threadIdx.x >> 4) * p.N + n];
+    }
+    if (p.mode == MODE_ROPE && (int)threadIdx.x < 8 * M) {
+        const int m = threadIdx.x >> 3, j = threadIdx.x & 7;
+        e_slot = p.row_slot[m];
+        e_pos = p.positions[m];
+        if (e_slot >= 0) {
+            if (p.store) e_page = p.table[(size_t)e_slot * p.max_blocks + e_pos / p.bs];
+            const int tiles_per_head = p.hd / 16;
+            const int head = tile0 / tiles_per_head, part = tile0 - head * tiles_per_head;
+            if (head < p.nq + p.nkv && p.cos_t != nullptr) {
+                const int jj = part * 8 + j;                                 // index of the pair, in both layouts
+                e_cos = p.cos_t[(size_t)e_pos * (p.hd / 2) + jj];
+                e_sin = p.sin_t[(size_t)e_pos * (p.hd / 2) + jj];
+            }
+        }
+    }
+
     for (int ps = crank; ps < n_pass; ps += ksplit) {
         const int kb = ps * GD_PASS + warp * GD_KW;                          // this warp's 256 k of the pass
         // stage x[0..M)[kb .. kb+256) as bf16; lane takes 8 consecutive k of every row
@@ -300,8 +327,11 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
             if (n >= p.N) continue;
             const float v = total(r, m);
             const size_t o = (size_t)m * p.N + n;
-            if (mode == MODE_ADD) reinterpret_cast<float*>(p.out)[o] += v;
-            else if (p.out_bf16) reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v);
+            if (mode == MODE_ADD) {
+                // (i == threadIdx.x: one pass of this loop covers a tile)
+                if (rt_cur == 0) reinterpret_cast<float*>(p.out)[o] = e_cur + v;
+                else reinterpret_cast<float*>(p.out)[o] += v;
+            } else if (p.out_bf16) reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(v);
             else reinterpret_cast<float*>(p.out)[o] = v;
         }
     } else if (mode == MODE_SWIGLU) {
@@ -321,17 +351,18 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
         const bool rotated = head < p.nq + p.nkv;
         for (int i = threadIdx.x; i < 8 * M; i += blockDim.x) {
             const int m = i >> 3, j = i & 7;
-            const int slot = p.row_slot[m];
+            const int slot = e_slot;                                         // (i == threadIdx.x)
             if (slot < 0) continue;                                          // padding row of a graph bucket
             float a = total(j, m), b = total(j + 8, m);
             int da, db;                                                      // dims within the head
             if (!rotated) { da = part * 16 + j; db = da + 8; }
             else if (p.interleaved) { da = part * 16 + 2 * j; db = da + 1; }
             else { da = part * 8 + j; db = da + half; }
-            const int pos = p.positions[m];
+            const int pos = e_pos;
             if (rotated && p.cos_t != nullptr) {
                 const int jj = p.interleaved ? (da >> 1) : da;               // index of the pair
-                const float c = p.cos_t[(size_t)pos * half + jj], s = p.sin_t[(size_t)pos * half + jj];
+                float c = e_cos, s = e_sin;
+                if (rt_cur > 0) { c = p.cos_t[(size_t)pos * half + jj]; s = p.sin_t[(size_t)pos * half + jj]; }
                 const float ar = a * c - b * s, br = a * s + b * c;
                 a = ar; b = br;
             }
@@ -341,7 +372,7 @@ __global__ void __launch_bounds__(GD_WARPS * 32, 2) gemm_decode_kernel(const Gem
                 o[da] = ha; o[db] = hb;
             }
             if (head >= p.nq && p.store) {
-                const int page = p.table[(size_t)slot * p.max_blocks + pos / p.bs];
+                const int page = e_page;
                 if (page < 0) continue;
                 const bool is_k = head < p.nq + p.nkv;
                 const int kvh = is_k ? head - p.nq : head - p.nq - p.nkv;
