@@ -41,8 +41,8 @@ class RefOps:
         out.copy_(table[token_ids.long()].float())
 
     # ---- BNORM (shaders.rs:545-564) --------------------------------------------------
-    def rmsnorm(self, x, weight, eps, out):
-        xf = x.float()
+    def rmsnorm(self, x, weight, eps, out, rows=None):
+        xf = x.float() if rows is None else x[rows.long()].float()
         inv = torch.rsqrt((xf * xf).mean(dim=-1, keepdim=True) + eps)
         out.copy_((xf * inv * weight.float()).to(out.dtype))
 
@@ -132,9 +132,9 @@ class RefOps:
             out[t].copy_(o.reshape(-1).to(out.dtype))
 
     # ---- fused forms (the compositions they stand for) ----------------------------------------
-    def linear_normed(self, x, norm_w, eps, w, out, mode, ws):
-        h = torch.empty(x.shape, dtype=w.dtype)
-        self.rmsnorm(x, norm_w, eps, h)
+    def linear_normed(self, x, norm_w, eps, w, out, mode, ws, rows=None):
+        h = torch.empty((out.shape[0], x.shape[1]), dtype=w.dtype)
+        self.rmsnorm(x, norm_w, eps, h, rows=rows)
         self.linear(h, w, out, mode)
 
     def qkv_rope_store(self, x, norm, w_qkv, qkv, ctx, rot, cache, nq, nkv, hd, write_cache, ws):

@@ -52,6 +52,42 @@ def test_rmsnorm(ops, H, T, wdtype, odtype):
     assert float((out.cpu().float() - want.float()).abs().max()) <= tol * float(want.float().abs().max())
 
 
+@pytest.mark.parametrize("H", [72, 2048, 8200])
+def test_rmsnorm_of_chosen_rows(ops, H):
+    """The norm of x[rows]: the rows whose logits are wanted go straight to the head's input (a
+    row may be named twice, the order is free)."""
+    x = rnd((9, H), torch.float32, 1, 3.0)
+    w = 1 + rnd((H,), torch.float32, 2, 0.1)
+    rows = torch.tensor([8, 0, 3, 3, 5], dtype=torch.int32)
+    out = torch.empty(5, H, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(x.to(DEV), w.to(DEV), 1e-6, out, rows=rows.to(DEV))
+    want = torch.empty(5, H, dtype=torch.bfloat16)
+    REF.rmsnorm(x[rows.long()], w, 1e-6, want)
+    assert torch.equal(out.cpu(), want) or float((out.cpu().float() - want.float()).abs().max()) <= 2 ** -7 * float(want.float().abs().max())
+    whole = torch.empty(9, H, dtype=torch.bfloat16, device=DEV)
+    ops.rmsnorm(x.to(DEV), w.to(DEV), 1e-6, whole)
+    assert torch.equal(out.cpu(), whole.cpu()[rows.long()])           # the same numbers as the rows of the whole
+
+
+@pytest.mark.parametrize("M,N", [(3, 264), (5, 40000)])               # the fused product, and the norm as a kernel of its own
+def test_linear_normed_of_chosen_rows(ops, M, N):
+    from zllm_b200.engine.batch import Workspace
+    K = 256
+    x = rnd((12, K), torch.float32, 1, 2.0)
+    nw = 1 + rnd((K,), torch.float32, 2, 0.1)
+    w = rnd((N, K), torch.bfloat16, 3, K ** -0.5)
+    rows = torch.tensor([11, 2, 7, 7, 0][:M], dtype=torch.int32)
+    ws = Workspace(64, DEV)
+    out = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+    ops.linear_normed(x.to(DEV), nw.to(DEV), 1e-5, w.to(DEV), out, "store", ws, rows=rows.to(DEV))
+    gathered = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+    ops.linear_normed(x[rows.long()].contiguous().to(DEV), nw.to(DEV), 1e-5, w.to(DEV), gathered, "store", ws)
+    assert torch.equal(out.cpu(), gathered.cpu())
+    want = torch.zeros(M, N)
+    REF.linear_normed(x, nw, 1e-5, w, want, "store", None, rows=rows)
+    assert float((out.cpu() - want).abs().max()) <= 2 ** -7 * max(1.0, float(want.abs().max()))
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_silu_mul(ops, dtype):
     a, b = rnd((7, 333), dtype, 3, 2.0), rnd((7, 333), dtype, 4)

@@ -35,13 +35,17 @@ ZLLM_API int zllm_embedding(const int* tok, const void* table, float* out, int T
 
 // ---------------------------------------------------------------- rmsnorm
 // y = x * rsqrt(mean(x^2) + eps) * w ; x float32 [T,H]; w float32 or bf16; y AT.
+// ``rows`` (may be null): y[t] is the norm of x[rows[t]] -- the rows whose logits are wanted go
+// from the residual straight to the head's input, without a copy of their own.  The index list is
+// an input of the step (no kernel writes it), so it is read before the wait.
 template <typename WT, typename OT>
-__global__ void rmsnorm_kernel(const float* x, const WT* __restrict__ w, OT* y, int H,
+__global__ void rmsnorm_kernel(const float* x, const int* __restrict__ rows, const WT* __restrict__ w, OT* y, int H,
                                float eps) {
     __shared__ float red[33];
     pdl_trigger();
+    const int src = rows != nullptr ? rows[blockIdx.x] : (int)blockIdx.x;
     pdl_wait();
-    const float* xr = x + (size_t)blockIdx.x * H;
+    const float* xr = x + (size_t)src * H;
     float ss = 0.f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = xr[i]; ss += v * v; }
     ss = block_sum(ss, red);
@@ -52,12 +56,13 @@ __global__ void rmsnorm_kernel(const float* x, const WT* __restrict__ w, OT* y, 
 
 // The same with 16-byte loads and the row kept in registers (H % 4 == 0, H <= 256 * 4 * RV).
 template <typename WT, typename OT, int RV>
-__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* x, const WT* __restrict__ w,
-                                                          OT* y, int H, float eps) {
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* x, const int* __restrict__ rows,
+                                                          const WT* __restrict__ w, OT* y, int H, float eps) {
     __shared__ float red[33];
     pdl_trigger();
+    const int src = rows != nullptr ? rows[blockIdx.x] : (int)blockIdx.x;
     pdl_wait();
-    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * H);
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * H);
     const int n4 = H >> 2;
     float4 v[RV];
     float ss = 0.f;
@@ -90,24 +95,24 @@ __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* x, const 
 }
 
 template <typename WT, typename OT>
-static int launch_rmsnorm(const float* x, const void* w, void* y, int T, int H, float eps, cudaStream_t s) {
+static int launch_rmsnorm(const float* x, const int* rows, const void* w, void* y, int T, int H, float eps, cudaStream_t s) {
     const bool vec = (H % 4 == 0) && (((uintptr_t)x | (uintptr_t)y) % 16 == 0);
     if (vec && H <= 256 * 4 * 2)
-        return launch_pdl(rmsnorm_vec_kernel<WT, OT, 2>, dim3(T), dim3(256), 0, s, x, (const WT*)w, (OT*)y, H, eps);
+        return launch_pdl(rmsnorm_vec_kernel<WT, OT, 2>, dim3(T), dim3(256), 0, s, x, rows, (const WT*)w, (OT*)y, H, eps);
     if (vec && H <= 256 * 4 * 8)
-        return launch_pdl(rmsnorm_vec_kernel<WT, OT, 8>, dim3(T), dim3(256), 0, s, x, (const WT*)w, (OT*)y, H, eps);
+        return launch_pdl(rmsnorm_vec_kernel<WT, OT, 8>, dim3(T), dim3(256), 0, s, x, rows, (const WT*)w, (OT*)y, H, eps);
     const int th = H >= 1024 ? 256 : 128;
-    return launch_pdl(rmsnorm_kernel<WT, OT>, dim3(T), dim3(th), 0, s, x, (const WT*)w, (OT*)y, H, eps);
+    return launch_pdl(rmsnorm_kernel<WT, OT>, dim3(T), dim3(th), 0, s, x, rows, (const WT*)w, (OT*)y, H, eps);
 }
 
-ZLLM_API int zllm_rmsnorm(const float* x, const void* w, void* y, int T, int H, float eps, int w_bf16, int out_bf16,
+ZLLM_API int zllm_rmsnorm(const float* x, const int* rows, const void* w, void* y, int T, int H, float eps, int w_bf16, int out_bf16,
                           void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (w_bf16 && out_bf16) return launch_rmsnorm<bf16, bf16>(x, w, y, T, H, eps, s);
-    if (w_bf16) return launch_rmsnorm<bf16, float>(x, w, y, T, H, eps, s);
-    if (out_bf16) return launch_rmsnorm<float, bf16>(x, w, y, T, H, eps, s);
-    return launch_rmsnorm<float, float>(x, w, y, T, H, eps, s);
+    if (w_bf16 && out_bf16) return launch_rmsnorm<bf16, bf16>(x, rows, w, y, T, H, eps, s);
+    if (w_bf16) return launch_rmsnorm<bf16, float>(x, rows, w, y, T, H, eps, s);
+    if (out_bf16) return launch_rmsnorm<float, bf16>(x, rows, w, y, T, H, eps, s);
+    return launch_rmsnorm<float, float>(x, rows, w, y, T, H, eps, s);
 }
 
 // ---------------------------------------------------------------- silu * up

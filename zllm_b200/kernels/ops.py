@@ -179,13 +179,18 @@ class CudaOps:
         self._check(code, "embedding")
 
     # ---- rmsnorm -------------------------------------------------------
-    def rmsnorm(self, x, weight, eps, out):
+    def rmsnorm(self, x, weight, eps, out, rows=None):
+        """out[t] = rmsnorm(x[t]), or of x[rows[t]] when an int32 index list is given."""
         self._dev(x, weight, out)
-        T, H = x.shape
-        if x.dtype != torch.float32 or weight.numel() != H or tuple(out.shape) != (T, H) \
+        T, H = out.shape
+        if x.dtype != torch.float32 or weight.numel() != H or x.shape[1] != H or (rows is None and x.shape[0] != T) \
                 or weight.dtype not in (torch.float32, torch.bfloat16) or out.dtype not in (torch.float32, torch.bfloat16):
             raise BackendError("rmsnorm: bad operand types or shapes")
-        code = self.lib("elementwise").zllm_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), c_int(T), c_int(H), c_float(eps),
+        if rows is not None:
+            self._dev(rows)
+            if rows.dtype != torch.int32 or rows.numel() != T:
+                raise BackendError("rmsnorm: the row list does not match the output")
+        code = self.lib("elementwise").zllm_rmsnorm(_ptr(x), _ptr(rows), _ptr(weight), _ptr(out), c_int(T), c_int(H), c_float(eps),
                                                     c_int(weight.dtype == torch.bfloat16),
                                                     c_int(out.dtype == torch.bfloat16), self._stream())
         self._check(code, "rmsnorm")
@@ -275,26 +280,33 @@ class CudaOps:
                 and not self._streams(M, w)
                 and (x.data_ptr() | w.data_ptr() | (norm_w.data_ptr() if norm_w is not None else 0)) & 15 == 0)
 
-    def linear_normed(self, x, norm_w, eps, w, out, mode, ws):
+    def linear_normed(self, x, norm_w, eps, w, out, mode, ws, rows=None):
         """out = epilogue(rmsnorm(x; norm_w, eps) w^T), x the float32 residual.  One kernel for decode
-        batches; otherwise the norm kernel into a scratch buffer, then the product."""
+        batches; otherwise the norm kernel into a scratch buffer, then the product.  ``rows`` (an
+        int32 index list): the product is taken over x[rows] -- the norm kernel reads those rows
+        where it stands alone, otherwise they are gathered first."""
         self._dev(x, norm_w, w, out)
-        M, K = x.shape
-        N = out.shape[1]
-        if x.dtype != torch.float32 or norm_w.numel() != K or w.shape[1] != K or out.shape[0] != M \
-                or w.shape[0] != (2 * N if mode == "swiglu" else N):
+        K = x.shape[1]
+        M, N = out.shape
+        if x.dtype != torch.float32 or norm_w.numel() != K or w.shape[1] != K or w.shape[0] != (2 * N if mode == "swiglu" else N) \
+                or (rows is None and x.shape[0] != M) or (rows is not None and rows.numel() != M):
             raise BackendError("linear_normed: bad operand types or shapes")
         # The fused form has every CTA read the float32 rows of x again (4 M K bytes beside its own
         # 32 K bytes of weights per 16 rows): from a few rows on and for matrices of many rows the
         # norm as a kernel of its own and bfloat16 rows are faster (8 rows: the head 90 against 130 us,
         # gate/up 16.7 against 18.9 us; one row: 88 against 100 and 16.3 against 15.1)
         unfuse = w.shape[0] >= self.UNFUSE_NORM_WEIGHT_ROWS and M >= (1 if w.shape[0] >= self.STREAM_MAX_WEIGHT_ROWS else 4)
-        if self._can_fuse_decode(x, norm_w, w, M, K) and not unfuse and not (mode == "swiglu" and N % 8) \
-                and not (mode == "add" and out.dtype != torch.float32):
+        fused = self._can_fuse_decode(x, norm_w, w, M, K) and not unfuse and not (mode == "swiglu" and N % 8) \
+            and not (mode == "add" and out.dtype != torch.float32)
+        if fused:
+            if rows is not None:
+                g = ws.get("normed_rows", (M, K), torch.float32)
+                self.gather_rows(x, rows, g)
+                x = g
             self._gemm_decode(x, norm_w, eps, w, out, mode, M, N, K)
             return
         h = ws.get("normed", (M, K), self.dtype)
-        self.rmsnorm(x, norm_w, eps, h)
+        self.rmsnorm(x, norm_w, eps, h, rows=rows)
         self.linear(h, w, out, mode)
 
     def qkv_rope_store(self, x, norm, w_qkv, qkv, ctx, rot, cache, nq, nkv, hd, write_cache, ws):

@@ -198,13 +198,14 @@ class DecoderModel:
         R = ctx.R
         if R == 0:
             return None
-        rows = ctx.ws.get("head_rows", (R, self.spec.hidden_size), torch.float32, cap=R)
-        ops.gather_rows(x, ctx.want_rows, rows)
         logits = ctx.ws.get("logits", (R, self.spec.vocab_size), torch.float32, cap=R)
         pro = self.final_norm.as_prologue()
         if pro is not None:
-            ops.linear_normed(rows, pro[0], pro[1], self.head, logits, "store", ctx.ws)
+            # a norm that can stand as a product's prologue also takes the wanted rows by index
+            ops.linear_normed(x, pro[0], pro[1], self.head, logits, "store", ctx.ws, rows=ctx.want_rows)
         else:
+            rows = ctx.ws.get("head_rows", (R, self.spec.hidden_size), torch.float32, cap=R)
+            ops.gather_rows(x, ctx.want_rows, rows)
             hn = ctx.ws.get("head_in", (R, self.spec.hidden_size), rt.dtype, cap=R)
             self.final_norm.forward(rows, hn, ctx)
             ops.linear(hn, self.head, logits, "store")
