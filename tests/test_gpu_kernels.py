@@ -354,6 +354,48 @@ def test_attention_finds_a_far_key_among_hundreds(ops, dtype):
         view.k_pages[page, :, far % bs] = saved
 
 
+@pytest.mark.parametrize("hd", [64, 80, 128])                 # 80: the mma.sync kernel, the others by TMA
+@pytest.mark.parametrize("n_ctx", [8200, 9100, 65500, 66000, 70100])    # 33, 36, 256, 258 and 274 splits of 256 keys
+def test_decode_attention_over_many_splits(ops, hd, n_ctx):
+    """Up to 32 splits are merged by one warp per (row, head), up to 255 by a block, from 256 on in
+    two passes (groups of 32, then the groups): eight full groups, a ninth group of two splits and
+    one of eighteen; beside a short row in the same launch (one split, one group).  One far key
+    per long row is made to stand out as well."""
+    nq, nkv, bs, dtype = 4, 2, 16, torch.bfloat16
+    cm = make_cache(nkv, hd, bs, n_ctx // bs + 40, 2, n_ctx + 300, dtype)
+    a, b = cm.admit(), cm.admit()
+    view = cm.view(0)
+    g = torch.Generator().manual_seed(17)
+    view.k_pages.copy_((torch.randn(view.k_pages.shape, generator=g) * 0.3).to(dtype))
+    view.v_pages.copy_(torch.randn(view.v_pages.shape, generator=g).to(dtype))
+    for slot, n in ((a, n_ctx - 1), (b, 200)):                # earlier contents: pages handed out, lengths advanced
+        assert cm.ensure(slot, n)
+        cm.advance(slot, n)
+    ctx = make_ctx(cm, [(a, 1), (b, 1)])
+    qkv = rnd((2, (nq + 2 * nkv) * hd), dtype, 18)
+    scale = 1.0 / math.sqrt(hd)
+    out = torch.zeros(2, nq * hd, dtype=dtype, device=DEV)
+    ops.paged_attention(qkv.to(DEV), out, ctx, view, nq, nkv, hd, scale, None)
+    want = torch.zeros(2, nq * hd)
+    REF.paged_attention(qkv.float(), want, cpu_ctx(ctx), CpuCacheView(view), nq, nkv, hd, scale, None)
+    assert float((out.cpu().float() - want).abs().max()) <= 0.02
+    # a far key in the last group's last split, and one in the first split
+    for far in (n_ctx - 300, 5):
+        page = int(view.block_table[a, far // bs])
+        direction = torch.randn(hd, generator=g)
+        direction /= direction.norm()
+        saved = view.k_pages[page, :, far % bs].clone()
+        view.k_pages[page, :, far % bs] = (direction * 40).to(dtype)
+        q2 = qkv.clone()
+        q2[0, :nq * hd] = (direction * 40).repeat(nq).to(dtype)
+        ops.paged_attention(q2.to(DEV), out, ctx, view, nq, nkv, hd, 1.0, None)
+        got = out[0].float().cpu().reshape(nq, hd)
+        for h in range(nq):
+            v = view.v_pages[page, h // (nq // nkv), far % bs].float().cpu()
+            assert float((got[h] - v).abs().max()) < 0.02, f"far key {far} head {h}"
+        view.k_pages[page, :, far % bs] = saved
+
+
 @pytest.mark.parametrize("slope", [0.0, 0.5, 3.0, -2.0])
 @pytest.mark.parametrize("hd,nq,nkv", [(64, 8, 2), (128, 4, 1)])
 def test_prefill_attention_when_the_maximum_keeps_moving(ops, slope, hd, nq, nkv):

@@ -115,39 +115,55 @@ __global__ void __launch_bounds__(NTHR) decode_combine_kernel(
     }
 }
 
-// The same merge for up to 32 splits (contexts up to 8,192) by ONE WARP per (row, head): lane s holds
-// split s's maximum and denominator, every lane takes HD / 32 dims and requests the numerators of
-// the first 16 splits BEFORE anything waits for the maxima, so the kernel is one round trip to L2
-// and a few shuffles, with no block-wide barrier (with the loads inside the loop over the splits
-// it was slower than the block kernel: a round trip per four splits; as it is, the batch-8 step
-// went from 0.988 to 0.975 ms and batch 64 from 24.0 k to 24.8 k tok/s).  The numerator is summed in split order, M and the denominator over a fixed
-// shuffle tree.  Eight warps per block.
+// The same merge by ONE WARP per (row, head): lane s holds split s's maximum and denominator, every
+// lane takes HD / 32 dims and requests the numerators of the first 16 splits BEFORE anything waits
+// for the maxima, so the kernel is one round trip to L2 and a few shuffles, with no block-wide
+// barrier (with the loads inside the loop over the splits it was slower than the block kernel: a
+// round trip per four splits; as it is, the batch-8 step went from 0.988 to 0.975 ms and batch 64
+// from 24.0 k to 24.8 k tok/s).  The numerator is summed in split order, M and the denominator over
+// a fixed shuffle tree.  Eight warps per block.
+// Up to 32 splits (contexts up to 8,192) in one pass (FINAL).  Up to 1,024 splits in two: a first
+// pass (not FINAL) merges every group of 32 splits into one partial of the same form (maximum,
+// denominator, numerators), written to the slots [slot_out, ..) that the caller left free behind
+// the row's own; the second pass merges those.  A row of 512 splits (131,000 positions) took the
+// block kernel 35 us, a third of such a step.
 #define COMBINE_WARP_MAX_SPLITS 32
-template <int HD>
+// Two passes pay from a few hundred splits on (batch 1: 131,000 positions 1.93 -> 1.64 ms, 65,536
+// 1.35 -> 1.31 ms; at 16,384 positions, 64 splits, two launches cost more than the block kernel:
+// 0.85 -> 0.93 ms).
+#define COMBINE_TWO_PASS_MIN_SPLITS 256
+template <int HD, bool FINAL>
 __global__ void __launch_bounds__(256) decode_combine_warp_kernel(
     const int* rows, const int* positions, const int* row_slot,
-    const float* part_o, const float* part_ml, bf16* out, int nq, int window,
-    int max_splits, int n_splits, int n_pairs) {
+    float* part_o, float* part_ml, bf16* out, int nq, int window,
+    int max_splits, int n_splits, int n_pairs, int slot_in, int level_div, int n_groups, int slot_out) {
     constexpr int DPL = (HD + 31) / 32;                      // dims per lane
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31;
-    const int pair = blockIdx.x * 8 + (threadIdx.x >> 5);    // (row index, head)
-    if (pair >= n_pairs) return;
+    const int item = blockIdx.x * 8 + (threadIdx.x >> 5);    // (row index, head, group of 32 inputs)
+    if (item >= n_pairs * n_groups) return;
+    const int pair = item / n_groups, grp = item - pair * n_groups;
     const int ri = pair / nq, h = pair - ri * nq;
     const int row = rows[ri];
     bf16* o = out + ((size_t)row * nq + h) * HD;
     if (row_slot[row] < 0) {
+        if (FINAL) {
 #pragma unroll
-        for (int j = 0; j < DPL; ++j)
-            if (lane + 32 * j < HD) o[lane + 32 * j] = __float2bfloat16_rn(0.f);
+            for (int j = 0; j < DPL; ++j)
+                if (lane + 32 * j < HD) o[lane + 32 * j] = __float2bfloat16_rn(0.f);
+        }
         return;
     }
     const int pos = positions[row];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int ns = min((pos - lo) / SPLIT_KEYS + 1, n_splits);
-    const size_t base = ((size_t)ri * nq + h) * max_splits;
-    // the numerators of the first 16 splits are requested before anything waits for M
+    const int ns_row = min((pos - lo) / SPLIT_KEYS + 1, n_splits);       // the row's splits
+    const int ns_in = (ns_row + level_div - 1) / level_div;              // inputs of this pass
+    const int first = grp * 32;
+    const int ns = min(32, ns_in - first);                               // inputs of this warp
+    if (ns <= 0) return;                                                 // (not FINAL: a group beyond the row's splits)
+    const size_t base = ((size_t)ri * nq + h) * max_splits + slot_in + first;
+    // the numerators of the first 16 inputs are requested before anything waits for M
     float ov[16][DPL];
 #pragma unroll
     for (int s = 0; s < 16; ++s)
@@ -169,7 +185,7 @@ __global__ void __launch_bounds__(256) decode_combine_warp_kernel(
     for (int s = 0; s < 16; ++s) {
         const float fs = __shfl_sync(0xffffffffu, f, s);
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) acc[j] += ov[s][j] * fs;      // splits beyond ns: 0 x 0
+        for (int j = 0; j < DPL; ++j) acc[j] += ov[s][j] * fs;      // inputs beyond ns: 0 x 0
     }
     for (int s = 16; s < ns; ++s) {
         const float fs = __shfl_sync(0xffffffffu, f, s);
@@ -177,10 +193,18 @@ __global__ void __launch_bounds__(256) decode_combine_warp_kernel(
         for (int j = 0; j < DPL; ++j)
             if (lane + 32 * j < HD) acc[j] += __ldcg(part_o + (base + s) * HD + lane + 32 * j) * fs;
     }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
+    if (FINAL) {
+        const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
-    for (int j = 0; j < DPL; ++j)
-        if (lane + 32 * j < HD) o[lane + 32 * j] = __float2bfloat16_rn(acc[j] * inv);
+        for (int j = 0; j < DPL; ++j)
+            if (lane + 32 * j < HD) o[lane + 32 * j] = __float2bfloat16_rn(acc[j] * inv);
+    } else {
+        const size_t dst = ((size_t)ri * nq + h) * max_splits + slot_out + grp;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j)
+            if (lane + 32 * j < HD) part_o[dst * HD + lane + 32 * j] = acc[j];
+        if (lane == 0) { part_ml[dst * 2] = M; part_ml[dst * 2 + 1] = L; }
+    }
 }
 
 // The merge after a decode kernel with ``n_splits`` splits in its grid (programmatic dependent launch).
@@ -189,10 +213,20 @@ static int launch_combine(int n_rows, int nq, int n_splits, cudaStream_t s, cons
                           const int* row_slot, const float* part_o, const float* part_ml, bf16* out, int window,
                           int max_splits) {
     constexpr int ONE = HD <= 32 ? 32 : (HD <= 64 ? 64 : 128);
-    if (n_splits <= COMBINE_WARP_MAX_SPLITS) {
-        const int n_pairs = n_rows * nq;
-        return launch_pdl(decode_combine_warp_kernel<HD>, dim3((n_pairs + 7) / 8), dim3(256), 0, s, rows, positions, row_slot,
-                          part_o, part_ml, out, nq, window, max_splits, n_splits, n_pairs);
+    const int n_pairs = n_rows * nq;
+    if (n_splits <= COMBINE_WARP_MAX_SPLITS)
+        return launch_pdl(decode_combine_warp_kernel<HD, true>, dim3((n_pairs + 7) / 8), dim3(256), 0, s, rows, positions, row_slot,
+                          (float*)part_o, (float*)part_ml, out, nq, window, max_splits, n_splits, n_pairs, 0, 1, 1, 0);
+    const int n_groups = (n_splits + COMBINE_WARP_MAX_SPLITS - 1) / COMBINE_WARP_MAX_SPLITS;
+    if (n_splits >= COMBINE_TWO_PASS_MIN_SPLITS && n_groups <= COMBINE_WARP_MAX_SPLITS && n_splits + n_groups <= max_splits) {
+        // two passes; the groups' partials go to the free slots behind the grid's own
+        int rc = launch_pdl(decode_combine_warp_kernel<HD, false>, dim3((n_pairs * n_groups + 7) / 8), dim3(256), 0, s, rows,
+                            positions, row_slot, (float*)part_o, (float*)part_ml, out, nq, window, max_splits, n_splits, n_pairs, 0,
+                            1, n_groups, n_splits);
+        if (rc) return rc;
+        return launch_pdl(decode_combine_warp_kernel<HD, true>, dim3((n_pairs + 7) / 8), dim3(256), 0, s, rows, positions, row_slot,
+                          (float*)part_o, (float*)part_ml, out, nq, window, max_splits, n_splits, n_pairs, n_splits,
+                          COMBINE_WARP_MAX_SPLITS, 1, 0);
     }
     if (n_splits <= 8)
         return launch_pdl(decode_combine_kernel<HD, ONE>, dim3(n_rows, nq), dim3(ONE), 0, s, rows, positions, row_slot, part_o,

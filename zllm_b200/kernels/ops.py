@@ -547,6 +547,9 @@ class CudaOps:
         if ctx.n_decode > 0:
             max_splits = max(1, -(-tb.shape[1] * cache.block_size // self.decode_split_keys))
             n_splits = min(max_splits, ctx.fixed_splits or self.decode_splits(ctx.max_context))
+            # slots per (row, head): the splits, and behind them room for the partials of a merge in
+            # two passes (one per 32 splits)
+            max_splits += -(-max_splits // 32)
             nd = ctx.n_decode
             part_o = ctx.ws.get("attn_part_o", (nd, nq * max_splits * hd), torch.float32, cap=nd)
             part_ml = ctx.ws.get("attn_part_ml", (nd, nq * max_splits * 2), torch.float32, cap=nd)
@@ -569,7 +572,8 @@ class CudaOps:
                     c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window or 0), _ptr(part_o), _ptr(part_ml),
                     c_int(n_splits), c_int(max_splits), self._stream())
                 self._check(code, "attention_decode_bf16")
-            self.launches += 1                  # split kernel + combine kernel
+            self.launches += 2 if 256 <= n_splits <= 1024 else 1               # split kernel + merge (in two passes
+                                                                                # from 256 to 1,024 splits)
         bs = cache.block_size
         tiles = ctx.aux.get("query_tiles")
         n_tiles = tiles.shape[0] if tiles is not None else 0
