@@ -133,6 +133,9 @@ STREAM_SHAPES = [  # rows, N, K, epilogue: what the TMA-fed streaming product ta
     (12, 4096, 3072, "store"), (9, 2048, 8192, "add"), (16, 8192, 1536, "swiglu"), (17, 48, 24, "store"),
     (33, 3072, 2048, "store"), (40, 2048, 8192, "add"), (64, 1000, 1032, "store"), (64, 4104, 520, "swiglu"),
     (23, 264, 4104, "add"), (32, 30000, 72, "store"),
+    # few rows on matrices that are large on both sides (from 5 rows; from one row with 50 M weights and a K of 4096)
+    (5, 3072, 3072, "add"), (8, 5120, 3072, "store"), (7, 3072, 8192, "add"), (6, 4096, 3072, "swiglu"),
+    (1, 12296, 4096, "store"), (3, 4096, 12296, "add"),
 ]
 
 

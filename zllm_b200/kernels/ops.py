@@ -225,7 +225,16 @@ class CudaOps:
         self._check(code, "gemm_plain")
 
     # Which kernel takes a bfloat16 product is decided by the sizes alone (never by trial):
-    #   rows <= 8: the fused decode product;  9..16: the same for small matrices (its fusions save
+    #   rows <= 8: the fused decode product -- except for models whose matrices are large on both
+    #   sides (STREAM_FEW_ROWS_MIN_SIDE: from 3B layer sizes on), whose products all go to the TMA-fed
+    #   streaming product from 5 rows on, and the largest of them (K of 4096 and more) at any row
+    #   count: the fused kernel streams weights through registers and reads the float32 rows again in
+    #   every CTA, which costs more the longer K is (8 rows at 8B layer sizes: 5.03 against 6.75 ms a
+    #   step, 1 row 3.65 against 3.94; at 3B sizes 2.81 against 3.02 at 5..8 rows and no gain below;
+    #   at 1B sizes the fused kernel wins: 0.966 against 1.006 ms with gate/up streamed).  All of a
+    #   model's products switch together: kernels with different shared-memory needs side by side
+    #   cost more than either kind alone (3B sizes, down alone streamed: 3.12 ms);
+    #   9..16: the fused product for small matrices (its fusions save
     #   kernels), the TMA-fed streaming product for matrices of STREAM_MIN_WEIGHTS elements and more;
     #   17..64: the streaming product, but matrices with STREAM_MAX_WEIGHT_ROWS rows and more (the
     #   vocabulary head) go to the many-row kernel, which re-reads x once per 256 rows, not per 128;
@@ -233,6 +242,8 @@ class CudaOps:
     STREAM_MAX_ROWS = 64
     STREAM_MIN_WEIGHTS = 12 * 1024 * 1024
     STREAM_MAX_WEIGHT_ROWS = 32768
+    STREAM_FEW_ROWS_MIN_SIDE = 3072
+    STREAM_ANY_ROWS_MIN_WEIGHTS = 50_000_000
     # Rotation and cache write ride in the QKV product's epilogue only when the product has tiles for
     # two waves, so that one tile's (slow, row-by-row) epilogue hides behind the next tile's MMAs:
     # measured per 16-layer step, fused against a pass of its own over qkv: 2,048 rows 4.25 / 4.29 ms,
@@ -269,6 +280,9 @@ class CudaOps:
 
     def _streams(self, M, w) -> bool:
         """True when a product of M rows with matrix w belongs to the streaming kernel."""
+        if M <= 8 and min(w.shape[0], w.shape[1]) >= self.STREAM_FEW_ROWS_MIN_SIDE and w.shape[0] < self.STREAM_MAX_WEIGHT_ROWS \
+                and (M >= 5 or (w.numel() >= self.STREAM_ANY_ROWS_MIN_WEIGHTS and w.shape[1] >= 4096)):
+            return True
         if M <= 8 or M > self.STREAM_MAX_ROWS:
             return False
         if M <= self.DECODE_MAX_ROWS:
