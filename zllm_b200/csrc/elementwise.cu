@@ -210,40 +210,48 @@ __global__ void __launch_bounds__(256) rope_kv_store_vec_kernel(bf16* qkv, const
                                                                 bf16* k_pages, bf16* v_pages,
                                                                 const int* __restrict__ table, int max_blocks, int bs,
                                                                 int nq, int nkv, int hd, int store) {
+    // The row's slot, position and page and the thread's first rotation factors are inputs of the
+    // step (no kernel of the step writes them): they are fetched BEFORE the wait on the kernel
+    // before, three dependent round trips that then cost nothing; after the wait only qkv is read.
     pdl_trigger();
-    pdl_wait();
     const int t = blockIdx.x;
     const int slot = row_slot[t];
-    if (slot < 0) return;
     const int pos = positions[t];
-    bf16* row = qkv + (size_t)t * (nq + 2 * nkv) * hd;
     const int half = hd >> 1;
     const int per_head = half >> 3;                                  // 8-pair groups per rotated head
     size_t kv_base = 0;
     bool have_page = false;
-    if (store) {
+    if (store && slot >= 0) {
         const int page = table[(size_t)slot * max_blocks + pos / bs];
         have_page = page >= 0;
         kv_base = ((size_t)(have_page ? page : 0) * nkv * bs + (size_t)(pos % bs)) * hd;   // + kvh * bs * hd
     }
     const int n_rot = (nq + nkv) * per_head;
     const int n_v = store ? nkv * (hd >> 3) : 0;
+    auto factors = [&](int i, float (&c)[8], float (&sn)[8]) {
+        if (cos_t != nullptr && i < n_rot) {
+            const int head = i / per_head, j = (i - head * per_head) * 8;
+            const float4* cp = reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j);
+            const float4* sp = reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j);
+            const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+            c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+            sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { c[e] = 1.f; sn[e] = 0.f; }
+        }
+    };
+    float c[8], sn[8];
+    if (slot >= 0) factors(threadIdx.x, c, sn);
+    pdl_wait();
+    if (slot < 0) return;
+    bf16* row = qkv + (size_t)t * (nq + 2 * nkv) * hd;
     for (int i = threadIdx.x; i < n_rot + n_v; i += blockDim.x) {
         if (i < n_rot) {
             const int head = i / per_head, j = (i - head * per_head) * 8;
             bf16* h = row + (size_t)head * hd;
             uint4 ra = *reinterpret_cast<uint4*>(h + j), rb = *reinterpret_cast<uint4*>(h + j + half);
-            float c[8], sn[8];
-            if (cos_t != nullptr) {
-                const float4* cp = reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j);
-                const float4* sp = reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j);
-                const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
-                c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
-                sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) { c[e] = 1.f; sn[e] = 0.f; }
-            }
+            if (i != (int)threadIdx.x) factors(i, c, sn);
             __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&ra);
             __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&rb);
 #pragma unroll
