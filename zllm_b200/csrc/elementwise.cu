@@ -61,9 +61,17 @@ __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* x, const 
     __shared__ float red[33];
     pdl_trigger();
     const int src = rows != nullptr ? rows[blockIdx.x] : (int)blockIdx.x;
+    const int n4 = H >> 2;
+    // the norm's weights are fetched before the wait (no kernel writes them): after it only x is read
+    float wv[RV][4];
+#pragma unroll
+    for (int r = 0; r < RV; ++r) {
+        const int i = threadIdx.x + r * 256;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wv[r][e] = i < n4 ? to_f32(w[4 * i + e]) : 0.f;
+    }
     pdl_wait();
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * H);
-    const int n4 = H >> 2;
     float4 v[RV];
     float ss = 0.f;
 #pragma unroll
@@ -79,9 +87,8 @@ __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* x, const 
     for (int r = 0; r < RV; ++r) {
         const int i = threadIdx.x + r * 256;
         if (i >= n4) continue;
-        const WT* wp = w + 4 * i;
-        const float o0 = v[r].x * inv * to_f32(wp[0]), o1 = v[r].y * inv * to_f32(wp[1]);
-        const float o2 = v[r].z * inv * to_f32(wp[2]), o3 = v[r].w * inv * to_f32(wp[3]);
+        const float o0 = v[r].x * inv * wv[r][0], o1 = v[r].y * inv * wv[r][1];
+        const float o2 = v[r].z * inv * wv[r][2], o3 = v[r].w * inv * wv[r][3];
         if (sizeof(OT) == 2) {
             __nv_bfloat162 a = __floats2bfloat162_rn(o0, o1), b = __floats2bfloat162_rn(o2, o3);
             uint2 pk;
