@@ -55,16 +55,17 @@ __global__ void __launch_bounds__(NTHR) decode_combine_kernel(
     __shared__ float s_red[NTHR / 32];
     __shared__ float s_acc[NTHR];
     pdl_trigger();
+    const int row = rows[blockIdx.x];                        // inputs of the step: read before the wait
+    const int slot_of_row = row_slot[row];
+    const int pos = positions[row];
     pdl_wait();
-    const int row = rows[blockIdx.x];
     const int h = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     bf16* o = out + ((size_t)row * nq + h) * HD;
-    if (row_slot[row] < 0) {
+    if (slot_of_row < 0) {
         for (int d = tid; d < HD; d += nthr) o[d] = __float2bfloat16_rn(0.f);
         return;
     }
-    const int pos = positions[row];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     // never beyond what the split kernel's grid wrote (a caller that passed too few splits for
     // this row gets the keys of the splits it asked for, not someone else's partials)
@@ -138,16 +139,21 @@ __global__ void __launch_bounds__(256) decode_combine_warp_kernel(
     float* part_o, float* part_ml, bf16* out, int nq, int window,
     int max_splits, int n_splits, int n_pairs, int slot_in, int level_div, int n_groups, int slot_out) {
     constexpr int DPL = (HD + 31) / 32;                      // dims per lane
+    // which row, its slot and its position are inputs of the step (no kernel of the step writes
+    // them): read before the wait, two dependent round trips that then cost nothing
     pdl_trigger();
-    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int item = blockIdx.x * 8 + (threadIdx.x >> 5);    // (row index, head, group of 32 inputs)
-    if (item >= n_pairs * n_groups) return;
-    const int pair = item / n_groups, grp = item - pair * n_groups;
+    const bool live = item < n_pairs * n_groups;
+    const int pair = live ? item / n_groups : 0, grp = item - pair * n_groups;
     const int ri = pair / nq, h = pair - ri * nq;
     const int row = rows[ri];
+    const int slot_of_row = row_slot[row];
+    const int pos = positions[row];
+    pdl_wait();
+    if (!live) return;
     bf16* o = out + ((size_t)row * nq + h) * HD;
-    if (row_slot[row] < 0) {
+    if (slot_of_row < 0) {
         if (FINAL) {
 #pragma unroll
             for (int j = 0; j < DPL; ++j)
@@ -155,7 +161,6 @@ __global__ void __launch_bounds__(256) decode_combine_warp_kernel(
         }
         return;
     }
-    const int pos = positions[row];
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int ns_row = min((pos - lo) / SPLIT_KEYS + 1, n_splits);       // the row's splits
     const int ns_in = (ns_row + level_div - 1) / level_div;              // inputs of this pass
