@@ -288,11 +288,12 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_stream_kernel(const __grid_co
             const int r = 16 * (crank + gi * csize) + 4 * q4;
             const int n = n0 + r;
             if (n >= p.N) continue;
-            float4 v = total4(m, r);
             const size_t o = (size_t)m * p.N + n;
+            float4 cur = make_float4(0.f, 0.f, 0.f, 0.f);    // the old residual is requested before the ranks' partials are summed
+            if (p.mode == MODE_ADD) cur = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.out) + o);
+            float4 v = total4(m, r);
             if (p.mode == MODE_ADD) {
                 float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
-                const float4 cur = *d;
                 v.x += cur.x; v.y += cur.y; v.z += cur.z; v.w += cur.w;
                 *d = v;
             } else if (p.out_bf16) {
